@@ -1,0 +1,127 @@
+/*
+ * Device-pointer C ABI of the GGUF row quantize / dequantize path, B200 build.
+ *
+ * The first group of functions keeps the names, argument order and status codes of upstream's
+ * native CUDA interface (upstream src/libgguf/libgguf_cuda/csrc/libgguf_cuda_native.h:10-107),
+ * which is what the upstream converter (csrc/quantize_gguf.cpp:1732-1931) and the upstream
+ * ctypes test bind.  Inputs and outputs of the row functions are DEVICE pointers.  All work is
+ * asynchronous on the context's stream (or the caller's stream for the *_on_stream variants);
+ * only libgguf_cuda_event_synchronize blocks.
+ *
+ * The second group ("additions") has no upstream counterpart; each is marked.
+ */
+#ifndef LIBGGUF_B200_CUDA_NATIVE_H
+#define LIBGGUF_B200_CUDA_NATIVE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(_WIN32) && !defined(__MINGW32__)
+#define LIBGGUF_CUDA_API __declspec(dllexport)
+#else
+#define LIBGGUF_CUDA_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* upstream libgguf_cuda_native.h:10-16 */
+enum libgguf_cuda_status {
+    LIBGGUF_CUDA_STATUS_SUCCESS = 0,
+    LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT = 1,
+    LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE = 2,
+    LIBGGUF_CUDA_STATUS_CUDA_ERROR = 3,
+    LIBGGUF_CUDA_STATUS_ALLOCATION_FAILED = 4
+};
+
+/* upstream libgguf_cuda_native.h:18-21 has F32 and F16; BF16 is an addition. */
+enum libgguf_cuda_dequantize_dtype {
+    LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32 = 0,
+    LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F16 = 1,
+    LIBGGUF_CUDA_DEQUANTIZE_DTYPE_BF16 = 2
+};
+
+typedef struct libgguf_cuda_context libgguf_cuda_context;
+typedef struct libgguf_cuda_buffer libgguf_cuda_buffer;
+typedef struct libgguf_cuda_event libgguf_cuda_event;
+typedef struct libgguf_cuda_host_buffer libgguf_cuda_host_buffer;
+
+/* ---- context, events (upstream libgguf_cuda_native.h:28-41) ---- */
+LIBGGUF_CUDA_API int libgguf_cuda_context_create(int device, libgguf_cuda_context **out);
+LIBGGUF_CUDA_API void libgguf_cuda_context_destroy(libgguf_cuda_context *ctx);
+LIBGGUF_CUDA_API const char *libgguf_cuda_last_error(const libgguf_cuda_context *ctx);
+LIBGGUF_CUDA_API int libgguf_cuda_event_create(libgguf_cuda_context *ctx, libgguf_cuda_event **out);
+LIBGGUF_CUDA_API void libgguf_cuda_event_destroy(libgguf_cuda_context *ctx, libgguf_cuda_event *event);
+LIBGGUF_CUDA_API int libgguf_cuda_event_record(libgguf_cuda_context *ctx, libgguf_cuda_event *event);
+LIBGGUF_CUDA_API int libgguf_cuda_event_synchronize(libgguf_cuda_context *ctx, libgguf_cuda_event *event);
+LIBGGUF_CUDA_API int libgguf_cuda_event_elapsed_ms(libgguf_cuda_context *ctx, const libgguf_cuda_event *start,
+                                                   const libgguf_cuda_event *end, float *out);
+
+/* ---- type queries (upstream libgguf_cuda_native.h:43-49) ---- */
+LIBGGUF_CUDA_API int libgguf_cuda_qtype_supported(int64_t qtype);
+LIBGGUF_CUDA_API int libgguf_cuda_qtype_needs_imatrix(int64_t qtype);
+LIBGGUF_CUDA_API int64_t libgguf_cuda_block_size(int64_t qtype);
+LIBGGUF_CUDA_API int64_t libgguf_cuda_row_size(int64_t qtype, int64_t n_per_row);
+LIBGGUF_CUDA_API int libgguf_cuda_dequantize_qtype_supported(int64_t qtype);
+LIBGGUF_CUDA_API int64_t libgguf_cuda_dequantize_block_size(int64_t qtype);
+LIBGGUF_CUDA_API int64_t libgguf_cuda_dequantize_row_size(int64_t qtype, int64_t n_per_row);
+
+/* ---- device and pinned-host buffers, grow-only (upstream libgguf_cuda_native.h:51-63) ---- */
+LIBGGUF_CUDA_API int libgguf_cuda_buffer_create(libgguf_cuda_context *ctx, size_t size, libgguf_cuda_buffer **out);
+LIBGGUF_CUDA_API void libgguf_cuda_buffer_destroy(libgguf_cuda_context *ctx, libgguf_cuda_buffer *buffer);
+LIBGGUF_CUDA_API int libgguf_cuda_buffer_resize_discard(libgguf_cuda_context *ctx, libgguf_cuda_buffer *buffer, size_t size);
+LIBGGUF_CUDA_API void *libgguf_cuda_buffer_data(libgguf_cuda_buffer *buffer);
+LIBGGUF_CUDA_API const void *libgguf_cuda_buffer_const_data(const libgguf_cuda_buffer *buffer);
+LIBGGUF_CUDA_API size_t libgguf_cuda_buffer_size(const libgguf_cuda_buffer *buffer);
+
+LIBGGUF_CUDA_API int libgguf_cuda_host_buffer_create(libgguf_cuda_context *ctx, size_t size, libgguf_cuda_host_buffer **out);
+LIBGGUF_CUDA_API void libgguf_cuda_host_buffer_destroy(libgguf_cuda_context *ctx, libgguf_cuda_host_buffer *buffer);
+LIBGGUF_CUDA_API int libgguf_cuda_host_buffer_resize_discard(libgguf_cuda_context *ctx, libgguf_cuda_host_buffer *buffer, size_t size);
+LIBGGUF_CUDA_API void *libgguf_cuda_host_buffer_data(libgguf_cuda_host_buffer *buffer);
+LIBGGUF_CUDA_API const void *libgguf_cuda_host_buffer_const_data(const libgguf_cuda_host_buffer *buffer);
+LIBGGUF_CUDA_API size_t libgguf_cuda_host_buffer_size(const libgguf_cuda_host_buffer *buffer);
+
+/* ---- async copies on the context stream (upstream libgguf_cuda_native.h:65-78) ---- */
+LIBGGUF_CUDA_API int libgguf_cuda_h2d(libgguf_cuda_context *ctx, libgguf_cuda_buffer *dst, size_t dst_offset,
+                                      const void *src, size_t size);
+LIBGGUF_CUDA_API int libgguf_cuda_d2h(libgguf_cuda_context *ctx, void *dst, const libgguf_cuda_buffer *src,
+                                      size_t src_offset, size_t size);
+
+/* ---- the hot path (upstream libgguf_cuda_native.h:80-105) ----
+ * device_imatrix may be NULL unless the type requires importance weights.  Unlike upstream's
+ * kernels, a non-NULL imatrix is honoured for every type whose CPU quantizer honours it. */
+LIBGGUF_CUDA_API int libgguf_cuda_quantize_f32_rows(libgguf_cuda_context *ctx, const float *device_input,
+                                                    const float *device_imatrix, void *device_output,
+                                                    int64_t qtype, int64_t rows, int64_t n_per_row);
+LIBGGUF_CUDA_API int libgguf_cuda_dequantize_rows(libgguf_cuda_context *ctx, const void *device_input, int64_t qtype,
+                                                  int64_t rows, int64_t n_per_row, int output_dtype,
+                                                  void *device_output);
+LIBGGUF_CUDA_API int libgguf_cuda_dequantize_rows_on_stream(const void *device_input, int64_t qtype, int64_t rows,
+                                                            int64_t n_per_row, int output_dtype,
+                                                            void *device_output, void *stream);
+
+/* ================= additions (no upstream counterpart) ================= */
+
+/* Same as libgguf_cuda_quantize_f32_rows but on the caller's stream (a cudaStream_t passed as
+ * void*) of the current device, without a context; this is what a framework binding that
+ * launches on "the current stream" needs.  Returns a libgguf_cuda_status. */
+LIBGGUF_CUDA_API int libgguf_cuda_quantize_f32_rows_on_stream(const float *device_input, const float *device_imatrix,
+                                                              void *device_output, int64_t qtype, int64_t rows,
+                                                              int64_t n_per_row, void *stream);
+
+/* Message of the last failing context-less call on this thread ("" if none). */
+LIBGGUF_CUDA_API const char *libgguf_cuda_thread_last_error(void);
+
+/* Number of kernels this library has launched in this process (all devices, all threads). */
+LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
+
+/* Builds (once per device) the IQ search tables a quantizer of this type needs, on the current
+ * device, and waits for the upload.  Optional: the row functions do it on first use. */
+LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LIBGGUF_B200_CUDA_NATIVE_H */

@@ -1,0 +1,630 @@
+// Row decoders: packed GGUF blocks -> fp32 / fp16 / bf16.
+//
+// One kernel template serves every type.  A CTA owns a tile of consecutive blocks:
+//   1. the tile's bytes are staged into shared memory with 16-byte loads from the 16-byte
+//      aligned span that covers it (block sizes such as 34, 110 or 210 bytes make per-block
+//      vector loads impossible; a span of blocks does not care),
+//   2. every thread decodes runs of 8 consecutive output elements from shared memory, so a warp
+//      writes 32 x 16 B (fp16/bf16) or 2 x 32 x 16 B (fp32) of contiguous output per step.
+// The arithmetic of each decoder follows the upstream scalar decoder expression by expression
+// (upstream csrc/dequant/dequant.cpp); products are formed in the same order because fp32
+// output must be bit-identical.  fp16/bf16 output is the round-to-nearest-even conversion of
+// that fp32 value.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
+#include "gguf_common.cuh"
+#include "gguf_tables.cuh"
+#include "kernels.h"
+
+namespace gguf {
+namespace {
+
+GGUF_D uint16_t ld16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+GGUF_D uint32_t ld32(const uint8_t *p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+
+// 6-bit scale / min pair j of a Q4_K / Q5_K block (upstream libgguf_common.h:672-684).
+GGUF_D void scale_min_k4(int j, const uint8_t *q, int &sc, int &m) {
+    if (j < 4) {
+        sc = q[j] & 63;
+        m = q[j + 4] & 63;
+    } else {
+        sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4);
+        m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4);
+    }
+}
+
+template <int TYPE>
+struct Decoder;
+
+// upstream dequant.cpp:120-134
+template <>
+struct Decoder<GGML_TYPE_Q8_0> {
+    static constexpr int ELEMS = 32, BYTES = 34;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)(int8_t)b[2 + e0 + i] * d;
+    }
+};
+
+// upstream dequant.cpp:21-35
+template <>
+struct Decoder<GGML_TYPE_Q4_0> {
+    static constexpr int ELEMS = 32, BYTES = 18;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int sh = e0 >= 16 ? 4 : 0;
+        const uint8_t *q = b + 2 + (e0 & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)(((q[i] >> sh) & 0xF) - 8) * d;
+    }
+};
+
+// upstream dequant.cpp:37-52
+template <>
+struct Decoder<GGML_TYPE_Q4_1> {
+    static constexpr int ELEMS = 32, BYTES = 20;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const float m = half_bits_to_f32(ld16(b + 2));
+        const int sh = e0 >= 16 ? 4 : 0;
+        const uint8_t *q = b + 4 + (e0 & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)((q[i] >> sh) & 0xF) * d + m;
+    }
+};
+
+// upstream dequant.cpp:54-76
+template <>
+struct Decoder<GGML_TYPE_Q5_0> {
+    static constexpr int ELEMS = 32, BYTES = 22;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const uint32_t qh = ld32(b + 2);
+        const int sh = e0 >= 16 ? 4 : 0;
+        const uint8_t *q = b + 6 + (e0 & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int hi = (int)((qh >> (e0 + i)) & 1) << 4;
+            v[i] = (float)((((q[i] >> sh) & 0xF) | hi) - 16) * d;
+        }
+    }
+};
+
+// upstream dequant.cpp:78-101
+template <>
+struct Decoder<GGML_TYPE_Q5_1> {
+    static constexpr int ELEMS = 32, BYTES = 24;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const float m = half_bits_to_f32(ld16(b + 2));
+        const uint32_t qh = ld32(b + 4);
+        const int sh = e0 >= 16 ? 4 : 0;
+        const uint8_t *q = b + 8 + (e0 & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int hi = (int)((qh >> (e0 + i)) & 1) << 4;
+            v[i] = (float)(((q[i] >> sh) & 0xF) | hi) * d + m;
+        }
+    }
+};
+
+// upstream dequant.cpp:6-19
+template <>
+struct Decoder<GGML_TYPE_Q1_0> {
+    static constexpr int ELEMS = 128, BYTES = 18;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const float neg_d = -d;
+        const uint32_t bits = b[2 + (e0 >> 3)];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = ((bits >> i) & 1) ? d : neg_d;
+    }
+};
+
+// upstream dequant.cpp:136-154
+template <>
+struct Decoder<GGML_TYPE_MXFP4> {
+    static constexpr int ELEMS = 32, BYTES = 17;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = e8m0_half_to_f32(b[0]);
+        const int sh = e0 >= 16 ? 4 : 0;
+        const uint8_t *q = b + 1 + (e0 & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)k_fp4_values[(q[i] >> sh) & 0xF] * d;
+    }
+};
+
+// upstream dequant.cpp:156-179
+template <>
+struct Decoder<GGML_TYPE_NVFP4> {
+    static constexpr int ELEMS = 64, BYTES = 36;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const int s = e0 >> 4;
+        const float d = ue4m3_half_to_f32(b[s]);
+        const int sh = (e0 & 8) ? 4 : 0;
+        const uint8_t *q = b + 4 + s * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)k_fp4_values[(q[i] >> sh) & 0xF] * d;
+    }
+};
+
+// upstream dequant.cpp:181-211.  Element e: half n = e/128, 2-bit plane j = (e%128)/32,
+// 16-wide group (e%32)/16; scale byte index 8n + 2j + group.
+template <>
+struct Decoder<GGML_TYPE_Q2_K> {
+    static constexpr int ELEMS = 256, BYTES = 84;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b + 80));
+        const float dmin = half_bits_to_f32(ld16(b + 82));
+        const int n = e0 >> 7, j = (e0 >> 5) & 3, r = e0 & 31;
+        const int sc = b[8 * n + 2 * j + (r >> 4)];
+        const float dl = d * (float)(sc & 0xF);
+        const float ml = dmin * (float)(sc >> 4);
+        const uint8_t *q = b + 16 + 32 * n + r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = dl * (float)((q[i] >> (2 * j)) & 3) - ml;
+    }
+};
+
+// upstream dequant.cpp:213-261
+template <>
+struct Decoder<GGML_TYPE_Q3_K> {
+    static constexpr int ELEMS = 256, BYTES = 110;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d_all = half_bits_to_f32(ld16(b + 108));
+        const int n = e0 >> 7, j = (e0 >> 5) & 3, r = e0 & 31;
+        const int is = 8 * n + 2 * j + (r >> 4);
+        // 6-bit scale `is`: low nibble from scales[is%8] (high nibble for is>=8), top 2 bits from scales[8 + is%4].
+        const uint8_t *s = b + 96;
+        const int lo = is < 8 ? (s[is] & 0xF) : (s[is - 8] >> 4);
+        const int hi = (s[8 + (is & 3)] >> (2 * (is >> 2))) & 3;
+        const float dl = d_all * (float)((int)(int8_t)(lo | (hi << 4)) - 32);
+        const uint8_t *q = b + 32 + 32 * n + r;
+        const uint8_t *hm = b + r;
+        const int mbit = 1 << (4 * n + j);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int ql = (q[i] >> (2 * j)) & 3;
+            v[i] = dl * (float)(ql - ((hm[i] & mbit) ? 0 : 4));
+        }
+    }
+};
+
+// upstream dequant.cpp:263-285
+template <>
+struct Decoder<GGML_TYPE_Q4_K> {
+    static constexpr int ELEMS = 256, BYTES = 144;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const float dmin = half_bits_to_f32(ld16(b + 2));
+        const int j64 = e0 >> 6, hi = (e0 >> 5) & 1, l0 = e0 & 31;
+        int sc, m;
+        scale_min_k4(2 * j64 + hi, b + 4, sc, m);
+        const float d1 = d * (float)sc;
+        const float m1 = dmin * (float)m;
+        const uint8_t *q = b + 16 + 32 * j64 + l0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = d1 * (float)((q[i] >> (4 * hi)) & 0xF) - m1;
+    }
+};
+
+// upstream dequant.cpp:287-312
+template <>
+struct Decoder<GGML_TYPE_Q5_K> {
+    static constexpr int ELEMS = 256, BYTES = 176;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const float dmin = half_bits_to_f32(ld16(b + 2));
+        const int j64 = e0 >> 6, hi = (e0 >> 5) & 1, l0 = e0 & 31;
+        int sc, m;
+        scale_min_k4(2 * j64 + hi, b + 4, sc, m);
+        const float d1 = d * (float)sc;
+        const float m1 = dmin * (float)m;
+        const uint8_t *qh = b + 16 + l0;
+        const uint8_t *q = b + 48 + 32 * j64 + l0;
+        const int hbit = 1 << (2 * j64 + hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = d1 * (float)(((q[i] >> (4 * hi)) & 0xF) + ((qh[i] & hbit) ? 16 : 0)) - m1;
+    }
+};
+
+// upstream dequant.cpp:314-343
+template <>
+struct Decoder<GGML_TYPE_Q6_K> {
+    static constexpr int ELEMS = 256, BYTES = 210;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b + 208));
+        const int n = e0 >> 7, quarter = (e0 >> 5) & 3, l0 = e0 & 31;
+        const int sc = (int8_t)b[192 + 8 * n + (l0 >> 4) + 2 * quarter];
+        const float ds = d * (float)sc;
+        const uint8_t *ql = b + 64 * n + 32 * (quarter & 1) + l0;
+        const uint8_t *qh = b + 128 + 32 * n + l0;
+        const int lsh = (quarter & 2) ? 4 : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int q = (int)(int8_t)(((ql[i] >> lsh) & 0xF) | (((qh[i] >> (2 * quarter)) & 3) << 4)) - 32;
+            v[i] = ds * (float)q;
+        }
+    }
+};
+
+// upstream dequant.cpp:345-383.  Layout: 32 bytes x 5 trits, 16 bytes x 5 trits, 4 bytes x 4 trits.
+template <>
+struct Decoder<GGML_TYPE_TQ1_0> {
+    static constexpr int ELEMS = 256, BYTES = 54;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b + 52));
+        const int pow3[5] = {1, 3, 9, 27, 81};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = e0 + i;
+            int byte, n;
+            if (e < 160) {
+                n = e >> 5;
+                byte = b[e & 31];
+            } else if (e < 240) {
+                n = (e - 160) >> 4;
+                byte = b[32 + ((e - 160) & 15)];
+            } else {
+                n = (e - 240) >> 2;
+                byte = b[48 + ((e - 240) & 3)];
+            }
+            const int q = (byte * pow3[n]) & 0xFF;
+            const int xi = (q * 3) >> 8;
+            v[i] = (float)(xi - 1) * d;
+        }
+    }
+};
+
+// upstream dequant.cpp:385-401
+template <>
+struct Decoder<GGML_TYPE_TQ2_0> {
+    static constexpr int ELEMS = 256, BYTES = 66;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b + 64));
+        const int j = e0 >> 7, l = (e0 >> 5) & 3, m0 = e0 & 31;
+        const uint8_t *q = b + 32 * j + m0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = (float)(((q[i] >> (2 * l)) & 3) - 1) * d;
+    }
+};
+
+// Eight values of one IQ2 grid point with its sign byte applied.
+GGUF_D void iq2_emit(uint32_t code, uint32_t signs, float db, float *v) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float g = db * (float)iq2_grid_byte((code >> (2 * i)) & 3);
+        v[i] = (signs >> i) & 1 ? -g : g;
+    }
+}
+
+// upstream dequant.cpp:403-427
+template <>
+struct Decoder<GGML_TYPE_IQ2_XXS> {
+    static constexpr int ELEMS = 256, BYTES = 66;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int ib32 = e0 >> 5, l = (e0 >> 3) & 3;
+        const uint8_t *q = b + 2 + 8 * ib32;
+        const uint32_t aux1 = ld32(q + 4);
+        const float db = d * (0.5f + (float)(aux1 >> 28)) * 0.25f;
+        iq2_emit(k_codebook_IQ2XXS[q[l]], iq_signs_from_index((aux1 >> (7 * l)) & 127), db, v);
+    }
+};
+
+// upstream dequant.cpp:429-452
+template <>
+struct Decoder<GGML_TYPE_IQ2_XS> {
+    static constexpr int ELEMS = 256, BYTES = 74;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int g = e0 >> 3, ib32 = g >> 2, l = g & 3;
+        const uint32_t q = ld16(b + 2 + 2 * g);
+        const int sc = b[66 + ib32];
+        const float db = d * (0.5f + (float)((l < 2) ? (sc & 0xF) : (sc >> 4))) * 0.25f;
+        iq2_emit(k_codebook_IQ2XS[q & 511], iq_signs_from_index(q >> 9), db, v);
+    }
+};
+
+// upstream dequant.cpp:454-482
+template <>
+struct Decoder<GGML_TYPE_IQ2_S> {
+    static constexpr int ELEMS = 256, BYTES = 82;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int g = e0 >> 3, ib32 = g >> 2, l = g & 3;
+        const int sc = b[74 + ib32];
+        const float db = d * (0.5f + (float)((l < 2) ? (sc & 0xF) : (sc >> 4))) * 0.25f;
+        const uint32_t idx = b[2 + g] | (((uint32_t)b[66 + ib32] << (8 - 2 * l)) & 0x300);
+        iq2_emit(k_codebook_IQ2S[idx], b[2 + 32 + g], db, v);
+    }
+};
+
+// upstream dequant.cpp:484-512
+template <>
+struct Decoder<GGML_TYPE_IQ3_XXS> {
+    static constexpr int ELEMS = 256, BYTES = 98;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int g = e0 >> 3, ib32 = g >> 2, l = g & 3;
+        const uint32_t aux = ld32(b + 2 + 64 + 4 * ib32);
+        const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+        const uint32_t signs = iq_signs_from_index((aux >> (7 * l)) & 127);
+        const uint32_t c1 = k_codebook_IQ3XXS[b[2 + 2 * g]];
+        const uint32_t c2 = k_codebook_IQ3XXS[b[2 + 2 * g + 1]];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float g1 = db * (float)iq3xxs_grid_byte((c1 >> (3 * i)) & 7);
+            const float g2 = db * (float)iq3xxs_grid_byte((c2 >> (3 * i)) & 7);
+            v[i] = (signs >> i) & 1 ? -g1 : g1;
+            v[i + 4] = (signs >> (i + 4)) & 1 ? -g2 : g2;
+        }
+    }
+};
+
+// upstream dequant.cpp:630-669
+template <>
+struct Decoder<GGML_TYPE_IQ3_S> {
+    static constexpr int ELEMS = 256, BYTES = 110;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int g = e0 >> 3, ib32 = g >> 2, l = g & 3;
+        const int sc = b[106 + (ib32 >> 1)];
+        const float db = d * (float)(1 + 2 * ((ib32 & 1) ? (sc >> 4) : (sc & 0xF)));
+        const uint32_t qh = b[66 + ib32];
+        const uint32_t i1 = b[2 + 2 * g] | ((qh << (8 - 2 * l)) & 256);
+        const uint32_t i2 = b[2 + 2 * g + 1] | ((qh << (7 - 2 * l)) & 256);
+        const uint32_t signs = b[74 + g];
+        const uint32_t c1 = k_codebook_IQ3S[i1];
+        const uint32_t c2 = k_codebook_IQ3S[i2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float g1 = db * (float)iq3s_grid_byte((c1 >> (3 * i)) & 7);
+            const float g2 = db * (float)iq3s_grid_byte((c2 >> (3 * i)) & 7);
+            v[i] = (signs >> i) & 1 ? -g1 : g1;
+            v[i + 4] = (signs >> (i + 4)) & 1 ? -g2 : g2;
+        }
+    }
+};
+
+// upstream dequant.cpp:514-538
+template <>
+struct Decoder<GGML_TYPE_IQ1_S> {
+    static constexpr int ELEMS = 256, BYTES = 50;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int g = e0 >> 3, ib = g >> 2, l = g & 3;
+        const uint32_t qh = ld16(b + 34 + 2 * ib);
+        const float dl = d * (float)(2 * ((qh >> 12) & 7) + 1);
+        const float delta = (qh & 0x8000) ? -0.125f : 0.125f;
+        const uint32_t code = k_codebook_IQ1S[b[2 + g] | (((qh >> (3 * l)) & 7) << 8)];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = dl * ((float)iq1_grid_value((code >> (2 * i)) & 3) + delta);
+    }
+};
+
+// upstream dequant.cpp:540-587
+template <>
+struct Decoder<GGML_TYPE_IQ1_M> {
+    static constexpr int ELEMS = 256, BYTES = 56;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const uint32_t s0 = ld16(b + 48), s1 = ld16(b + 50), s2 = ld16(b + 52), s3 = ld16(b + 54);
+        const uint16_t dbits = (uint16_t)((s0 >> 12) | ((s1 >> 8) & 0x00f0) | ((s2 >> 4) & 0x0f00) | (s3 & 0xf000));
+        const float d = half_bits_to_f32(dbits);
+        const int g = e0 >> 3, ib = g >> 2, l = g & 3;
+        const uint32_t sc = ld16(b + 48 + 2 * (ib >> 1));
+        const float dl = d * (float)(2 * ((sc >> (6 * (ib & 1) + (l >= 2 ? 3 : 0))) & 7) + 1);
+        const uint32_t qh = b[32 + 2 * ib + (l >> 1)];
+        const uint32_t idx = b[g] | ((qh << ((l & 1) ? 4 : 8)) & 0x700);
+        const float delta = (qh & ((l & 1) ? 0x80 : 0x08)) ? -0.125f : 0.125f;
+        const uint32_t code = k_codebook_IQ1S[idx];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = dl * ((float)iq1_grid_value((code >> (2 * i)) & 3) + delta);
+    }
+};
+
+// upstream dequant.cpp:589-603
+template <>
+struct Decoder<GGML_TYPE_IQ4_NL> {
+    static constexpr int ELEMS = 32, BYTES = 18;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int sh = e0 >= 16 ? 4 : 0;
+        const uint8_t *q = b + 2 + (e0 & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = d * (float)k_iq4nl_values[(q[i] >> sh) & 0xF];
+    }
+};
+
+// upstream dequant.cpp:605-628
+template <>
+struct Decoder<GGML_TYPE_IQ4_XS> {
+    static constexpr int ELEMS = 256, BYTES = 136;
+    static GGUF_D void run(const uint8_t *b, int e0, float *v) {
+        const float d = half_bits_to_f32(ld16(b));
+        const int ib = e0 >> 5, r = e0 & 31;
+        const uint32_t scales_h = ld16(b + 2);
+        const int ls = ((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((scales_h >> (2 * ib)) & 3) << 4);
+        const float dl = d * (float)(ls - 32);
+        const int sh = r >= 16 ? 4 : 0;
+        const uint8_t *q = b + 8 + 16 * ib + (r & 15);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = dl * (float)k_iq4nl_values[(q[i] >> sh) & 0xF];
+    }
+};
+
+// bf16 storage "decoder": widen by shifting into the high half (upstream libgguf_common.h:262-271).
+template <>
+struct Decoder<GGML_TYPE_BF16> {
+    static constexpr int ELEMS = 8, BYTES = 16;
+    static GGUF_D void run(const uint8_t *b, int, float *v) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = bits_to_f32((uint32_t)ld16(b + 2 * i) << 16);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+template <class OutT>
+struct OutPack;
+
+template <>
+struct OutPack<float> {
+    static GGUF_D void store8(float *dst, const float *v, bool aligned) {
+        if (aligned) {
+            __stcs(reinterpret_cast<float4 *>(dst), make_float4(v[0], v[1], v[2], v[3]));
+            __stcs(reinterpret_cast<float4 *>(dst) + 1, make_float4(v[4], v[5], v[6], v[7]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = v[i];
+        }
+    }
+    static GGUF_D void store1(float *dst, float v) { *dst = v; }
+};
+
+template <>
+struct OutPack<__half> {
+    static GGUF_D void store8(__half *dst, const float *v, bool aligned) {
+        if (aligned) {
+            uint4 u;
+            __half2 h;
+            h = __floats2half2_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t *>(&h);
+            h = __floats2half2_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t *>(&h);
+            h = __floats2half2_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t *>(&h);
+            h = __floats2half2_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t *>(&h);
+            __stcs(reinterpret_cast<uint4 *>(dst), u);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = __float2half_rn(v[i]);
+        }
+    }
+};
+
+template <>
+struct OutPack<__nv_bfloat16> {
+    static GGUF_D void store8(__nv_bfloat16 *dst, const float *v, bool aligned) {
+        if (aligned) {
+            uint4 u;
+            __nv_bfloat162 h;
+            h = __floats2bfloat162_rn(v[0], v[1]); u.x = *reinterpret_cast<uint32_t *>(&h);
+            h = __floats2bfloat162_rn(v[2], v[3]); u.y = *reinterpret_cast<uint32_t *>(&h);
+            h = __floats2bfloat162_rn(v[4], v[5]); u.z = *reinterpret_cast<uint32_t *>(&h);
+            h = __floats2bfloat162_rn(v[6], v[7]); u.w = *reinterpret_cast<uint32_t *>(&h);
+            __stcs(reinterpret_cast<uint4 *>(dst), u);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+        }
+    }
+};
+
+constexpr int kThreads = 256;
+constexpr int kRunsPerThread = 4;                       // runs of 8 elements each thread decodes
+constexpr int kTileElems = kThreads * 8 * kRunsPerThread;  // 8192 elements per CTA
+
+template <int TYPE, class OutT>
+__global__ void __launch_bounds__(kThreads) dequant_tile_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
+                                                               int64_t nblocks, int dst_aligned) {
+    using D = Decoder<TYPE>;
+    constexpr int TILE_BLOCKS = kTileElems / D::ELEMS;
+    constexpr int TILE_BYTES = TILE_BLOCKS * D::BYTES;
+    __shared__ __align__(16) uint8_t tile[TILE_BYTES + 32];
+
+    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
+    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
+    const uint8_t *gsrc = src + b0 * D::BYTES;
+    const int nbytes = nb * D::BYTES;
+    // Stage the 16-byte aligned span [gsrc - mis, gsrc + nbytes) rounded up to 16.  The extra
+    // bytes share a 16-byte granule with bytes of the tile, so they are in the same page.
+    const int mis = (int)(reinterpret_cast<uintptr_t>(gsrc) & 15);
+    const uint4 *g16 = reinterpret_cast<const uint4 *>(gsrc - mis);
+    const int nvec = (mis + nbytes + 15) >> 4;
+    uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+    for (int i = threadIdx.x; i < nvec; i += kThreads) s16[i] = __ldcs(g16 + i);
+    __syncthreads();
+
+    const uint8_t *blocks = tile + mis;
+    OutT *out = dst + b0 * D::ELEMS;
+    const int nruns = nb * (D::ELEMS / 8);
+#pragma unroll
+    for (int u = 0; u < kRunsPerThread; ++u) {
+        const int run = u * kThreads + threadIdx.x;
+        if (run < nruns) {
+            const int e = run * 8;
+            const int blk = e / D::ELEMS;
+            float v[8];
+            D::run(blocks + blk * D::BYTES, e - blk * D::ELEMS, v);
+            OutPack<OutT>::store8(out + e, v, dst_aligned != 0);
+        }
+    }
+}
+
+template <int TYPE, class OutT>
+cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_t stream) {
+    using D = Decoder<TYPE>;
+    const int64_t nblocks = nelems / D::ELEMS;
+    constexpr int TILE_BLOCKS = kTileElems / D::ELEMS;
+    const int64_t grid = (nblocks + TILE_BLOCKS - 1) / TILE_BLOCKS;
+    if (grid <= 0) return cudaSuccess;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const int aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    dequant_tile_kernel<TYPE, OutT><<<(unsigned)grid, kThreads, 0, stream>>>(static_cast<const uint8_t *>(src),
+                                                                           static_cast<OutT *>(dst), nblocks, aligned);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// bf16 rows whose length is not a multiple of 8: scalar tail handled by a tiny kernel.
+template <class OutT>
+__global__ void bf16_tail_kernel(const uint16_t *src, OutT *dst, int64_t begin, int64_t n) {
+    const int64_t i = begin + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float f = bits_to_f32((uint32_t)src[i] << 16);
+        if constexpr (sizeof(OutT) == 4) dst[i] = f;
+        else if constexpr (std::is_same<OutT, __half>::value) dst[i] = __float2half_rn(f);
+        else dst[i] = __float2bfloat16_rn(f);
+    }
+}
+
+template <class OutT>
+cudaError_t launch_for_out(int type, const void *src, void *dst, int64_t nelems, cudaStream_t stream) {
+    switch (type) {
+#define GGUF_CASE(T) case T: return launch_typed<T, OutT>(src, dst, nelems, stream);
+        GGUF_CASE(GGML_TYPE_Q4_0) GGUF_CASE(GGML_TYPE_Q4_1) GGUF_CASE(GGML_TYPE_Q5_0) GGUF_CASE(GGML_TYPE_Q5_1)
+        GGUF_CASE(GGML_TYPE_Q8_0) GGUF_CASE(GGML_TYPE_Q1_0) GGUF_CASE(GGML_TYPE_MXFP4) GGUF_CASE(GGML_TYPE_NVFP4)
+        GGUF_CASE(GGML_TYPE_Q2_K) GGUF_CASE(GGML_TYPE_Q3_K) GGUF_CASE(GGML_TYPE_Q4_K) GGUF_CASE(GGML_TYPE_Q5_K)
+        GGUF_CASE(GGML_TYPE_Q6_K) GGUF_CASE(GGML_TYPE_TQ1_0) GGUF_CASE(GGML_TYPE_TQ2_0) GGUF_CASE(GGML_TYPE_IQ2_XXS)
+        GGUF_CASE(GGML_TYPE_IQ2_XS) GGUF_CASE(GGML_TYPE_IQ2_S) GGUF_CASE(GGML_TYPE_IQ3_XXS) GGUF_CASE(GGML_TYPE_IQ3_S)
+        GGUF_CASE(GGML_TYPE_IQ1_S) GGUF_CASE(GGML_TYPE_IQ1_M) GGUF_CASE(GGML_TYPE_IQ4_NL) GGUF_CASE(GGML_TYPE_IQ4_XS)
+#undef GGUF_CASE
+        case GGML_TYPE_BF16: {
+            const int64_t main_elems = nelems & ~(int64_t)7;
+            cudaError_t err = launch_typed<GGML_TYPE_BF16, OutT>(src, dst, main_elems, stream);
+            if (err != cudaSuccess) return err;
+            if (main_elems < nelems) {
+                bf16_tail_kernel<OutT><<<1, 8, 0, stream>>>(static_cast<const uint16_t *>(src), static_cast<OutT *>(dst),
+                                                           main_elems, nelems);
+                count_launch();
+                err = cudaGetLastError();
+            }
+            return err;
+        }
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_dequantize(int type, const void *src, void *dst, int64_t nelems, int out_dtype, cudaStream_t stream) {
+    switch (out_dtype) {
+        case 0: return launch_for_out<float>(type, src, dst, nelems, stream);
+        case 1: return launch_for_out<__half>(type, src, dst, nelems, stream);
+        case 2: return launch_for_out<__nv_bfloat16>(type, src, dst, nelems, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace gguf

@@ -1,0 +1,128 @@
+// Host-built tables and their per-device copies.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <mutex>
+#include <utility>
+#include <vector>
+
+#include "device_state.h"
+#include "gguf_common.cuh"
+#include "gguf_tables.cuh"
+#include "iq_tables_host.h"
+
+namespace gguf {
+namespace {
+
+struct Slot {
+    std::mutex lock;
+    DeviceState state;
+    std::vector<void *> allocations;
+};
+Slot g_slots[kMaxDevices];
+
+// floorf(log2f(x)) as computed by this machine's libm, per binade.  For t = -149..127 the entry is
+// the smallest float x in [2^t, 2^(t+1)) with floorf(log2f(x)) == t+1, or +inf when every x of the
+// binade gives t.  upstream mxfp4.cpp:39 takes the exponent from that libm expression, and a
+// correctly rounded log2f of a value just below a power of two can round up to the integer.
+// log2f is assumed monotonic (glibc's is), so a bisection over the mantissa finds the step.
+std::vector<float> build_mx_steps() {
+    std::vector<float> steps(277);
+    for (int t = -149; t <= 127; ++t) {
+        const float lo = ldexpf(1.0f, t);
+        // largest float of the binade
+        const float hi = t >= -126 ? nextafterf(ldexpf(1.0f, t + 1), 0.0f) : nextafterf(ldexpf(1.0f, t + 1), 0.0f);
+        float result = INFINITY;
+        if (floorf(log2f(hi)) >= (float)(t + 1)) {
+            uint32_t a = f32_to_bits(lo), b = f32_to_bits(hi);  // positive floats order like their bits
+            if (floorf(log2f(lo)) >= (float)(t + 1)) {
+                b = a;
+            } else {
+                while (b - a > 1) {
+                    const uint32_t mid = a + (b - a) / 2;
+                    if (floorf(log2f(bits_to_f32(mid))) >= (float)(t + 1)) b = mid; else a = mid;
+                }
+            }
+            result = bits_to_f32(b);
+        }
+        steps[t + 149] = result;
+    }
+    return steps;
+}
+
+const std::vector<float> &mx_steps_host() {
+    static const std::vector<float> steps = build_mx_steps();
+    return steps;
+}
+
+template <class T>
+const T *upload(Slot &slot, const std::vector<T> &host) {
+    void *p = nullptr;
+    const size_t bytes = host.size() * sizeof(T);
+    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (bytes && cudaMemcpy(p, host.data(), bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return nullptr;
+    }
+    slot.allocations.push_back(p);
+    return static_cast<const T *>(p);
+}
+
+int table_for_type(int type) {
+    switch (type) {
+        case GGML_TYPE_IQ2_XXS: return IQT_2XXS;
+        case GGML_TYPE_IQ2_XS: return IQT_2XS;
+        case GGML_TYPE_IQ1_S: case GGML_TYPE_IQ1_M: return IQT_1S;
+        case GGML_TYPE_IQ2_S: return IQT_2S;
+        case GGML_TYPE_IQ3_XXS: return IQT_3XXS;
+        case GGML_TYPE_IQ3_S: return IQT_3S;
+        default: return -1;
+    }
+}
+
+}  // namespace
+
+const DeviceState *device_state_for(int type, int dev) {
+    if (dev < 0 || dev >= kMaxDevices) return nullptr;
+    Slot &slot = g_slots[dev];
+    std::lock_guard<std::mutex> guard(slot.lock);
+    slot.state.device = dev;
+    if (type == GGML_TYPE_MXFP4 && !slot.state.mx_steps) {
+        slot.state.mx_steps = upload(slot, mx_steps_host());
+        if (!slot.state.mx_steps) return nullptr;
+    }
+    const int id = table_for_type(type);
+    if (id >= 0 && !slot.state.iq[id].grid) {
+        const IqHostTable &h = iq_host_table(id);
+        IqSearchTable t;
+        t.grid = upload(slot, h.grid);
+        t.map = upload(slot, h.map);
+        t.neighbours = upload(slot, h.neighbours);
+        if (!t.grid || !t.map || !t.neighbours) return nullptr;
+        t.grid_size = h.grid_size;
+        t.dims = h.dims;
+        t.map_size = (int)h.map.size();
+        t.neighbours_len = (int)h.neighbours.size();
+        slot.state.iq[id] = t;
+    }
+    return &slot.state;
+}
+
+void device_state_release_all() {
+    for (int dev = 0; dev < kMaxDevices; ++dev) {
+        Slot &slot = g_slots[dev];
+        std::lock_guard<std::mutex> guard(slot.lock);
+        if (slot.allocations.empty()) continue;
+        if (cudaSetDevice(dev) == cudaSuccess) {
+            for (void *p : slot.allocations) cudaFree(p);
+        }
+        cudaGetLastError();
+        slot.allocations.clear();
+        slot.state = DeviceState();
+    }
+}
+
+}  // namespace gguf

@@ -1,0 +1,44 @@
+// Per-device read-only tables the quantizers need: the MXFP4 exponent steps measured from the
+// host libm, and the IQ search tables (grid, lattice-point map, neighbour lists).  Built on the
+// host once per process, uploaded once per device on first use, released by
+// libgguf_quantize_free().
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gguf {
+
+constexpr int kMaxDevices = 64;
+
+// One IQ codebook prepared for searching (device pointers).
+struct IqSearchTable {
+    const uint8_t *grid = nullptr;         // grid_size x dims bytes, coordinate value 2*code+1
+    const int32_t *map = nullptr;          // lattice index -> grid index (>= 0) or -(offset+1) into neighbours
+    const uint16_t *neighbours = nullptr;  // [count, idx0, idx1, ...] runs
+    int grid_size = 0;
+    int dims = 0;
+    int map_size = 0;
+    int neighbours_len = 0;
+};
+
+enum IqTableId { IQT_2XXS = 0, IQT_2XS, IQT_1S, IQT_2S, IQT_3XXS, IQT_3S, IQT_COUNT };
+
+struct DeviceState {
+    int device = -1;
+    const float *mx_steps = nullptr;  // 277 floats, see quant_simple.cu
+    IqSearchTable iq[IQT_COUNT];
+};
+
+// Returns the state of device `dev` with everything quantizing `type` needs present, building
+// and uploading on first use (blocking).  The caller must have made `dev` current.  nullptr on
+// allocation or copy failure.
+const DeviceState *device_state_for(int type, int dev);
+
+void device_state_release_all();
+
+cudaError_t launch_store(int type, const float *src, void *dst, int64_t nelems, cudaStream_t stream);
+cudaError_t launch_quantize(int type, const float *src, const float *imatrix, void *dst, int64_t nrows,
+                            int64_t n_per_row, const DeviceState *state, cudaStream_t stream);
+
+}  // namespace gguf
