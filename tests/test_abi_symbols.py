@@ -1,0 +1,47 @@
+"""The C-ABI shared library loads and exports every function the public headers declare
+(no compute calls, so no GPU needed)."""
+import ctypes
+import re
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_functions(header: Path) -> list[str]:
+    text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+    text = re.sub(r"//.*", "", text)
+    return re.findall(r"\b(libgguf_[a-z0-9_]+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    from libgguf_b200 import _native
+    lib = ctypes.CDLL(str(_native.LIB_PATH))
+    names = []
+    for header in sorted((ROOT / "include").glob("*.h")):
+        names += declared_functions(header)
+    assert len(set(names)) >= 7 + 30
+    missing = [n for n in sorted(set(names)) if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_binding_table_covers_the_headers():
+    from libgguf_b200 import _native
+    bound = set(_native.HOST_ABI) | set(_native.NATIVE_ABI)
+    declared = set()
+    for header in sorted((ROOT / "include").glob("*.h")):
+        declared |= set(declared_functions(header))
+    assert declared == bound
+
+
+def test_type_queries_need_no_device():
+    from libgguf_b200._native import lib
+    assert lib.libgguf_cuda_qtype_supported(12) == 1
+    assert lib.libgguf_cuda_qtype_supported(0) == 0
+    assert lib.libgguf_cuda_qtype_needs_imatrix(16) == 1
+    assert lib.libgguf_cuda_block_size(12) == 256
+    assert lib.libgguf_cuda_row_size(12, 4096) == 2304
+    assert lib.libgguf_cuda_dequantize_qtype_supported(30) == 1
+    assert lib.libgguf_cuda_dequantize_block_size(30) == 1
+    assert lib.libgguf_cuda_dequantize_row_size(30, 10) == 20
+    assert lib.libgguf_cuda_dequantize_row_size(14, 256) == 210
+    assert lib.libgguf_cuda_last_error(None) == b"libgguf CUDA context is null"

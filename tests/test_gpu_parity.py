@@ -1,0 +1,166 @@
+"""Parity of the CUDA path with the checkers, through the C ABI.
+
+Encoded bytes must be identical; fp32 decodes must have identical bit patterns; fp16/bf16
+decodes must equal the round-to-nearest-even conversion of the fp32 decode (bit patterns)."""
+import hashlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import inputs
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = Path(__file__).parent / "golden"
+UPSTREAM = json.loads((GOLDEN / "upstream_manifest.json").read_text())["entries"]
+FIXTURES = json.loads((GOLDEN / "golden.json").read_text())["entries"]
+ALL = sorted(inputs.QTYPES)
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.fixture(scope="module")
+def checker():
+    from oracle import reference
+    if reference.available("ref"):
+        return reference.load("ref")
+    import subprocess
+    if not reference.available("port"):
+        subprocess.run(["make", "-C", str(Path(__file__).parents[1] / "oracle"), "oracle"], check=True, capture_output=True)
+    return reference.load("port")
+
+
+def supported_by(checker, qtype):
+    if checker.kind == "port":
+        return checker.lib.gguf_oracle_quantize_supported(int(qtype)) != 0
+    return True
+
+
+def test_upstream_frozen_vectors(gguf):
+    """The 70 SHA-256 vectors upstream freezes for its CPU backend (tests/golden/manifest.json)."""
+    for e in UPSTREAM:
+        rows, width = (int(v) for v in e["shape"].split("x"))
+        x = inputs.pattern_rows(e["pattern"], rows, width)
+        enc = gguf.quantize_rows(x, inputs.QTYPES[e["qtype"]])
+        assert enc.nbytes == e["encoded_nbytes"]
+        assert sha(enc) == e["encoded_sha256"], e
+        dec = gguf.dequantize_rows(enc, inputs.QTYPES[e["qtype"]], width)
+        assert np.all(np.isfinite(dec))
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_golden_fixtures(gguf, name):
+    """Every type x 11 patterns x {no imatrix, imatrix}: encoded bytes and fp32 decode."""
+    n = 0
+    for e in FIXTURES:
+        if e["qtype"] != name:
+            continue
+        qtype = inputs.QTYPES[name]
+        x = inputs.pattern_rows(e["pattern"], e["rows"], e["width"], seed=qtype * 1009 + sum(e["pattern"].encode()))
+        im = inputs.imatrix_for(e["width"], seed=qtype) if e["weighted"] else None
+        enc = gguf.quantize_rows(x, qtype, im)
+        assert sha(enc) == e["encoded_sha256"], e
+        assert sha(gguf.dequantize_rows(enc, qtype, e["width"])) == e["decoded_sha256"], e
+        n += 1
+    assert n == 2 * len(inputs.PATTERNS)
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_random_rows_match_checker(gguf, checker, name):
+    """512 x 4096 standard normal rows, seed 0 (upstream test_cuda_quantize.py:279-311 shape)."""
+    qtype = inputs.QTYPES[name]
+    if not supported_by(checker, qtype):
+        pytest.skip("checker has no quantizer for this type")
+    slow = name.startswith("IQ1") or name.startswith("IQ2") or name.startswith("IQ3")
+    rows = 64 if slow else 512
+    x = np.random.default_rng(0).standard_normal((rows, 4096), dtype=np.float32)
+    want = checker.quantize_rows(x, qtype)
+    got = gguf.quantize_rows(x, qtype)
+    bad_rows = np.flatnonzero((want != got).any(axis=-1))
+    assert bad_rows.size == 0, f"{bad_rows.size} rows differ, first {bad_rows[:5]}"
+    np.testing.assert_array_equal(gguf.dequantize_rows(want, qtype, 4096).view(np.uint32),
+                                  checker.dequantize_rows(want, qtype, 4096).view(np.uint32))
+
+
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K", "IQ4_NL", "IQ4_XS",
+                                  "IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"])
+def test_importance_weighted_rows_match_checker(gguf, checker, name):
+    qtype = inputs.QTYPES[name]
+    if not supported_by(checker, qtype):
+        pytest.skip("checker has no quantizer for this type")
+    x, im = inputs.config4(32, 2048)
+    np.testing.assert_array_equal(gguf.quantize_rows(x, qtype, im), checker.quantize_rows(x, qtype, im))
+
+
+@pytest.mark.parametrize("name", ALL)
+def test_ragged_sizes_and_chunk_offsets(gguf, checker, name):
+    """1 block, 1 row, row counts that do not fill a CTA, and start offsets into a larger matrix."""
+    from libgguf_b200._native import lib
+    qtype = inputs.QTYPES[name]
+    if not supported_by(checker, qtype):
+        pytest.skip("checker has no quantizer for this type")
+    block = inputs.block_size(name)
+    rng = np.random.default_rng(5)
+    for rows, width in ((1, block), (3, block * 3), (7, block * 5), (33, block)):
+        x = rng.standard_normal((rows, width), dtype=np.float32)
+        np.testing.assert_array_equal(gguf.quantize_rows(x, qtype), checker.quantize_rows(x, qtype))
+    # chunked call: rows 5..11 of a 16-row matrix land at their own offset, the rest untouched
+    width = block * 4
+    x = rng.standard_normal((16, width), dtype=np.float32)
+    want = checker.quantize_rows(x, qtype)
+    im = None
+    if checker.requires_imatrix(qtype):
+        im = np.sum(x * x, axis=0, dtype=np.float32)
+    out = np.full_like(want, 0xAB)
+    rs = want.shape[-1]
+    n = lib.libgguf_quantize_chunk(qtype, x.ctypes.data, out.ctypes.data, 5 * width, 6, width,
+                                   None if im is None else im.ctypes.data)
+    assert n == 6 * rs
+    np.testing.assert_array_equal(out[5:11], want[5:11])
+    assert (out[:5] == 0xAB).all() and (out[11:] == 0xAB).all()
+    dec = np.full((16, width), np.float32(-7), np.float32)
+    n = lib.libgguf_dequantize_chunk(qtype, want.ctypes.data, dec.ctypes.data, 5 * width, 6, width)
+    assert n == 6 * width * 4
+    np.testing.assert_array_equal(dec[5:11].view(np.uint32), checker.dequantize_rows(want[5:11], qtype, width).view(np.uint32))
+    assert (dec[:5] == -7).all() and (dec[11:] == -7).all()
+
+
+def test_config1_q4k_roundtrip_properties(gguf, checker):
+    """BASELINE config 1 at full size (4096 x 4096, N(0, 0.02), seed 0): bytes against the checker
+    on a 256-row slice; on the whole matrix, chunk independence (any row range encodes to the same
+    bytes as in the full call) and idempotence of decode -> encode -> decode."""
+    x = inputs.config1()
+    enc = gguf.quantize_rows(x, 12)
+    np.testing.assert_array_equal(enc[1000:1256], checker.quantize_rows(x[1000:1256], 12))
+    np.testing.assert_array_equal(enc[17:83], gguf.quantize_rows(x[17:83], 12))
+    dec = gguf.dequantize_rows(enc, 12, 4096)
+    np.testing.assert_array_equal(dec[1000:1256].view(np.uint32),
+                                  checker.dequantize_rows(enc[1000:1256], 12, 4096).view(np.uint32))
+    err = np.abs(dec - x).max()
+    assert err < 0.02 * 0.6
+    dec2 = gguf.dequantize_rows(gguf.quantize_rows(dec, 12), 12, 4096)
+    assert np.abs(dec2 - dec).max() <= err
+
+
+def test_storage_types(gguf, checker):
+    x = np.random.default_rng(3).standard_normal((5, 96), dtype=np.float32)
+    x[0, :4] = [np.inf, -np.inf, np.nan, 1e-8]
+    assert np.array_equal(gguf.quantize_rows(x, 0).view(np.uint32), x.view(np.uint32))
+    h = gguf.quantize_rows(x, 1)
+    assert h.dtype == np.float16 and h.shape == x.shape
+    if checker.kind == "ref":
+        np.testing.assert_array_equal(h.view(np.uint16).reshape(5, -1), checker.quantize_rows(x, 1).view(np.uint16))
+        np.testing.assert_array_equal(gguf.quantize_rows(x, 30), checker.quantize_rows(x, 30))
+    else:
+        finite = np.isfinite(x)
+        np.testing.assert_array_equal(h[finite], x.astype(np.float16)[finite])
+
+
+def test_zero_rows_and_empty(gguf):
+    out = gguf.quantize_rows(np.zeros((0, 256), np.float32), 12)
+    assert out.shape == (0, 144)
+    assert gguf.dequantize_rows(np.zeros((0, 144), np.uint8), 12).shape == (0, 256)
