@@ -210,39 +210,44 @@ def main() -> None:
 
     rows = args.rows
     enc = make_encoded_on_gpu(torch, ops, device, rows)
-    outs = {torch.float16: torch.empty((rows, WIDTH), dtype=torch.float16, device=device),
-            torch.bfloat16: torch.empty((rows, WIDTH), dtype=torch.bfloat16, device=device)}
+    # NSETS distinct copies of every input and output so that consecutive launches of one kernel
+    # never touch the same lines: a launch moves 137-180 MB and the L2 holds 126 MB.
+    NSETS = 4
+    enc_sets = {name: [enc[name]] + [enc[name].clone() for _ in range(NSETS - 1)] for name, *_ in SWEEP}
+    out_sets = {dt: [torch.empty((rows, WIDTH), dtype=dt, device=device) for _ in range(NSETS)]
+                for dt in (torch.float16, torch.bfloat16)}
     dtype_code = {torch.float16: 1, torch.bfloat16: 2}
     stream = torch.cuda.current_stream(device)
     algo_bytes = {name: enc[name].numel() + rows * WIDTH * 2 for name, *_ in SWEEP}
     step_bytes = 2 * sum(algo_bytes.values())
 
-    def decode(name, qtype, dt):
-        st = lib.libgguf_cuda_dequantize_rows_on_stream(enc[name].data_ptr(), qtype, rows, WIDTH, dtype_code[dt],
-                                                        outs[dt].data_ptr(), stream.cuda_stream)
+    def decode(name, qtype, dt, k):
+        st = lib.libgguf_cuda_dequantize_rows_on_stream(enc_sets[name][k % NSETS].data_ptr(), qtype, rows, WIDTH, dtype_code[dt],
+                                                        out_sets[dt][k % NSETS].data_ptr(), stream.cuda_stream)
         if st != 0:
             raise RuntimeError(lib.libgguf_cuda_thread_last_error().decode())
 
-    def step(events=None):
-        # dtype outer, qtype inner: an encoded input is re-read only after ~0.8 GB of other traffic
+    def run_steps(nsteps, events=None):
+        """nsteps passes over the sweep.  The launches are issued kernel-major (all nsteps launches of
+        one (qtype, dtype) kernel back to back, each on its own buffer set) so that one event pair
+        brackets every kernel's launches without sitting between two short kernels."""
         for dt in (torch.float16, torch.bfloat16):
             for name, qtype, _, _ in SWEEP:
                 if events is not None:
                     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     a.record(stream)
-                    decode(name, qtype, dt)
+                for k in range(nsteps):
+                    decode(name, qtype, dt, k)
+                if events is not None:
                     b.record(stream)
                     events.append((name, a, b))
-                else:
-                    decode(name, qtype, dt)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
+    run_steps(max(args.warmup, 3))
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -251,8 +256,7 @@ def main() -> None:
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_start.record(stream)
-    for _ in range(args.steps):
-        step(events)
+    run_steps(args.steps, events)
     t_end.record(stream)
     barrier()
     launches = lib.libgguf_cuda_kernel_launch_count() - launches0
@@ -267,7 +271,7 @@ def main() -> None:
     # per-kernel durations inside the timed region
     per = {}
     for name, a, b in events:
-        per.setdefault(name, []).append(a.elapsed_time(b))
+        per.setdefault(name, []).append(a.elapsed_time(b) / args.steps)
     hbm, peak_kind = peaks()
     per_qtype = {}
     for name in per:
@@ -305,7 +309,8 @@ def main() -> None:
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"dequant_sweep Q8_0,Q6_K,Q5_K,Q4_K,Q3_K,Q2_K {rows}x{WIDTH} -> fp16+bf16",
                        "per_gpu_bytes_per_step": step_bytes,
-                       "l2": "no flush: 12 launches/step each move 137-180 MB (> 126 MB L2); an input is re-read only after ~0.8 GB of other traffic"},
+                       "l2": "no flush: every launch moves 137-180 MB (> 126 MB L2) and consecutive launches rotate over 4 distinct input/output buffer sets",
+                       "launch_order": "kernel-major: the K launches of each of the 12 kernels run back to back inside one CUDA-event pair"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "per_qtype": per_qtype,
         }
         if cpu:
@@ -338,7 +343,9 @@ def run_e2e(torch, lib, enc, rows, device_index, world, dist, device, steps):
     for name, t in enc.items():
         hb = ctypes.c_void_p()
         chk(lib.libgguf_cuda_host_buffer_create(ctx, t.numel(), ctypes.byref(hb)))
-        ctypes.memmove(lib.libgguf_cuda_host_buffer_data(hb), t.cpu().numpy().ctypes.data, t.numel())
+        host_copy = t.cpu().numpy()  # keep the array alive while memmove reads it
+        ctypes.memmove(lib.libgguf_cuda_host_buffer_data(hb), host_copy.ctypes.data, host_copy.nbytes)
+        del host_copy
         h_in[name] = hb
     ev = ctypes.c_void_p()
     chk(lib.libgguf_cuda_event_create(ctx, ctypes.byref(ev)))

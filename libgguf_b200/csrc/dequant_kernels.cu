@@ -468,6 +468,217 @@ struct Decoder<GGML_TYPE_BF16> {
 };
 
 // ---------------------------------------------------------------------------------------------
+// Fast decoders for the types the bandwidth targets are quoted on.  Same arithmetic as the
+// generic decoders above, restructured to spend few instructions per element (the generic kernel
+// is limited by instruction issue, not by memory):
+//   * constants shared by a group of 16 or 32 elements (d*scale, dmin*min) are computed once per
+//     group by a first pass over the staged tile and parked in shared memory;
+//   * a thread decodes 16 consecutive elements and writes them with one 256-bit store;
+//   * quants are pulled out of 32-bit words four at a time and turned into floats by dropping
+//     each byte into the mantissa of 2^23 (PRMT) and subtracting 2^23 plus the format's offset,
+//     which is exact and avoids the integer-to-float conversion pipe;
+//   * the subtract / multiply / subtract run as packed two-wide fp32 instructions (add.f32x2,
+//     mul.f32x2 on sm_100), each lane rounded exactly like the scalar instruction.
+// They require the encoded data to start on a 16-byte boundary and the output on a 32-byte
+// boundary; otherwise the generic kernel is used.
+constexpr float kTwo23 = 8388608.f;
+
+// float(byte k of w) + 2^23
+GGUF_D float magic_byte(uint32_t w, int k) { return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (uint32_t)k)); }
+
+// 16 bytes from a shared-memory address of any alignment, via aligned 32-bit loads.
+GGUF_D uint4 lds16_any(const uint8_t *p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    const uint32_t sh = (a & 3u) * 8u;
+    const uint32_t *w = reinterpret_cast<const uint32_t *>(p - (a & 3u));
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
+    return make_uint4(__funnelshift_r(w0, w1, sh), __funnelshift_r(w1, w2, sh), __funnelshift_r(w2, w3, sh),
+                      __funnelshift_r(w3, w4, sh));
+}
+GGUF_D uint4 lds16_a4(const uint8_t *p) { const uint32_t *w = reinterpret_cast<const uint32_t *>(p); return make_uint4(w[0], w[1], w[2], w[3]); }
+GGUF_D uint4 lds16_a16(const uint8_t *p) { return *reinterpret_cast<const uint4 *>(p); }
+GGUF_D uint32_t lds_u16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
+// fp16 bits -> fp32 by the hardware conversion (exact for every finite value and infinity)
+GGUF_D float half_hw(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// Four quants in the bytes of w -> v[0..3] = scale * (byte - offset) [- minus], packed two-wide.
+// neg_bias = -(2^23 + offset).
+template <bool HAS_MIN>
+GGUF_D void affine4(uint32_t w, float neg_bias, float2 c, float *v) {
+    const float2 nb = make_float2(neg_bias, neg_bias), sc = make_float2(c.x, c.x), nm = make_float2(-c.y, -c.y);
+    float2 a = make_float2(magic_byte(w, 0), magic_byte(w, 1));
+    float2 b = make_float2(magic_byte(w, 2), magic_byte(w, 3));
+    a = __fmul2_rn(sc, __fadd2_rn(a, nb));
+    b = __fmul2_rn(sc, __fadd2_rn(b, nb));
+    if (HAS_MIN) { a = __fadd2_rn(a, nm); b = __fadd2_rn(b, nm); }
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <bool HAS_MIN>
+GGUF_D void affine16(uint4 q, float neg_bias, float2 c, float *v) {
+    affine4<HAS_MIN>(q.x, neg_bias, c, v);
+    affine4<HAS_MIN>(q.y, neg_bias, c, v + 4);
+    affine4<HAS_MIN>(q.z, neg_bias, c, v + 8);
+    affine4<HAS_MIN>(q.w, neg_bias, c, v + 12);
+}
+GGUF_D uint4 shr_and(uint4 q, int sh, uint32_t mask) {
+    return make_uint4((q.x >> sh) & mask, (q.y >> sh) & mask, (q.z >> sh) & mask, (q.w >> sh) & mask);
+}
+GGUF_D uint4 or_shl(uint4 q, uint4 h, int sh) { return make_uint4(q.x | (h.x << sh), q.y | (h.y << sh), q.z | (h.z << sh), q.w | (h.w << sh)); }
+
+// scale and min code j of the 12 packed bytes of a Q4_K / Q5_K block, from its three words
+GGUF_D void scale_min_words(int j, uint32_t s0, uint32_t s1, uint32_t s2, int &sc, int &m) {
+    if (j < 4) {
+        sc = (s0 >> (8 * j)) & 63;
+        m = (s1 >> (8 * j)) & 63;
+    } else {
+        const int k = 8 * (j - 4);
+        sc = ((s2 >> k) & 0xF) | (((s0 >> (k + 6)) & 3) << 4);
+        m = ((s2 >> (k + 4)) & 0xF) | (((s1 >> (k + 6)) & 3) << 4);
+    }
+}
+
+template <int TYPE>
+struct Fast { static constexpr bool kEnabled = false; };
+
+// Each Fast<T>: ELEMS/BYTES of a block, GROUP = elements sharing one constant pair,
+// prep(block, group index in block) and run(block, e0 (multiple of 16), constants, v[16]).
+template <>
+struct Fast<GGML_TYPE_Q8_0> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 34, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        uint4 q = lds16_any(b + 2 + e0);
+        q.x ^= 0x80808080u; q.y ^= 0x80808080u; q.z ^= 0x80808080u; q.w ^= 0x80808080u;
+        affine16<false>(q, -(kTwo23 + 128.f), c, v);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_Q4_K> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 144, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int g) {
+        const uint4 head = lds16_a16(b);  // d, dmin, 12 scale bytes
+        int sc, m;
+        scale_min_words(g, head.y, head.z, head.w, sc, m);
+        return make_float2(half_hw(head.x & 0xFFFFu) * (float)sc, half_hw(head.x >> 16) * (float)m);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint4 q = lds16_a16(b + 16 + 32 * (e0 >> 6) + (e0 & 16));
+        affine16<true>(shr_and(q, (e0 & 32) ? 4 : 0, 0x0F0F0F0Fu), -kTwo23, c, v);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_Q5_K> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 176, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int g) { return Fast<GGML_TYPE_Q4_K>::prep(b, g); }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint4 q = lds16_a16(b + 48 + 32 * (e0 >> 6) + (e0 & 16));
+        const uint4 h = lds16_a16(b + 16 + (e0 & 16));
+        const uint4 lo = shr_and(q, (e0 & 32) ? 4 : 0, 0x0F0F0F0Fu);
+        affine16<true>(or_shl(lo, shr_and(h, e0 >> 5, 0x01010101u), 4), -kTwo23, c, v);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_Q6_K> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 210, GROUP = 16;
+    // group g covers elements 16g..16g+15: half n = g/8, quarter = (g/2)%4, is = g%2 -> scale 8n + is + 2*quarter
+    static GGUF_D float2 prep(const uint8_t *b, int g) {
+        const int sc = (int8_t)b[192 + 8 * (g >> 3) + (g & 1) + 2 * ((g >> 1) & 3)];
+        return make_float2(half_hw(lds_u16(b + 208)) * (float)sc, 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int n = e0 >> 7, quarter = (e0 >> 5) & 3, l0 = e0 & 16;
+        const uint4 ql = lds16_any(b + 64 * n + 32 * (quarter & 1) + l0);
+        const uint4 qh = lds16_any(b + 128 + 32 * n + l0);
+        const uint4 lo = shr_and(ql, (quarter & 2) ? 4 : 0, 0x0F0F0F0Fu);
+        affine16<false>(or_shl(lo, shr_and(qh, 2 * quarter, 0x03030303u), 4), -(kTwo23 + 32.f), c, v);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_Q3_K> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 110, GROUP = 16;
+    // group g = scale index of the upstream loop (8n + 2j + half)
+    static GGUF_D float2 prep(const uint8_t *b, int g) {
+        const uint8_t *s = b + 96;
+        const int lo = g < 8 ? (s[g] & 0xF) : (s[g - 8] >> 4);
+        const int hi = (s[8 + (g & 3)] >> (2 * (g >> 2))) & 3;
+        return make_float2(half_hw(lds_u16(b + 108)) * (float)((lo | (hi << 4)) - 32), 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int n = e0 >> 7, j = (e0 >> 5) & 3, r = e0 & 16;
+        const uint4 q = lds16_any(b + 32 + 32 * n + r);
+        const uint4 hm = lds16_any(b + r);
+        // level = low2 + 4*highbit - 4
+        affine16<false>(or_shl(shr_and(q, 2 * j, 0x03030303u), shr_and(hm, 4 * n + j, 0x01010101u), 2), -(kTwo23 + 4.f), c, v);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_Q2_K> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 84, GROUP = 16;
+    static GGUF_D float2 prep(const uint8_t *b, int g) {
+        const uint32_t dm = *reinterpret_cast<const uint32_t *>(b + 80);
+        const int sc = b[g];
+        return make_float2(half_hw(dm & 0xFFFFu) * (float)(sc & 0xF), half_hw(dm >> 16) * (float)(sc >> 4));
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint4 q = lds16_a4(b + 16 + 32 * (e0 >> 7) + (e0 & 16));
+        affine16<true>(shr_and(q, 2 * ((e0 >> 5) & 3), 0x03030303u), -kTwo23, c, v);
+    }
+};
+
+// E2M1 magnitudes times two, as bytes of a 64-bit table indexed by PRMT; negative levels are
+// formed as 0 - m so that code 8 decodes to +0 like the int8 table entry does.
+GGUF_D float fp4_level(uint32_t nib) {
+    const uint32_t mag = __byte_perm(0x03020100u, 0x0C080604u, nib & 7u);
+    const float m = __uint_as_float(mag | 0x4B000000u) - kTwo23;
+    return (nib & 8u) ? 0.f - m : m;
+}
+
+template <>
+struct Fast<GGML_TYPE_MXFP4> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 17, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(e8m0_half_to_f32(b[0]), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint4 q = lds16_any(b + 1);
+        const int sh = e0 ? 4 : 0;
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[4 * k + i] = fp4_level((w[k] >> (8 * i + sh)) & 0xFu) * c.x;
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_NVFP4> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 64, BYTES = 36, GROUP = 16;
+    static GGUF_D float2 prep(const uint8_t *b, int g) { return make_float2(ue4m3_half_to_f32(b[g]), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(b + 4 + (e0 >> 4) * 8);
+        const uint32_t q[2] = {w[0], w[1]};
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[4 * k + i] = fp4_level((q[k] >> (8 * i)) & 0xFu) * c.x;
+                v[8 + 4 * k + i] = fp4_level((q[k] >> (8 * i + 4)) & 0xFu) * c.x;
+            }
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
 template <class OutT>
 struct OutPack;
 
@@ -562,6 +773,88 @@ __global__ void __launch_bounds__(kThreads) dequant_tile_kernel(const uint8_t *_
     }
 }
 
+// 256-bit streaming store of 8 words (sm_100).
+GGUF_D void st_v8(void *p, const uint32_t (&w)[8]) {
+    asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
+}
+template <class OutT>
+GGUF_D void store16(OutT *dst, const float *v) {
+    uint32_t w[8];
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(v[8 * h + i]);
+            st_v8(reinterpret_cast<float *>(dst) + 8 * h, w);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if constexpr (std::is_same<OutT, __half>::value) {
+                const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t *>(&h);
+            } else {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t *>(&h);
+            }
+        }
+        st_v8(dst, w);
+    }
+}
+
+template <int TYPE, class OutT>
+__global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
+                                                               int64_t nblocks) {
+    using D = Fast<TYPE>;
+    constexpr int TILE_BLOCKS = kTileElems / D::ELEMS;
+    constexpr int TILE_BYTES = TILE_BLOCKS * D::BYTES;
+    constexpr int TILE_VECS = (TILE_BYTES + 15) / 16;
+    constexpr int TILE_GROUPS = kTileElems / D::GROUP;
+    constexpr int GROUPS_PER_BLOCK = D::ELEMS / D::GROUP;
+    constexpr int CHUNKS_PER_BLOCK = D::ELEMS / 16;
+    constexpr int CHUNKS_PER_THREAD = kTileElems / 16 / kThreads;  // 2
+    static_assert(kThreads % CHUNKS_PER_BLOCK == 0, "a thread keeps its position inside the block across iterations");
+    __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 32];
+    __shared__ float2 consts[TILE_GROUPS];
+
+    const int tid = threadIdx.x;
+    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
+    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
+    const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
+    const int nvec = (nb * D::BYTES + 15) >> 4;
+    uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+#pragma unroll
+    for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
+        const int i = k * kThreads + tid;
+        if (i < nvec) s16[i] = __ldcs(g16 + i);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
+        const int g = k * kThreads + tid;
+        const int blk = g / GROUPS_PER_BLOCK;
+        if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
+    }
+    __syncthreads();
+    // chunk c = u*kThreads + tid: position inside the block (e0) does not depend on u
+    const int e0 = (tid % CHUNKS_PER_BLOCK) * 16;
+    const int blk0 = tid / CHUNKS_PER_BLOCK;
+    OutT *out = dst + b0 * D::ELEMS + (int64_t)blk0 * D::ELEMS + e0;
+    const uint8_t *bp = tile + blk0 * D::BYTES;
+    const float2 *cp = consts + (blk0 * D::ELEMS + e0) / D::GROUP;
+#pragma unroll
+    for (int u = 0; u < CHUNKS_PER_THREAD; ++u) {
+        constexpr int BLOCK_STEP = kThreads / CHUNKS_PER_BLOCK;
+        if (blk0 + u * BLOCK_STEP < nb) {
+            float v[16];
+            D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
+            store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS, v);
+        }
+    }
+}
+
 template <int TYPE, class OutT>
 cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_t stream) {
     using D = Decoder<TYPE>;
@@ -571,6 +864,14 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
     if (grid <= 0) return cudaSuccess;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
     const int aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    if constexpr (Fast<TYPE>::kEnabled) {
+        if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            dequant_fast_kernel<TYPE, OutT><<<(unsigned)grid, kThreads, 0, stream>>>(static_cast<const uint8_t *>(src),
+                                                                                   static_cast<OutT *>(dst), nblocks);
+            count_launch();
+            return cudaGetLastError();
+        }
+    }
     dequant_tile_kernel<TYPE, OutT><<<(unsigned)grid, kThreads, 0, stream>>>(static_cast<const uint8_t *>(src),
                                                                            static_cast<OutT *>(dst), nblocks, aligned);
     count_launch();

@@ -206,7 +206,8 @@ def test_misaligned_device_pointers(checker):
         assert torch.equal(out[1:1 + 9 * 512].cpu().view(torch.int16), want.view(torch.int16))
         # quantize into a misaligned destination
         dst = torch.full((enc.size + 64,), 0xCD, dtype=torch.uint8, device="cuda")
-        st = lib.libgguf_cuda_quantize_f32_rows_on_stream(torch.from_numpy(x).cuda().data_ptr(), None, dst.data_ptr() + 5, qtype,
+        xt = torch.from_numpy(x).cuda()
+        st = lib.libgguf_cuda_quantize_f32_rows_on_stream(xt.data_ptr(), None, dst.data_ptr() + 5, qtype,
                                                           9, 512, torch.cuda.current_stream().cuda_stream)
         assert st == 0
         torch.cuda.synchronize()
