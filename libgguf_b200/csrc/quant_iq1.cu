@@ -1,0 +1,349 @@
+// Ternary lattice quantizers IQ1_S (32-element blocks) and IQ1_M (16-element blocks).
+//
+// One thread per block.  The upstream algorithm sorts the block's values, then searches all
+// split points (i1 <= i2) of the sorted order into the three levels {-1, 0, +1} (+- a fixed
+// shift), keeping the split with the best weighted projection score; the accept/reject chain is
+// order dependent through fp32 rounding, so it is replayed sequentially.  The winning level
+// pattern of each group of eight is then mapped to the 2048-entry codebook, through the
+// neighbour lists when it is not a codebook point.  Arrays that are indexed by data (the sorted
+// order, the prefix sums, the level scatter) live in shared memory, laid out [index][thread] so
+// that the uniform loops of a warp hit one row; everything indexed statically stays in registers.
+// upstream: csrc/quant/iq1_s.cpp:6-204, iq1_m.cpp:4-318, libgguf_iq_tables.cpp:714-789.
+#include <float.h>
+#include <math.h>
+
+#include "device_state.h"
+#include "gguf_common.cuh"
+#include "kernels.h"
+
+namespace gguf {
+namespace {
+
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kThreads = 64;
+
+GGUF_D void st16(uint8_t *p, uint32_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }
+
+template <int N>
+GGUF_D void load_group(const float *p, float (&x)[N]) {
+#pragma unroll
+    for (int k = 0; k < N / 4; ++k) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(p) + k);
+        x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+    }
+}
+
+// upstream libgguf_iq_tables.cpp:714-781 (the reachable part: a non-empty neighbour list)
+GGUF_D int best_neighbour_ternary(const uint16_t *__restrict__ nb, const uint8_t *__restrict__ grid, const float *xv,
+                                  const float *wv, float scale, const float (&xg)[3], int *L) {
+    const int n = __ldg(nb);
+    float best_score = FLT_MAX;
+    int best = -1;
+    for (int j = 1; j <= n; ++j) {
+        const int g = __ldg(nb + j);
+        const uint2 pgw = __ldg(reinterpret_cast<const uint2 *>(grid) + g);
+        float d2 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = (((i < 4 ? pgw.x : pgw.y) >> (8 * (i & 3))) & 0xFF) >> 1;  // (pg-1)/2 for pg in {1,3,5}
+            const float q = c == 0 ? xg[0] : c == 1 ? xg[1] : xg[2];
+            const float diff = scale * q - xv[i];
+            d2 += wv[i] * diff * diff;
+        }
+        if (d2 < best_score) { best_score = d2; best = g; }
+    }
+    const uint2 pgw = __ldg(reinterpret_cast<const uint2 *>(grid) + best);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) L[i] = (int)(((i < 4 ? pgw.x : pgw.y) >> (8 * (i & 3))) & 0xFF) >> 1;
+    return best;
+}
+
+GGUF_D float level_value(const uint8_t *__restrict__ grid, int index, int i, const float (&xg)[3]) {
+    const int c = (__ldg(grid + index * 8 + i) - 1) / 2;
+    return c == 0 ? xg[0] : c == 1 ? xg[1] : xg[2];
+}
+
+template <int BS>
+struct Scratch {
+    float xs[BS][kThreads];       // values, by element
+    float ws[BS][kThreads];       // weights, by element
+    float pa[BS + 1][kThreads];   // sort keys, then prefix sums of w*x (IQ1_S)
+    float pb[BS + 1][kThreads];   // prefix sums of w (IQ1_S)
+    uint8_t order[BS][kThreads];  // element index at each sorted position
+    uint8_t level[BS][kThreads];  // level of each element
+};
+
+// Stable ascending insertion sort of the keys in s.pa[0..BS) with their element indices
+// (upstream sorts (value, index) pairs with qsort comparing values only; the C library's merge
+// sort keeps equal values in index order).
+template <int BS>
+GGUF_D void sort_block(Scratch<BS> &s, int t) {
+    for (int jj = 1; jj < BS; ++jj) {
+        const float v = s.pa[jj][t];
+        const uint8_t id = s.order[jj][t];
+        int p = jj - 1;
+        while (p >= 0 && s.pa[p][t] > v) {
+            s.pa[p + 1][t] = s.pa[p][t];
+            s.order[p + 1][t] = s.order[p][t];
+            --p;
+        }
+        s.pa[p + 1][t] = v;
+        s.order[p + 1][t] = id;
+    }
+}
+
+template <bool IS_M>
+__global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
+                                                            uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
+                                                            IqSearchTable tab) {
+    constexpr int BS = IS_M ? 16 : 32, NG = BS / 8, W = 256 / BS, BYTES = IS_M ? 56 : 50;
+    __shared__ Scratch<BS> s;
+    const int t = threadIdx.x;
+    const int lane = t & 31, j = lane & (W - 1), gbase = lane & ~(W - 1);
+    int64_t blk = (int64_t)blockIdx.x * kThreads + t;
+    const bool active = blk < nblocks;
+    if (!active) blk = nblocks - 1;
+    float xb[BS], weight[BS];
+    load_group<BS>(src + blk * BS, xb);
+    const float x_p[3] = {-1 + 0.125f, 0.125f, 1 + 0.125f};
+    const float x_m[3] = {-1 - 0.125f, -0.125f, 1 - 0.125f};
+
+    float sumx2 = 0.f;
+#pragma unroll 1
+    for (int l = 0; l < W; ++l) {
+        if (j == l) {
+#pragma unroll
+            for (int i = 0; i < BS; ++i) sumx2 += xb[i] * xb[i];
+        }
+        sumx2 = __shfl_sync(kFull, sumx2, gbase + l);
+    }
+    const float sigma2 = 2 * sumx2 / QK_K;
+    if (qw) {
+        const float *qwp = qw + (blk * BS) % n_per_row;
+#pragma unroll
+        for (int i = 0; i < BS; ++i) weight[i] = __ldg(qwp + i) * sqrtf(sigma2 + xb[i] * xb[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < BS; ++i) weight[i] = xb[i] * xb[i];
+    }
+    float max = fabsf(xb[0]);
+#pragma unroll
+    for (int i = 1; i < BS; ++i) max = max > fabsf(xb[i]) ? max : fabsf(xb[i]);
+
+    float scale = 0.f;
+    int shift = IS_M ? 0 : 1;  // IQ1_S: +1 / -1, IQ1_M: sign pattern 0..3
+    int index[NG];
+#pragma unroll
+    for (int k = 0; k < NG; ++k) index[k] = 0;
+    bool skipped = max < (IS_M ? 1e-7f : 1e-12f);
+
+    if (!skipped) {
+#pragma unroll
+        for (int i = 0; i < BS; ++i) {
+            s.xs[i][t] = xb[i];
+            s.ws[i][t] = weight[i];
+            s.pa[i][t] = xb[i];
+            s.order[i][t] = (uint8_t)i;
+        }
+        sort_block<BS>(s, t);
+        float best_score = -FLT_MAX;
+        scale = max;
+        int besti1 = -1, besti2 = -1, best_k = IS_M ? -1 : 0;
+        if (!IS_M) {
+            // prefix sums over the sorted order
+            float sx = 0.f, sw = 0.f;
+            s.pa[0][t] = 0.f;
+            s.pb[0][t] = 0.f;
+            for (int jj = 0; jj < BS; ++jj) {
+                const int i = s.order[jj][t];
+                sx = sx + s.ws[i][t] * s.xs[i][t];
+                sw = sw + s.ws[i][t];
+                s.pa[jj + 1][t] = sx;
+                s.pb[jj + 1][t] = sw;
+            }
+            const float sx0 = s.pa[0][t], sw0 = s.pb[0][t], sxn = s.pa[BS][t], swn = s.pb[BS][t];
+            for (int i1 = 0; i1 <= BS; ++i1) {
+                const float sx1 = s.pa[i1][t], sw1 = s.pb[i1][t];
+                for (int i2 = i1; i2 <= BS; ++i2) {
+                    const float sx2 = s.pa[i2][t], sw2 = s.pb[i2][t];
+                    float sumqx = (sx1 - sx0) * x_p[0] + (sx2 - sx1) * x_p[1] + (sxn - sx2) * x_p[2];
+                    float sumq2 = (sw1 - sw0) * x_p[0] * x_p[0] + (sw2 - sw1) * x_p[1] * x_p[1] + (swn - sw2) * x_p[2] * x_p[2];
+                    if (sumq2 > 0 && sumqx * sumqx > best_score * sumq2) {
+                        scale = sumqx / sumq2; best_score = scale * sumqx; besti1 = i1; besti2 = i2; best_k = 1;
+                    }
+                    sumqx = (sx1 - sx0) * x_m[0] + (sx2 - sx1) * x_m[1] + (sxn - sx2) * x_m[2];
+                    sumq2 = (sw1 - sw0) * x_m[0] * x_m[0] + (sw2 - sw1) * x_m[1] * x_m[1] + (swn - sw2) * x_m[2] * x_m[2];
+                    if (sumq2 > 0 && sumqx * sumqx > best_score * sumq2) {
+                        scale = sumqx / sumq2; best_score = scale * sumqx; besti1 = i1; besti2 = i2; best_k = -1;
+                    }
+                }
+            }
+            if (besti1 < 0 || besti2 < 0 || best_k == 0) skipped = true;
+        } else {
+            // sorted copies in registers: weight, value, "element is in the first half"
+            float wso[BS], xso[BS];
+            uint32_t lo_mask = 0;
+#pragma unroll
+            for (int jj = 0; jj < BS; ++jj) {
+                const int i = s.order[jj][t];
+                wso[jj] = s.ws[i][t];
+                xso[jj] = s.xs[i][t];
+                if (i < BS / 2) lo_mask |= 1u << jj;
+            }
+            for (int i1 = 0; i1 <= BS; ++i1) {
+                for (int i2 = i1; i2 <= BS; ++i2) {
+                    float qx0 = 0, qx1 = 0, qx2 = 0, qx3 = 0, q20 = 0, q21 = 0, q22 = 0, q23 = 0;
+#pragma unroll
+                    for (int jj = 0; jj < BS; ++jj) {
+                        const int lv = jj < i1 ? 0 : (jj < i2 ? 1 : 2);
+                        const float xp = lv == 0 ? x_p[0] : lv == 1 ? x_p[1] : x_p[2];
+                        const float xm = lv == 0 ? x_m[0] : lv == 1 ? x_m[1] : x_m[2];
+                        const float ap = wso[jj] * xp * xso[jj], am = wso[jj] * xm * xso[jj];
+                        const float bp = wso[jj] * xp * xp, bm = wso[jj] * xm * xm;
+                        const bool lo = (lo_mask >> jj) & 1;
+                        qx0 += ap; qx1 += lo ? ap : am; qx2 += lo ? am : ap; qx3 += am;
+                        q20 += bp; q21 += lo ? bp : bm; q22 += lo ? bm : bp; q23 += bm;
+                    }
+                    const float sqx[4] = {qx0, qx1, qx2, qx3}, sq2[4] = {q20, q21, q22, q23};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (sq2[k] > 0 && sqx[k] * sqx[k] > best_score * sq2[k]) {
+                            scale = sqx[k] / sq2[k]; best_score = scale * sqx[k]; besti1 = i1; besti2 = i2; best_k = k;
+                        }
+                    }
+                }
+            }
+            if (besti1 < 0 || besti2 < 0 || best_k < 0) skipped = true;
+        }
+        if (skipped) {
+            scale = 0.f;
+        } else {
+            for (int jj = 0; jj < BS; ++jj) s.level[s.order[jj][t]][t] = (uint8_t)(jj < besti1 ? 0 : (jj < besti2 ? 1 : 2));
+            int L[BS];
+#pragma unroll
+            for (int i = 0; i < BS; ++i) L[i] = s.level[i][t];
+            if (scale < 0) {
+#pragma unroll
+                for (int i = 0; i < BS; ++i) L[i] = 2 - L[i];
+                scale = -scale;
+                best_k = IS_M ? 3 - best_k : -best_k;
+            }
+            bool all_on_grid = true;
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                const bool plus = IS_M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
+                const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
+                uint32_t u = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) u |= (uint32_t)L[8 * k + i] << (2 * i);
+                int g = __ldg(tab.map + u);
+                if (g < 0) {
+                    all_on_grid = false;
+                    g = best_neighbour_ternary(tab.neighbours + (-g - 1), tab.grid, xb + 8 * k, weight + 8 * k, scale, xx, L + 8 * k);
+                }
+                index[k] = g;
+            }
+            if (!all_on_grid) {
+                float sumqx = 0, sumq2 = 0;
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    const bool plus = IS_M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
+                    const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float w = weight[8 * k + i];
+                        const float q = level_value(tab.grid, index[k], i, xx);
+                        sumqx += w * q * xb[8 * k + i];
+                        sumq2 += w * q * q;
+                    }
+                }
+                if (sumqx > 0 && sumq2 > 0) scale = sumqx / sumq2;
+            }
+            shift = best_k;
+        }
+    }
+    if (skipped) { scale = 0.f; shift = IS_M ? 0 : 1; }
+
+    // ---- super-block stage ----
+    float max_scale = scale;
+#pragma unroll
+    for (int m = 1; m < W; m <<= 1) {
+        const float o = __shfl_xor_sync(kFull, max_scale, m);
+        max_scale = max_scale > o ? max_scale : o;
+    }
+    const bool empty = !(max_scale != 0.f);
+    float d = max_scale / 15;
+    const float idd = 1 / d;
+    int l = 0;
+    if (!empty) l = imax(0, imin(7, nearest_int(0.5f * (idd * scale - 1))));
+    uint8_t *out = dst + (blk / W) * BYTES;
+
+    if constexpr (!IS_M) {
+        if (!active) return;
+        if (j == 0) st16(out, empty ? 0u : f32_to_half_bits(d * 1.125f));
+        uint32_t h = 0;
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            out[2 + 4 * j + k] = (uint8_t)index[k];
+            h |= (uint32_t)(index[k] >> 8) << (3 * k);
+        }
+        if (!empty) h |= (uint32_t)(l | (shift == -1 ? 8 : 0)) << 12;
+        st16(out + 34 + 2 * j, h);
+    } else {
+        // refit of the super-block scale over all 256 elements in block order (lane to lane)
+        const uint32_t masks[4] = {0x00, 0x80, 0x08, 0x88};
+        float sumqx_f = 0.f, sumq2_f = 0.f;
+#pragma unroll 1
+        for (int sidx = 0; sidx < W; ++sidx) {
+            if (j == sidx && !empty) {
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    const bool plus = k == 0 ? shift < 2 : (shift % 2 == 0);
+                    const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float w = weight[8 * k + i];
+                        const float q = level_value(tab.grid, index[k], i, xx) * (float)(2 * l + 1);
+                        sumqx_f += w * q * xb[8 * k + i];
+                        sumq2_f += w * q * q;
+                    }
+                }
+            }
+            sumqx_f = __shfl_sync(kFull, sumqx_f, gbase + sidx);
+            sumq2_f = __shfl_sync(kFull, sumq2_f, gbase + sidx);
+        }
+        if (sumq2_f > 0) d = sumqx_f / sumq2_f;
+        const uint32_t s16 = empty ? 0u : f32_to_half_bits(d * 1.1125f);
+        // scale word w = 3-bit codes of blocks 4w..4w+3 plus one nibble of the fp16 super-scale
+        const int l1 = __shfl_down_sync(kFull, l, 1), l2 = __shfl_down_sync(kFull, l, 2), l3 = __shfl_down_sync(kFull, l, 3);
+        if (!active) return;
+        out[2 * j] = (uint8_t)index[0];
+        out[2 * j + 1] = (uint8_t)index[1];
+        out[32 + j] = (uint8_t)((index[0] >> 8) | ((index[1] >> 8) << 4) | (empty ? 0u : masks[shift]));
+        if ((j & 3) == 0) {
+            const int w = j >> 2;
+            uint32_t word = 0;
+            if (!empty) word = (uint32_t)(l | (l1 << 3) | (l2 << 6) | (l3 << 9)) | (((s16 >> (4 * w)) & 0xF) << 12);
+            st16(out + 48 + 2 * w, word);
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_quantize_iq1(int type, const float *src, const float *qw, void *dst, int64_t nelems, int64_t n_per_row,
+                                const DeviceState *state, cudaStream_t stream) {
+    const IqSearchTable &tab = state->iq[IQT_1S];
+    if (!tab.grid) return cudaErrorInvalidValue;
+    const bool is_m = type == GGML_TYPE_IQ1_M;
+    const int64_t nblocks = nelems / (is_m ? 16 : 32);
+    if (nblocks <= 0) return cudaSuccess;
+    const int64_t grid = (nblocks + kThreads - 1) / kThreads;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    if (is_m) quant_iq1_kernel<true><<<(unsigned)grid, kThreads, 0, stream>>>(src, qw, static_cast<uint8_t *>(dst), nblocks, n_per_row, tab);
+    else quant_iq1_kernel<false><<<(unsigned)grid, kThreads, 0, stream>>>(src, qw, static_cast<uint8_t *>(dst), nblocks, n_per_row, tab);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace gguf
