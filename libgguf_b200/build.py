@@ -1,6 +1,8 @@
 """Builds libgguf_b200.so, the C-ABI shared library with the sm_100a kernels, in-tree.
 
-    python -m libgguf_b200.build [--force] [--verbose]
+    python libgguf_b200/build.py [--force] [--verbose]
+
+(run it as a script: importing the package needs the library this script produces)
 
 Every translation unit is compiled with
     -gencode arch=compute_100a,code=sm_100a --fmad=false
