@@ -120,6 +120,32 @@ LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
  * device, and waits for the upload.  Optional: the row functions do it on first use. */
 LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
 
+/* Importance-weighted Q4_0 / Q4_1 / Q5_0 / Q5_1 quantization that allocates nothing.  It has no
+ * counterpart in upstream.  It exists for callers that are not allowed to allocate device memory
+ * at the moment they quantize: a host that owns all GPU memory through its own pool and rejects
+ * outside allocations, a process pinned to a fixed memory budget, or a latency-critical loop in
+ * which an allocator call is not acceptable.  libgguf_cuda_quantize_f32_rows[_on_stream] obtains
+ * one float of scratch per row from the stream-ordered allocator for these types; this entry
+ * point keeps that scratch in a fixed array inside the library instead (256 KiB, present on every
+ * GPU that loads the library, for the life of the process) and calls no cudaMalloc, cudaFree or
+ * other allocating routine.
+ *   - device_imatrix is required (n_per_row floats); qtype must be one of the four types above.
+ *   - rows may be at most libgguf_cuda_quantize_weighted_rows_static_max_rows() (65536); larger
+ *     requests are refused with LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT and a message -- split them.
+ *   - The first call on a device looks up the array's device address (once per device, with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls share the one array, which keeps whatever the previous call left in it.  Each
+ *     call writes the entries it needs before it reads them, so no clearing is needed, but calls
+ *     whose kernels can overlap on the GPU (other streams, other host threads) would race on it:
+ *     serialise them.
+ * Output bytes are identical to those of libgguf_cuda_quantize_f32_rows_on_stream.
+ * Runs asynchronously on `stream` (a cudaStream_t passed as void*) of the current device and
+ * returns a libgguf_cuda_status; the message is read with libgguf_cuda_thread_last_error(). */
+LIBGGUF_CUDA_API int libgguf_cuda_quantize_weighted_rows_static(const float *device_input, const float *device_imatrix,
+                                                                void *device_output, int64_t qtype, int64_t rows,
+                                                                int64_t n_per_row, void *stream);
+LIBGGUF_CUDA_API int64_t libgguf_cuda_quantize_weighted_rows_static_max_rows(void);
+
 #ifdef __cplusplus
 }
 #endif

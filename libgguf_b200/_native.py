@@ -59,13 +59,15 @@ NATIVE_ABI = {
     "libgguf_cuda_thread_last_error": (c_char_p, []),
     "libgguf_cuda_kernel_launch_count": (c_uint64, []),
     "libgguf_cuda_prepare_qtype": (c_int, [c_int64]),
+    "libgguf_cuda_quantize_weighted_rows_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "libgguf_cuda_quantize_weighted_rows_static_max_rows": (c_int64, []),
 }
 
 
 def _load() -> ctypes.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m libgguf_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python libgguf_b200/build.py` "
             "(nvcc, sm_100a); libgguf_b200 has no CPU implementation to fall back to")
     lib = ctypes.CDLL(str(LIB_PATH))
     for table in (HOST_ABI, NATIVE_ABI):

@@ -31,6 +31,12 @@ struct libgguf_cuda_event {
 
 using namespace gguf;
 
+namespace gguf {
+int64_t static_scratch_max_rows();
+cudaError_t launch_quantize_legacy_weighted_static(int type, const float *src, const float *qw, void *dst, int64_t nrows,
+                                                   int64_t n_per_row, cudaStream_t stream);
+}  // namespace gguf
+
 namespace {
 
 thread_local std::string t_thread_error;
@@ -335,6 +341,27 @@ int libgguf_cuda_dequantize_rows_on_stream(const void *device_input, int64_t qty
                                            int output_dtype, void *device_output, void *stream) {
     return run_dequantize(nullptr, device_input, qtype, rows, n_per_row, output_dtype, device_output,
                           reinterpret_cast<cudaStream_t>(stream));
+}
+
+int64_t libgguf_cuda_quantize_weighted_rows_static_max_rows(void) { return static_scratch_max_rows(); }
+
+int libgguf_cuda_quantize_weighted_rows_static(const float *device_input, const float *device_imatrix, void *device_output,
+                                               int64_t qtype, int64_t rows, int64_t n_per_row, void *stream) {
+    if (!device_input || !device_imatrix || !device_output || rows < 0 || n_per_row <= 0)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "invalid quantize arguments (input, imatrix and output are all required)");
+    if (qtype != GGML_TYPE_Q4_0 && qtype != GGML_TYPE_Q4_1 && qtype != GGML_TYPE_Q5_0 && qtype != GGML_TYPE_Q5_1)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE,
+                    "the allocation-free entry point covers the importance-weighted Q4_0, Q4_1, Q5_0 and Q5_1 quantizers only");
+    if (n_per_row % 32 != 0)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "row width is not divisible by quantization block size");
+    if (rows > static_scratch_max_rows())
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT,
+                    "too many rows for the built-in scratch array (limit 65536 rows per call): split the call by rows");
+    if (rows == 0) return ok(nullptr);
+    const cudaError_t error = launch_quantize_legacy_weighted_static((int)qtype, device_input, device_imatrix, device_output, rows,
+                                                                     n_per_row, reinterpret_cast<cudaStream_t>(stream));
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    return ok(nullptr);
 }
 
 int libgguf_cuda_prepare_qtype(int64_t qtype) {

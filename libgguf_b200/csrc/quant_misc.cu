@@ -3,6 +3,9 @@
 // registers as in search.cuh.
 #include <math.h>
 
+#include <mutex>
+
+#include "device_state.h"
 #include "gguf_common.cuh"
 #include "gguf_tables.cuh"
 #include "kernels.h"
@@ -253,6 +256,64 @@ cudaError_t launch_quantize_legacy_weighted(int type, const float *src, const fl
     err = cudaGetLastError();
     const cudaError_t free_err = cudaFreeAsync(sigma2, stream);
     return err != cudaSuccess ? err : free_err;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the importance-weighted legacy quantizer.
+//
+// The two-kernel scheme above needs one float of scratch per row (the row's mean square).  Here
+// that scratch is a fixed array in the library's device image instead of a stream-ordered
+// allocation, for callers that must not allocate: code running where the CUDA allocator is off
+// limits (inside a memory-pool owner that forbids foreign allocations, under a hard memory
+// budget, or in a real-time loop where an allocation's latency is not acceptable).
+// Every GPU that loads the library carries the array (kStaticScratchRows * 4 bytes = 256 KiB)
+// until the process exits.  All calls share it and it keeps the previous call's contents; each
+// call overwrites the entries it uses before reading them, so nothing has to be cleared, but two
+// calls whose kernels overlap on the GPU (different streams, or different host threads) race.
+constexpr int64_t kStaticScratchRows = 65536;
+static __device__ __align__(256) float g_row_scratch[kStaticScratchRows];
+
+// Device address of g_row_scratch on each device.  In host code the array's name is only a
+// stand-in; the address a kernel may use comes from cudaGetSymbolAddress, asked once per device
+// with that device current.
+static float *g_row_scratch_addr[kMaxDevices];
+static std::mutex g_row_scratch_lock;
+
+int64_t static_scratch_max_rows() { return kStaticScratchRows; }
+
+cudaError_t launch_quantize_legacy_weighted_static(int type, const float *src, const float *qw, void *dst, int64_t nrows,
+                                                   int64_t n_per_row, cudaStream_t stream) {
+    if (nrows <= 0) return cudaSuccess;
+    if (nrows > kStaticScratchRows) return cudaErrorInvalidValue;
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    float *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(g_row_scratch_lock);
+        if (!g_row_scratch_addr[dev]) {
+            void *p = nullptr;
+            err = cudaGetSymbolAddress(&p, g_row_scratch);
+            if (err != cudaSuccess) return err;
+            g_row_scratch_addr[dev] = static_cast<float *>(p);
+        }
+        scratch = g_row_scratch_addr[dev];
+    }
+    row_sigma2_kernel<<<(unsigned)((nrows + 3) / 4), kThreads, 0, stream>>>(src, scratch, nrows, n_per_row);
+    count_launch();
+    const int64_t nblocks = nrows * n_per_row / 32;
+    const unsigned grid = (unsigned)((nblocks + kThreads - 1) / kThreads);
+    uint8_t *out = static_cast<uint8_t *>(dst);
+    switch (type) {
+        case GGML_TYPE_Q4_0: legacy_weighted_kernel<GGML_TYPE_Q4_0><<<grid, kThreads, 0, stream>>>(src, qw, scratch, out, nblocks, n_per_row); break;
+        case GGML_TYPE_Q4_1: legacy_weighted_kernel<GGML_TYPE_Q4_1><<<grid, kThreads, 0, stream>>>(src, qw, scratch, out, nblocks, n_per_row); break;
+        case GGML_TYPE_Q5_0: legacy_weighted_kernel<GGML_TYPE_Q5_0><<<grid, kThreads, 0, stream>>>(src, qw, scratch, out, nblocks, n_per_row); break;
+        case GGML_TYPE_Q5_1: legacy_weighted_kernel<GGML_TYPE_Q5_1><<<grid, kThreads, 0, stream>>>(src, qw, scratch, out, nblocks, n_per_row); break;
+        default: return cudaErrorInvalidValue;
+    }
+    count_launch();
+    return cudaGetLastError();
 }
 
 cudaError_t launch_quantize_iq4(int type, const float *src, const float *qw, void *dst, int64_t nelems, int64_t n_per_row,
