@@ -287,7 +287,7 @@ def main() -> None:
         t = json.loads(tfile.read_text()).get(f"dequant_{dominant}")
         if t:
             traffic = t["dram_bytes_per_elem"] * rows * WIDTH
-    roofline = {"bound": "hbm", "kernel": f"dequant_tile_kernel<{dominant}, fp16|bf16>", "achieved": achieved, "peak": hbm,
+    roofline = {"bound": "hbm", "kernel": f"dequant_fast_kernel<{dominant}, fp16|bf16>", "achieved": achieved, "peak": hbm,
                 "unit": "GB/s", "frac": achieved / hbm, "traffic": traffic, "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": algo_bytes[dominant], "launch_ms": dom_ms}
 

@@ -1,0 +1,205 @@
+"""Secondary workloads of bench.py (`--workload NAME`): the quantizer and conversion configurations.
+
+  q4k_roundtrip  BASELINE config 1: Q4_K quantize + dequantize->fp32 of 4096x4096 N(0, 0.02)
+  kquant         quantize 14336x4096 to Q8_0, Q6_K, Q5_K, Q4_K, Q3_K, Q2_K
+  legacy         quantize 14336x4096 to Q4_0, Q4_1, Q5_0, Q5_1, Q1_0, TQ1_0, TQ2_0, IQ4_NL, IQ4_XS
+  iq             BASELINE config 4: IQ2_XXS, IQ2_S, IQ3_XXS, IQ1_S (+ IQ2_XS, IQ3_S, IQ1_M) on 4096x11008
+                 Student-t(5)*0.02 with a chi-square(4)/4 imatrix
+  fp4            BASELINE config 5: MXFP4 / NVFP4 quantize and dequantize->bf16 of 8192x8192 Laplace(0, 0.01)
+  convert        BASELINE config 3: synthetic Llama-3-8B-shaped weight set through the multi-GPU streaming
+                 pipeline (pinned host memory in and out), Q4_K_M-style mix
+
+Each prints one JSON line: metric Melem/s (GB/s of source for `convert`), per-type table with the fraction of the
+bound that applies (HBM for the cheap encoders, fp32 issue rate for the search-heavy ones).
+Inputs live in HBM; every timed launch uses one of NSETS distinct input/output buffer sets."""
+from __future__ import annotations
+
+import json
+import statistics
+import time
+
+NSETS = 3
+FP32_LANES = 148 * 128  # fp32 lanes of a B200
+
+# flop per element of the upstream algorithm (no FMA), for the pipe-bound encoders
+FLOP_PER_ELEM = {"Q4_K": 480, "Q5_K": 370, "Q2_K": 375, "Q6_K": 280, "Q3_K": 125, "MXFP4": 85, "NVFP4": 85}
+
+BLOCK = {"Q4_0": (32, 18), "Q4_1": (32, 20), "Q5_0": (32, 22), "Q5_1": (32, 24), "Q8_0": (32, 34), "Q1_0": (128, 18),
+         "MXFP4": (32, 17), "NVFP4": (64, 36), "Q2_K": (256, 84), "Q3_K": (256, 110), "Q4_K": (256, 144),
+         "Q5_K": (256, 176), "Q6_K": (256, 210), "TQ1_0": (256, 54), "TQ2_0": (256, 66), "IQ2_XXS": (256, 66),
+         "IQ2_XS": (256, 74), "IQ2_S": (256, 82), "IQ3_XXS": (256, 98), "IQ3_S": (256, 110), "IQ1_S": (256, 50),
+         "IQ1_M": (256, 56), "IQ4_NL": (32, 18), "IQ4_XS": (256, 136)}
+CODE = {"Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14,
+        "IQ2_XXS": 16, "IQ2_XS": 17, "IQ3_XXS": 18, "IQ1_S": 19, "IQ4_NL": 20, "IQ3_S": 21, "IQ2_S": 22, "IQ4_XS": 23,
+        "IQ1_M": 29, "TQ1_0": 34, "TQ2_0": 35, "MXFP4": 39, "NVFP4": 40, "Q1_0": 41}
+
+
+def _time_launches(torch, stream, fn, reps):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for k in range(reps):
+        fn(k)
+    b.record(stream)
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def _make_input(torch, device, kind, rows, cols, seed):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    if kind == "normal":
+        return torch.randn((rows, cols), generator=g, device=device) * 0.02
+    if kind == "student":
+        z = torch.randn((rows, cols), generator=g, device=device)
+        chi = sum(torch.randn((rows, cols), generator=g, device=device) ** 2 for _ in range(5))
+        return z / torch.sqrt(chi / 5) * 0.02
+    if kind == "laplace":
+        u = torch.rand((rows, cols), generator=g, device=device) - 0.5
+        x = -0.01 * torch.sign(u) * torch.log1p(-2 * u.abs())
+        x = x.to(torch.bfloat16).to(torch.float32)
+        nblk = rows * cols // 32
+        pick = torch.randperm(nblk, generator=g, device=device)[: max(1, nblk // 100)]
+        pos = torch.randint(0, 32, (pick.numel(),), generator=g, device=device)
+        sign = torch.randint(0, 2, (pick.numel(),), generator=g, device=device).float() * 2 - 1
+        flat = x.reshape(-1)
+        flat[pick * 32 + pos] = (sign * 50 * 0.01 * 2 ** 0.5).to(torch.bfloat16).to(torch.float32)
+        return flat.reshape(rows, cols)
+    raise ValueError(kind)
+
+
+def run(args, torch, dist, lib, ops, device, rank, world):
+    import bench
+    stream = torch.cuda.current_stream(device)
+    hbm, peak_kind = bench.peaks()
+    wl = args.workload
+    if wl == "convert":
+        return run_convert(args, torch, dist, lib, device, rank, world, hbm)
+    shapes = {"q4k_roundtrip": (4096, 4096, "normal", ["Q4_K"], False),
+              "kquant": (14336, 4096, "normal", ["Q8_0", "Q6_K", "Q5_K", "Q4_K", "Q3_K", "Q2_K"], False),
+              "legacy": (14336, 4096, "normal", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q1_0", "TQ1_0", "TQ2_0", "IQ4_NL", "IQ4_XS"], False),
+              "iq": (4096, 11008, "student", ["IQ2_XXS", "IQ2_S", "IQ3_XXS", "IQ1_S", "IQ2_XS", "IQ3_S", "IQ1_M"], True),
+              "fp4": (8192, 8192, "laplace", ["MXFP4", "NVFP4"], False)}
+    rows, cols, kind, types, weighted = shapes[wl]
+    if args.rows != bench.ROWS:
+        rows = args.rows
+    xs = [_make_input(torch, device, kind, rows, cols, seed) for seed in range(NSETS)]
+    im = None
+    if weighted:
+        g = torch.Generator(device=device)
+        g.manual_seed(1)
+        im = (sum(torch.randn(cols, generator=g, device=device) ** 2 for _ in range(4)) / 4).contiguous()
+    n = rows * cols
+    sampler = bench.ClockSampler(int(device.index or 0))
+    launches0 = lib.libgguf_cuda_kernel_launch_count()
+    table = {}
+    reps = max(1, args.steps)
+    total_ms = 0.0
+    sampler.start()
+    for name in types:
+        code, (bel, bby) = CODE[name], BLOCK[name]
+        enc_bytes = n // bel * bby
+        outs = [torch.empty((rows, cols // bel * bby), dtype=torch.uint8, device=device) for _ in range(NSETS)]
+
+        def quant(k):
+            st = lib.libgguf_cuda_quantize_f32_rows_on_stream(xs[k % NSETS].data_ptr(), im.data_ptr() if im is not None else None,
+                                                              outs[k % NSETS].data_ptr(), code, rows, cols, stream.cuda_stream)
+            if st != 0:
+                raise RuntimeError(lib.libgguf_cuda_thread_last_error().decode())
+
+        for k in range(max(3, args.warmup)):
+            quant(k)
+        torch.cuda.synchronize()
+        ms = _time_launches(torch, stream, quant, reps)
+        total_ms += ms
+        row = {"quant_ms": round(ms, 4), "quant_Melem/s": round(n / ms / 1e3, 1),
+               "quant_GB/s": round((4 * n + enc_bytes) / ms / 1e6, 1), "hbm_frac": round((4 * n + enc_bytes) / ms / 1e6 / hbm, 4)}
+        if name in FLOP_PER_ELEM:
+            row["fp32_issue_frac_at_max_clock"] = round(FLOP_PER_ELEM[name] * n / (ms * 1e-3) / (FP32_LANES * 1.965e9), 4)
+        if wl in ("q4k_roundtrip", "fp4"):
+            dt = torch.float32 if wl == "q4k_roundtrip" else torch.bfloat16
+            code_dt = 0 if dt == torch.float32 else 2
+            dec = [torch.empty((rows, cols), dtype=dt, device=device) for _ in range(NSETS)]
+
+            def dequant(k):
+                st = lib.libgguf_cuda_dequantize_rows_on_stream(outs[k % NSETS].data_ptr(), code, rows, cols, code_dt,
+                                                                dec[k % NSETS].data_ptr(), stream.cuda_stream)
+                if st != 0:
+                    raise RuntimeError(lib.libgguf_cuda_thread_last_error().decode())
+
+            for k in range(3):
+                dequant(k)
+            torch.cuda.synchronize()
+            dms = _time_launches(torch, stream, dequant, reps)
+            db = enc_bytes + n * dec[0].element_size()
+            row.update({"dequant_ms": round(dms, 4), "dequant_GB/s": round(db / dms / 1e6, 1), "dequant_hbm_frac": round(db / dms / 1e6 / hbm, 4)})
+            total_ms += dms
+            del dec
+        table[name] = row
+        del outs
+    clocks = sampler.stop()
+    launches = lib.libgguf_cuda_kernel_launch_count() - launches0
+    value = len(types) * n / total_ms / 1e3
+    if rank == 0:
+        print(json.dumps({
+            "metric": "quant Melem/s", "value": value, "unit": "Melem/s", "n_gpus": world, "steps": reps, "warmup": max(3, args.warmup),
+            "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{wl} {rows}x{cols} {kind}{' +imatrix' if weighted else ''}: {','.join(types)}",
+                       "l2": f"{NSETS} rotating input/output buffer sets per kernel"},
+            "clocks": clocks, "gpu_launches": int(launches), "per_qtype": table, "peak_source": peak_kind}))
+
+
+def run_convert(args, torch, dist, lib, device, rank, world, hbm):
+    """Whole-model conversion through the in-process multi-GPU pipeline; rank 0 drives the first `--gpus` devices."""
+    import numpy as np
+    from libgguf_b200 import row_size
+    from libgguf_b200.convert import ConversionPipeline, llama3_8b_plan
+    if rank != 0:
+        return
+    ndev = min(args.gpus, torch.cuda.device_count())
+    plan = llama3_8b_plan()
+    # one pinned source per distinct shape (layer tensors are re-used by all 32 layers), values N(0, 0.02) with
+    # 0.1% of the columns scaled by 20; outputs are distinct pinned buffers per tensor
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+    sources = {}
+    for t in plan:
+        key = (t.rows, t.cols)
+        if key not in sources:
+            x = torch.randn((t.rows, t.cols), generator=g, device=device) * 0.02
+            cols = torch.randperm(t.cols, generator=g, device=device)[: max(1, t.cols // 1000)]
+            x[:, cols] *= 20
+            host = torch.empty((t.rows, t.cols), dtype=torch.float32).pin_memory()
+            host.copy_(x)
+            sources[key] = host
+            del x
+    torch.cuda.synchronize()
+    outs, batch = [], []
+    for t in plan:
+        o = torch.empty(t.rows * row_size(t.qtype, t.cols), dtype=torch.uint8).pin_memory()
+        outs.append(o)
+        batch.append((t.qtype, sources[(t.rows, t.cols)].numpy(), None, o.numpy()))
+    in_bytes = sum(t.rows * t.cols * 4 for t in plan)
+    out_bytes = sum(o.numel() for o in outs)
+    times = []
+    with ConversionPipeline(list(range(ndev)), slots=3, chunk_bytes=128 << 20) as pipe:
+        for it in range(1 + max(1, min(args.steps, 3))):
+            t0 = time.perf_counter()
+            pipe.quantize(batch)
+            times.append(time.perf_counter() - t0)
+        stats = pipe.stats()
+    best = min(times[1:])
+    # spot check against the single-GPU device path
+    from libgguf_b200.libgguf_cuda import ops
+    ok = True
+    for idx in (1, 3, 7, len(plan) - 1):
+        t = plan[idx]
+        rows = min(t.rows, 256)
+        ref = ops.quantize(sources[(t.rows, t.cols)][:rows].to(device), t.qtype).cpu().numpy().reshape(-1)
+        ok = ok and bool(np.array_equal(ref, outs[idx].numpy()[: ref.size]))
+    print(json.dumps({
+        "metric": "conversion GB/s of fp32 source", "value": in_bytes / best / 1e9, "unit": "GB/s", "n_gpus": ndev, "steps": len(times) - 1,
+        "warmup": 1, "ms_per_step": best * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": "convert Llama-3-8B-shaped set, Q4_K_M mix, pinned host in/out", "tensors": len(plan),
+                                       "source_bytes": in_bytes, "output_bytes": out_bytes,
+                                       "note": "layer sources shared by the 32 layers (one 0.87 GB layer + 2.1 GB embedding resident in pinned memory)"},
+        "elements_per_s": in_bytes / 4 / best, "all_times_s": [round(x, 4) for x in times], "pipeline": stats, "spot_check_ok": ok}))

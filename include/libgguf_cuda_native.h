@@ -120,6 +120,45 @@ LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
  * device, and waits for the upload.  Optional: the row functions do it on first use. */
 LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
 
+/* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,
+ * csrc/quantize_gguf.cpp:1732-1931 and :2072-2146; the pool itself has no upstream counterpart) ----
+ * A batch of tensors (host memory, fp32 rows in, encoded rows out) is cut into shards of whole rows of at most
+ * chunk_bytes of input, and the shards are streamed through `slots` in-flight copies per GPU on every listed GPU.
+ * Pinned host memory is copied from / to directly, pageable memory through pinned staging.  No GPU talks to
+ * another GPU.  libgguf_cuda_pipeline_quantize blocks until the batch is done; the output bytes are independent
+ * of the number of GPUs, the chunk size and the order in which shards complete. */
+typedef struct libgguf_cuda_pipeline libgguf_cuda_pipeline;
+typedef struct libgguf_cuda_tensor_desc {
+    int64_t qtype;
+    const float *src;     /* rows x n_per_row fp32, host */
+    const float *imatrix; /* n_per_row floats (host) or NULL */
+    void *dst;            /* rows x row_size bytes, host */
+    int64_t rows;
+    int64_t n_per_row;
+} libgguf_cuda_tensor_desc;
+typedef struct libgguf_cuda_shard {
+    int32_t tensor;
+    int64_t row0;
+    int64_t rows;
+} libgguf_cuda_shard;
+/* slots <= 0 -> 3, chunk_bytes == 0 -> 128 MiB */
+LIBGGUF_CUDA_API int libgguf_cuda_pipeline_create(const int *devices, int n_devices, int slots, size_t chunk_bytes,
+                                                  libgguf_cuda_pipeline **out);
+LIBGGUF_CUDA_API void libgguf_cuda_pipeline_destroy(libgguf_cuda_pipeline *pipe);
+LIBGGUF_CUDA_API const char *libgguf_cuda_pipeline_last_error(const libgguf_cuda_pipeline *pipe);
+LIBGGUF_CUDA_API int libgguf_cuda_pipeline_quantize(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc *tensors,
+                                                    int n_tensors);
+/* The shard list the pipeline would use (largest first); returns the shard count, -1 on a bad descriptor.
+ * Needs no GPU. */
+LIBGGUF_CUDA_API int64_t libgguf_cuda_pipeline_plan(const libgguf_cuda_tensor_desc *tensors, int n_tensors, size_t chunk_bytes,
+                                                    libgguf_cuda_shard *out, int64_t max_out);
+/* Shards completed and seconds spent by each GPU worker in the last batch, and how many shards were handed back. */
+LIBGGUF_CUDA_API int libgguf_cuda_pipeline_stats(const libgguf_cuda_pipeline *pipe, int64_t *shards_per_device,
+                                                 double *seconds_per_device, int64_t *requeued);
+/* Test hook, host side only: the worker of devices[device_slot] reports a failure once it has completed
+ * after_shards shards (-1 = never); its unfinished shards go back to the queue for the other GPUs. */
+LIBGGUF_CUDA_API int libgguf_cuda_pipeline_inject_failure(libgguf_cuda_pipeline *pipe, int device_slot, int64_t after_shards);
+
 /* Importance-weighted Q4_0 / Q4_1 / Q5_0 / Q5_1 quantization that allocates nothing.  It has no
  * counterpart in upstream.  It exists for callers that are not allowed to allocate device memory
  * at the moment they quantize: a host that owns all GPU memory through its own pool and rejects

@@ -7,7 +7,19 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_bool, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p, POINTER
+from ctypes import c_bool, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p, POINTER
+
+
+class TensorDesc(ctypes.Structure):
+    """libgguf_cuda_tensor_desc"""
+    _fields_ = [("qtype", c_int64), ("src", c_void_p), ("imatrix", c_void_p), ("dst", c_void_p),
+                ("rows", c_int64), ("n_per_row", c_int64)]
+
+
+class ShardDesc(ctypes.Structure):
+    """libgguf_cuda_shard"""
+    _fields_ = [("tensor", c_int32), ("row0", c_int64), ("rows", c_int64)]
+
 from pathlib import Path
 
 LIB_PATH = Path(os.environ.get("LIBGGUF_B200_LIBRARY", Path(__file__).with_name("libgguf_b200.so")))
@@ -61,6 +73,13 @@ NATIVE_ABI = {
     "libgguf_cuda_prepare_qtype": (c_int, [c_int64]),
     "libgguf_cuda_quantize_weighted_rows_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "libgguf_cuda_quantize_weighted_rows_static_max_rows": (c_int64, []),
+    "libgguf_cuda_pipeline_create": (c_int, [POINTER(c_int), c_int, c_int, c_size_t, POINTER(c_void_p)]),
+    "libgguf_cuda_pipeline_destroy": (None, [c_void_p]),
+    "libgguf_cuda_pipeline_last_error": (c_char_p, [c_void_p]),
+    "libgguf_cuda_pipeline_quantize": (c_int, [c_void_p, POINTER(TensorDesc), c_int]),
+    "libgguf_cuda_pipeline_plan": (c_int64, [POINTER(TensorDesc), c_int, c_size_t, POINTER(ShardDesc), c_int64]),
+    "libgguf_cuda_pipeline_stats": (c_int, [c_void_p, POINTER(c_int64), POINTER(c_double), POINTER(c_int64)]),
+    "libgguf_cuda_pipeline_inject_failure": (c_int, [c_void_p, c_int, c_int64]),
 }
 
 

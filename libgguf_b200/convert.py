@@ -1,0 +1,121 @@
+"""Multi-GPU streaming conversion: the converter's tensor loop over the C-ABI pipeline.
+
+`ConversionPipeline` wraps libgguf_cuda_pipeline_* (csrc/pipeline.cu): a batch of host tensors is cut into
+row-range shards and streamed through every listed GPU with no GPU-to-GPU traffic.  `llama3_8b_plan` is the
+synthetic stand-in for the Llama-3-8B weight set of the conversion benchmark (shapes and the Q4_K_M-style
+type mix only; the values are generated, no checkpoint is involved).
+
+upstream counterpart: csrc/quantize_gguf.cpp:1990-2223 (write_tensor_payload) driven by the plan of
+:1235-1316; upstream runs it on GPU 0 with two pinned slots."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import GGMLQuantizationType, row_size
+from ._native import ShardDesc, TensorDesc, lib
+
+
+@dataclass
+class PlannedTensor:
+    name: str
+    rows: int
+    cols: int
+    qtype: int
+
+
+def llama3_8b_plan(n_layers: int = 32) -> list[PlannedTensor]:
+    """Tensor list of a Llama-3-8B-shaped model with the Q4_K_M mix: Q6_K for `output` and for `attn_v` and
+    `ffn_down` of every second layer, Q4_K elsewhere."""
+    q4, q6 = int(GGMLQuantizationType.Q4_K), int(GGMLQuantizationType.Q6_K)
+    plan = [PlannedTensor("token_embd", 128256, 4096, q4)]
+    for layer in range(n_layers):
+        more_bits = layer % 2 == 0
+        plan += [
+            PlannedTensor(f"blk.{layer}.attn_q", 4096, 4096, q4),
+            PlannedTensor(f"blk.{layer}.attn_k", 1024, 4096, q4),
+            PlannedTensor(f"blk.{layer}.attn_v", 1024, 4096, q6 if more_bits else q4),
+            PlannedTensor(f"blk.{layer}.attn_output", 4096, 4096, q4),
+            PlannedTensor(f"blk.{layer}.ffn_gate", 14336, 4096, q4),
+            PlannedTensor(f"blk.{layer}.ffn_up", 14336, 4096, q4),
+            PlannedTensor(f"blk.{layer}.ffn_down", 4096, 14336, q6 if more_bits else q4),
+        ]
+    plan.append(PlannedTensor("output", 128256, 4096, q6))
+    return plan
+
+
+class ConversionPipeline:
+    def __init__(self, devices: list[int], slots: int = 3, chunk_bytes: int = 128 << 20):
+        self.devices = list(devices)
+        arr = (ctypes.c_int * len(self.devices))(*self.devices)
+        self._handle = ctypes.c_void_p()
+        status = lib.libgguf_cuda_pipeline_create(arr, len(self.devices), slots, chunk_bytes, ctypes.byref(self._handle))
+        if status != 0:
+            raise RuntimeError(f"libgguf_cuda_pipeline_create failed with status {status}")
+
+    def close(self) -> None:
+        if self._handle:
+            lib.libgguf_cuda_pipeline_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    @staticmethod
+    def _descs(tensors):
+        keep = []
+        descs = (TensorDesc * len(tensors))()
+        for d, (qtype, src, imatrix, dst) in zip(descs, tensors):
+            if src.dtype != np.float32 or src.ndim != 2 or not src.flags.c_contiguous:
+                raise ValueError("src must be a C-contiguous 2-D float32 array")
+            if dst.dtype != np.uint8 or not dst.flags.c_contiguous or not dst.flags.writeable:
+                raise ValueError("dst must be a writable C-contiguous uint8 array")
+            rs = row_size(qtype, src.shape[1])
+            if rs == 0 or dst.size != src.shape[0] * rs:
+                raise ValueError("dst size does not match rows * row_size for this type")
+            im = None
+            if imatrix is not None:
+                im = np.ascontiguousarray(imatrix, dtype=np.float32)
+                if im.shape != (src.shape[1],):
+                    raise ValueError("imatrix length must match n_per_row")
+                keep.append(im)
+            d.qtype, d.src, d.imatrix, d.dst = int(qtype), src.ctypes.data, (im.ctypes.data if im is not None else None), dst.ctypes.data
+            d.rows, d.n_per_row = src.shape
+        return descs, keep
+
+    def quantize(self, tensors) -> None:
+        """tensors: list of (qtype, src float32 [rows, n], imatrix or None, dst uint8 [rows * row_size])."""
+        descs, keep = self._descs(tensors)
+        status = lib.libgguf_cuda_pipeline_quantize(self._handle, descs, len(tensors))
+        if status != 0:
+            raise RuntimeError(f"pipeline failed (status {status}): {lib.libgguf_cuda_pipeline_last_error(self._handle).decode()}")
+
+    def inject_failure(self, device_slot: int, after_shards: int) -> None:
+        if lib.libgguf_cuda_pipeline_inject_failure(self._handle, device_slot, after_shards) != 0:
+            raise ValueError("bad device slot")
+
+    def stats(self) -> dict:
+        n = len(self.devices)
+        shards = (ctypes.c_int64 * n)()
+        secs = (ctypes.c_double * n)()
+        requeued = ctypes.c_int64()
+        lib.libgguf_cuda_pipeline_stats(self._handle, shards, secs, ctypes.byref(requeued))
+        return {"shards_per_device": list(shards), "seconds_per_device": list(secs), "requeued": requeued.value}
+
+
+def plan_shards(tensors: list[tuple[int, int, int]], chunk_bytes: int = 128 << 20) -> list[tuple[int, int, int]]:
+    """Shard list for tensors given as (qtype, rows, n_per_row); needs no GPU.  Returns (tensor, row0, rows)."""
+    descs = (TensorDesc * len(tensors))()
+    for d, (qtype, rows, n) in zip(descs, tensors):
+        d.qtype, d.rows, d.n_per_row = int(qtype), rows, n
+    count = lib.libgguf_cuda_pipeline_plan(descs, len(tensors), chunk_bytes, None, 0)
+    if count < 0:
+        raise ValueError("bad tensor descriptor")
+    out = (ShardDesc * count)()
+    lib.libgguf_cuda_pipeline_plan(descs, len(tensors), chunk_bytes, out, count)
+    return [(s.tensor, s.row0, s.rows) for s in out]

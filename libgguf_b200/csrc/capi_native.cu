@@ -97,6 +97,8 @@ int run_quantize(libgguf_cuda_context *ctx, const float *device_input, const flo
         return fail(ctx, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "invalid quantize arguments");
     if (qtype < 0 || qtype >= GGML_TYPE_COUNT || !quantize_supported((int)qtype))
         return fail(ctx, LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE, "unsupported CUDA quantization type");
+    if (reinterpret_cast<uintptr_t>(device_input) & 15)
+        return fail(ctx, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "device_input must be 16-byte aligned");
     const int64_t block = block_geom((int)qtype).elems;
     if (n_per_row % block != 0)
         return fail(ctx, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "row width is not divisible by quantization block size");
@@ -354,6 +356,8 @@ int libgguf_cuda_quantize_weighted_rows_static(const float *device_input, const 
                     "the allocation-free entry point covers the importance-weighted Q4_0, Q4_1, Q5_0 and Q5_1 quantizers only");
     if (n_per_row % 32 != 0)
         return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "row width is not divisible by quantization block size");
+    if (reinterpret_cast<uintptr_t>(device_input) & 15)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "device_input must be 16-byte aligned");
     if (rows > static_scratch_max_rows())
         return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT,
                     "too many rows for the built-in scratch array (limit 65536 rows per call): split the call by rows");
