@@ -182,7 +182,7 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
     out_bytes = sum(o.numel() for o in outs)
     times = []
     with ConversionPipeline(list(range(ndev)), slots=3, chunk_bytes=128 << 20) as pipe:
-        for it in range(1 + max(1, min(args.steps, 3))):
+        for it in range(1 + max(1, min(args.steps, 8))):
             t0 = time.perf_counter()
             pipe.quantize(batch)
             times.append(time.perf_counter() - t0)

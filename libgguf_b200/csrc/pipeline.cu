@@ -75,6 +75,9 @@ struct libgguf_cuda_pipeline {
     std::vector<int64_t> shards_done;
     std::vector<double> busy_seconds;
     int64_t requeued = 0;
+    // per worker: its slots (streams, events, device and pinned buffers), created on first use and kept
+    // until the pipeline is destroyed so that consecutive batches pay no allocation or stream set-up
+    std::vector<std::vector<Slot>> worker_slots;
 };
 
 namespace {
@@ -144,13 +147,16 @@ bool wait_slot(Slot &s, int timeout_ms, std::string &err) {
 
 void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
     const int dev = pipe->devices[widx];
-    std::vector<Slot> slots(pipe->slots);
+    std::vector<Slot> &slots = pipe->worker_slots[widx];
     std::string err;
     bool ok = cudaSetDevice(dev) == cudaSuccess;
-    for (Slot &s : slots) {
-        if (!ok) break;
-        ok = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
-             cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming) == cudaSuccess;
+    if (ok && slots.empty()) {
+        slots.resize(pipe->slots);
+        for (Slot &s : slots) {
+            if (!ok) break;
+            ok = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming) == cudaSuccess;
+        }
     }
     if (!ok) err = "failed to set up streams on device " + std::to_string(dev);
     const auto t_begin = std::chrono::steady_clock::now();
@@ -242,10 +248,9 @@ void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
         batch->worker_failed[widx] = 1;
     }
     for (Slot &s : slots) {
-        if (s.stream) { cudaStreamSynchronize(s.stream); cudaStreamDestroy(s.stream); }
-        if (s.done) cudaEventDestroy(s.done);
-        cudaFree(s.d_in); cudaFree(s.d_out); cudaFree(s.d_imatrix);
-        cudaFreeHost(s.h_in); cudaFreeHost(s.h_out);
+        if (s.stream) cudaStreamSynchronize(s.stream);
+        s.busy = false;
+        s.copy_out_to = nullptr;
     }
     cudaGetLastError();
     pipe->busy_seconds[widx] = std::chrono::duration<double>(std::chrono::steady_clock::now() - t_begin).count();
@@ -267,11 +272,25 @@ int libgguf_cuda_pipeline_create(const int *devices, int n_devices, int slots, s
     p->fail_after.assign(n_devices, -1);
     p->shards_done.assign(n_devices, 0);
     p->busy_seconds.assign(n_devices, 0.0);
+    p->worker_slots.resize(n_devices);
     *out = p;
     return LIBGGUF_CUDA_STATUS_SUCCESS;
 }
 
-void libgguf_cuda_pipeline_destroy(libgguf_cuda_pipeline *pipe) { delete pipe; }
+void libgguf_cuda_pipeline_destroy(libgguf_cuda_pipeline *pipe) {
+    if (!pipe) return;
+    for (size_t w = 0; w < pipe->worker_slots.size(); ++w) {
+        if (pipe->worker_slots[w].empty() || cudaSetDevice(pipe->devices[w]) != cudaSuccess) continue;
+        for (Slot &s : pipe->worker_slots[w]) {
+            if (s.stream) { cudaStreamSynchronize(s.stream); cudaStreamDestroy(s.stream); }
+            if (s.done) cudaEventDestroy(s.done);
+            cudaFree(s.d_in); cudaFree(s.d_out); cudaFree(s.d_imatrix);
+            cudaFreeHost(s.h_in); cudaFreeHost(s.h_out);
+        }
+    }
+    cudaGetLastError();
+    delete pipe;
+}
 
 const char *libgguf_cuda_pipeline_last_error(const libgguf_cuda_pipeline *pipe) {
     return pipe ? pipe->last_error.c_str() : "libgguf CUDA pipeline is null";
