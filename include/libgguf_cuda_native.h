@@ -120,6 +120,12 @@ LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
  * device, and waits for the upload.  Optional: the row functions do it on first use. */
 LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
 
+/* Self-test, no upstream counterpart: the MXFP4 / NVFP4 quantizers pick each element's level by threshold
+ * comparisons instead of upstream's 16-way scan (libgguf_common.h:321-335).  This runs both on every one of the
+ * 2^32 float bit patterns at block scale `scale` on the current device (about a second) and stores how many
+ * inputs disagree (the quantizers rely on it being 0).  Blocking. */
+LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches);
+
 /* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,
  * csrc/quantize_gguf.cpp:1732-1931 and :2072-2146; the pool itself has no upstream counterpart) ----
  * A batch of tensors (host memory, fp32 rows in, encoded rows out) is cut into shards of whole rows of at most

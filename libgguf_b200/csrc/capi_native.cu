@@ -32,6 +32,7 @@ struct libgguf_cuda_event {
 using namespace gguf;
 
 namespace gguf {
+cudaError_t selftest_fp4(float e, unsigned long long *device_counter, cudaStream_t stream);
 int64_t static_scratch_max_rows();
 cudaError_t launch_quantize_legacy_weighted_static(int type, const float *src, const float *qw, void *dst, int64_t nrows,
                                                    int64_t n_per_row, cudaStream_t stream);
@@ -365,6 +366,21 @@ int libgguf_cuda_quantize_weighted_rows_static(const float *device_input, const 
     const cudaError_t error = launch_quantize_legacy_weighted_static((int)qtype, device_input, device_imatrix, device_output, rows,
                                                                      n_per_row, reinterpret_cast<cudaStream_t>(stream));
     if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    return ok(nullptr);
+}
+
+int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches) {
+    if (!mismatches) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "mismatches must not be null");
+    unsigned long long *counter = nullptr;
+    cudaError_t error = cudaMalloc((void **)&counter, sizeof(unsigned long long));
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    error = cudaMemset(counter, 0, sizeof(unsigned long long));
+    if (error == cudaSuccess) error = selftest_fp4(scale, counter, nullptr);
+    unsigned long long host = 0;
+    if (error == cudaSuccess) error = cudaMemcpy(&host, counter, sizeof(host), cudaMemcpyDeviceToHost);
+    cudaFree(counter);
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    *mismatches = host;
     return ok(nullptr);
 }
 

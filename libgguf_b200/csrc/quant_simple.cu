@@ -7,6 +7,7 @@
 // shuffles inside the 8-lane group; the one place where the upstream loop is order sensitive --
 // "first element with the largest magnitude" in Q4_0 / Q5_0 -- is reduced on (|v|, index) pairs.
 // Each CTA assembles its encoded blocks in shared memory and writes them out as 16-byte vectors.
+#include <float.h>
 #include <math.h>
 
 #include "gguf_common.cuh"
@@ -20,49 +21,9 @@ namespace {
 constexpr int kThreads = 256;
 constexpr unsigned kFull = 0xffffffffu;
 
-// max over the 8 lanes of a block group
-GGUF_D float group8_max(float v) {
-    v = fmaxf(v, __shfl_xor_sync(kFull, v, 1));
-    v = fmaxf(v, __shfl_xor_sync(kFull, v, 2));
-    v = fmaxf(v, __shfl_xor_sync(kFull, v, 4));
-    return v;
-}
-GGUF_D float group8_min(float v) {
-    v = fminf(v, __shfl_xor_sync(kFull, v, 1));
-    v = fminf(v, __shfl_xor_sync(kFull, v, 2));
-    v = fminf(v, __shfl_xor_sync(kFull, v, 4));
-    return v;
-}
-GGUF_D uint32_t group8_or(uint32_t v) {
-    v |= __shfl_xor_sync(kFull, v, 1);
-    v |= __shfl_xor_sync(kFull, v, 2);
-    v |= __shfl_xor_sync(kFull, v, 4);
-    return v;
-}
-
-// Signed value of the first element (lowest index) with the largest magnitude in the 32-element
-// block spread over 8 lanes x 4 elements (upstream q4_0.cpp:27-38, q5_0.cpp:29-40).
-GGUF_D float group8_first_absmax(const float (&x)[4], int lane8) {
-    float amax = 0.0f, vmax = 0.0f;
-    int idx = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float a = fabsf(x[i]);
-        if (amax < a) { amax = a; vmax = x[i]; idx = lane8 * 4 + i; }
-    }
-#pragma unroll
-    for (int m = 1; m < 8; m <<= 1) {
-        const float oa = __shfl_xor_sync(kFull, amax, m);
-        const float ov = __shfl_xor_sync(kFull, vmax, m);
-        const int oi = __shfl_xor_sync(kFull, idx, m);
-        if (oa > amax || (oa == amax && oi < idx)) { amax = oa; vmax = ov; idx = oi; }
-    }
-    return vmax;
-}
-
 // The 16-way nearest-level scan of the FP4 formats (upstream libgguf_common.h:321-335):
 // first index with the smallest |level*e - x|.
-GGUF_D int best_index_fp4(float x, float e) {
+GGUF_D int best_index_fp4_scan(float x, float e) {
     int best = 0;
     float best_err = fabsf((float)k_fp4_values[0] * e - x);
 #pragma unroll
@@ -73,125 +34,192 @@ GGUF_D int best_index_fp4(float x, float e) {
     return best;
 }
 
-enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4 };
+// Same result as the scan, by thresholds.  The levels are +-{0,1,2,3,4,6,8,12}*e; level*e is exact
+// (e has at most 4 significant bits), and for the two levels adjacent to |x| the differences the
+// scan compares are exact too (Sterbenz), so the scan's winner is the true nearest magnitude with
+// ties going to the smaller one (it comes first in scan order, for both signs), i.e. the number
+// of midpoints {0.5,1.5,2.5,3.5,5,7,10}*e strictly below |x|.  Farther levels cannot tie with the
+// nearest while |x| < 2^20*e (their distance exceeds the nearest's by at least e, far above the
+// rounding of the subtraction); beyond that, for e == 0 and for NaN the scan itself is used.
+// Checked against the scan over all 2^32 inputs for a set of scales by libgguf_cuda_selftest_fp4.
+GGUF_D bool fp4_thresholds_valid(float amax, float e) { return amax <= e * 1048576.f && e != 0.f; }  // false for NaN too
+GGUF_D int best_index_fp4_thresholds(float x, float e) {
+    const float m = fabsf(x);
+    int idx = (m > 0.5f * e) + (m > 1.5f * e) + (m > 2.5f * e) + (m > 3.5f * e) + (m > 5.f * e) + (m > 7.f * e) + (m > 10.f * e);
+    if (x < 0.f && idx > 0) idx += 8;
+    return idx;
+}
+GGUF_D int best_index_fp4(float x, float e) {
+    return fp4_thresholds_valid(fabsf(x), e) ? best_index_fp4_thresholds(x, e) : best_index_fp4_scan(x, e);
+}
+
+// Packs the levels of N elements (element j low nibble, element j + N/2 high nibble of byte j).  The
+// threshold form is valid for the whole group when it is valid for the group's largest magnitude; the
+// scan runs as a rolled loop so that its code exists once per kernel.
+template <int N>
+GGUF_D void pack_fp4(const float *x, float amax, float e, uint8_t *out) {
+    if (fp4_thresholds_valid(amax, e)) {
+#pragma unroll
+        for (int j = 0; j < N / 2; ++j)
+            out[j] = (uint8_t)(best_index_fp4_thresholds(x[j], e) | (best_index_fp4_thresholds(x[j + N / 2], e) << 4));
+    } else {
+        // x is a register array: select by comparison instead of indexing it dynamically
+#pragma unroll 1
+        for (int j = 0; j < N / 2; ++j) {
+            float lo = 0.f, hi = 0.f;
+#pragma unroll
+            for (int k = 0; k < N / 2; ++k) {
+                if (k == j) { lo = x[k]; hi = x[k + N / 2]; }
+            }
+            out[j] = (uint8_t)(best_index_fp4_scan(lo, e) | (best_index_fp4_scan(hi, e) << 4));
+        }
+    }
+}
+
+__global__ void selftest_fp4_kernel(float e, unsigned long long *mismatches) {
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    unsigned long long bad = 0;
+    for (uint64_t bits = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; bits < (1ull << 32); bits += stride) {
+        const float x = __uint_as_float((uint32_t)bits);
+        if (best_index_fp4(x, e) != best_index_fp4_scan(x, e)) ++bad;
+    }
+    if (bad) atomicAdd(mismatches, bad);
+}
+
+enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4, NVFP4 };
 
 template <Simple K> struct SimpleGeom;
-template <> struct SimpleGeom<Simple::Q8_0> { static constexpr int BYTES = 34; };
+template <> struct SimpleGeom<Simple::Q8_0> { static constexpr int BYTES = 34; };   // bytes per 32 elements
 template <> struct SimpleGeom<Simple::Q4_0> { static constexpr int BYTES = 18; };
 template <> struct SimpleGeom<Simple::Q4_1> { static constexpr int BYTES = 20; };
 template <> struct SimpleGeom<Simple::Q5_0> { static constexpr int BYTES = 22; };
 template <> struct SimpleGeom<Simple::Q5_1> { static constexpr int BYTES = 24; };
 template <> struct SimpleGeom<Simple::MXFP4> { static constexpr int BYTES = 17; };
-
-// Nibble pair packing: element j (lanes 0..3 of the group) shares a byte with element j+16
-// (lanes 4..7).  Lanes 0..3 write 4 bytes each.
-GGUF_D void pack_nibbles(uint8_t *qs, const int (&q)[4], int lane8, bool write) {
-    int partner[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) partner[i] = __shfl_xor_sync(kFull, q[i], 4);
-    if (write && lane8 < 4) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) qs[lane8 * 4 + i] = (uint8_t)((q[i] & 0xF) | ((partner[i] & 0xF) << 4));
-    }
-}
-
-GGUF_D uint32_t fifth_bits(const int (&q)[4], int lane8) {
-    uint32_t bits = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) bits |= (uint32_t)((q[i] >> 4) & 1) << (lane8 * 4 + i);
-    return group8_or(bits);
-}
+template <> struct SimpleGeom<Simple::NVFP4> { static constexpr int BYTES = 18; };  // half of a 64-element block
 
 GGUF_D void st16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }
 GGUF_D void st32(uint8_t *p, uint32_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); p[2] = (uint8_t)(v >> 16); p[3] = (uint8_t)(v >> 24); }
 
+// (int8_t)(float) as the x86 build of upstream does it: truncation to int32 with out-of-range
+// values and NaN giving INT_MIN, then the low byte.
+GGUF_D int trunc_to_i8(float v) {
+    const int i = fabsf(v) < 2147483648.f ? __float2int_rz(v) : (int)0x80000000;
+    return (int)(int8_t)(i & 0xFF);
+}
+
+// roundf (halves away from zero) for |v| < 2^23 without the library call
+GGUF_D int round_half_away(float v) {
+    const float t = truncf(v);
+    const float frac = v - t;  // exact
+    return (int)t + (frac >= 0.5f ? 1 : 0) - (frac <= -0.5f ? 1 : 0);
+}
+
+constexpr int kBlockThreads = 128;   // one thread per 32 elements
+constexpr int kRowStride = 36;       // floats per staged 32-element run: 16-byte aligned rows, conflict-free LDS.128
+
+// 32-element types (and NVFP4 as two 16-element sub-blocks per thread).  The CTA stages
+// 128 x 32 floats in shared memory with coalesced 16-byte loads; then every thread encodes its own
+// 32 elements from registers, serially and in upstream's element order (so "first element with
+// the largest magnitude" and the like need no cross-lane exchange); the encoded tile is written
+// out as 16-byte vectors.
 // `mx_steps` : for MXFP4, table of the smallest float in each binade [2^t, 2^(t+1)), t = -149..127,
 // for which the host libm's floorf(log2f(x)) already returns t+1 (+inf bits if it never does).
 template <Simple K>
-__global__ void __launch_bounds__(kThreads) quant32_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
-                                                          int64_t nblocks, const float *__restrict__ mx_steps) {
+__global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
+                                                               int64_t nruns, const float *__restrict__ mx_steps) {
     constexpr int BYTES = SimpleGeom<K>::BYTES;
-    constexpr int BLOCKS_PER_ITER = kThreads / 8;  // 32
-    constexpr int ITERS = 4;
-    constexpr int TILE_BLOCKS = BLOCKS_PER_ITER * ITERS;  // 128 blocks = 4096 elements per CTA
-    __shared__ __align__(16) uint8_t stage[TILE_BLOCKS * BYTES + 32];
+    __shared__ __align__(16) float xin[kBlockThreads * kRowStride];
+    __shared__ __align__(16) uint8_t stage[kBlockThreads * BYTES + 32];
 
-    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
-    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
-    uint8_t *gdst = dst + b0 * BYTES;
+    const int64_t r0 = (int64_t)blockIdx.x * kBlockThreads;
+    const int nr = (int)(nruns - r0 < kBlockThreads ? nruns - r0 : kBlockThreads);
+    uint8_t *gdst = dst + r0 * BYTES;
     uint8_t *tile = stage + (reinterpret_cast<uintptr_t>(gdst) & 15);
-    const int lane8 = threadIdx.x & 7;
-
-    float x[ITERS][4];
+    const float4 *g4 = reinterpret_cast<const float4 *>(src + r0 * 32);
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int blk = it * BLOCKS_PER_ITER + (threadIdx.x >> 3);
-        if (blk < nb) {
-            const float4 v = __ldcs(reinterpret_cast<const float4 *>(src + (b0 + blk) * 32) + lane8);
-            x[it][0] = v.x; x[it][1] = v.y; x[it][2] = v.z; x[it][3] = v.w;
-        } else {
-            x[it][0] = x[it][1] = x[it][2] = x[it][3] = 0.0f;
-        }
+    for (int k = 0; k < 8; ++k) {
+        const int i = k * kBlockThreads + threadIdx.x;  // float4 index inside the tile
+        if (i < nr * 8) *reinterpret_cast<float4 *>(xin + (i >> 3) * kRowStride + (i & 7) * 4) = __ldcs(g4 + i);
     }
-
+    __syncthreads();
+    if (threadIdx.x < nr) {
+        float x[32];
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int blk = it * BLOCKS_PER_ITER + (threadIdx.x >> 3);
-        uint8_t *out = tile + blk * BYTES;
-        const float(&v)[4] = x[it];
-        int q[4];
+        for (int k = 0; k < 8; ++k) {
+            const float4 v = *reinterpret_cast<const float4 *>(xin + threadIdx.x * kRowStride + 4 * k);
+            x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+        }
+        uint8_t *out = tile + threadIdx.x * BYTES;
         if constexpr (K == Simple::Q8_0) {
             // upstream q8_0.cpp:16-43
-            const float amax = group8_max(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+            float amax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
             const float d = amax / 127.0f;
             const float id = d ? 1.0f / d : 0.0f;
-            if (blk < nb) {
-                if (lane8 == 0) st16(out, f32_to_half_bits(d));
+            st16(out, f32_to_half_bits(d));
 #pragma unroll
-                for (int i = 0; i < 4; ++i) out[2 + lane8 * 4 + i] = (uint8_t)(int8_t)(int)roundf(v[i] * id);
+            for (int j = 0; j < 32; ++j) out[2 + j] = (uint8_t)(int8_t)round_half_away(x[j] * id);
+        } else if constexpr (K == Simple::Q4_0 || K == Simple::Q5_0) {
+            // upstream q4_0.cpp:16-58, q5_0.cpp:18-65
+            constexpr bool FIVE = K == Simple::Q5_0;
+            float amax = 0.0f, vmax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (amax < fabsf(x[j])) { amax = fabsf(x[j]); vmax = x[j]; }
             }
-        } else if constexpr (K == Simple::Q4_0) {
-            // upstream q4_0.cpp:16-58
-            const float vmax = group8_first_absmax(v, lane8);
-            const float d = vmax / -8.0f;
+            const float d = vmax / (FIVE ? -16.0f : -8.0f);
             const float id = d ? 1.0f / d : 0.0f;
+            st16(out, f32_to_half_bits(d));
+            uint32_t qh = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = imin(15, cast_f32_to_i8_x86(v[i] * id + 8.5f)) & 0xFF;
-            if (blk < nb && lane8 == 0) st16(out, f32_to_half_bits(d));
-            pack_nibbles(out + 2, q, lane8, blk < nb);
-        } else if constexpr (K == Simple::Q4_1) {
-            // upstream q4_1.cpp:16-57
-            const float mn = group8_min(fminf(fminf(v[0], v[1]), fminf(v[2], v[3])));
-            const float mx = group8_max(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
-            const float d = (mx - mn) / 15.0f;
+            for (int j = 0; j < 16; ++j) {
+                const int q0 = imin(FIVE ? 31 : 15, trunc_to_i8(x[j] * id + (FIVE ? 16.5f : 8.5f))) & 0xFF;
+                const int q1 = imin(FIVE ? 31 : 15, trunc_to_i8(x[j + 16] * id + (FIVE ? 16.5f : 8.5f))) & 0xFF;
+                if (FIVE) {
+                    out[6 + j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
+                    qh |= (uint32_t)((q0 & 0x10) >> 4) << j;
+                    qh |= (uint32_t)((q1 & 0x10) >> 4) << (j + 16);
+                } else {
+                    out[2 + j] = (uint8_t)(q0 | (q1 << 4));
+                }
+            }
+            if (FIVE) st32(out + 2, qh);
+        } else if constexpr (K == Simple::Q4_1 || K == Simple::Q5_1) {
+            // upstream q4_1.cpp:16-57, q5_1.cpp:18-68
+            constexpr bool FIVE = K == Simple::Q5_1;
+            float mn = FLT_MAX, mx = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (x[j] < mn) mn = x[j];
+                if (x[j] > mx) mx = x[j];
+            }
+            const float d = (mx - mn) / (FIVE ? 31.0f : 15.0f);
             const float id = d ? 1.0f / d : 0.0f;
+            st16(out, f32_to_half_bits(d));
+            st16(out + 2, f32_to_half_bits(mn));
+            uint32_t qh = 0;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = imin(15, cast_f32_to_i8_x86((v[i] - mn) * id + 0.5f)) & 0xFF;
-            if (blk < nb && lane8 == 0) { st16(out, f32_to_half_bits(d)); st16(out + 2, f32_to_half_bits(mn)); }
-            pack_nibbles(out + 4, q, lane8, blk < nb);
-        } else if constexpr (K == Simple::Q5_0) {
-            // upstream q5_0.cpp:18-65
-            const float vmax = group8_first_absmax(v, lane8);
-            const float d = vmax / -16.0f;
-            const float id = d ? 1.0f / d : 0.0f;
+            for (int j = 0; j < 16; ++j) {
+                const float t0 = (x[j] - mn) * id + 0.5f, t1 = (x[j + 16] - mn) * id + 0.5f;
+                if (FIVE) {
+                    // (uint8_t)(float): truncation through int32, low byte
+                    const int q0 = (fabsf(t0) < 2147483648.f ? __float2int_rz(t0) : (int)0x80000000) & 0xFF;
+                    const int q1 = (fabsf(t1) < 2147483648.f ? __float2int_rz(t1) : (int)0x80000000) & 0xFF;
+                    out[8 + j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
+                    qh |= (uint32_t)((q0 & 0x10) >> 4) << j;
+                    qh |= (uint32_t)((q1 & 0x10) >> 4) << (j + 16);
+                } else {
+                    const int q0 = imin(15, trunc_to_i8(t0)) & 0xFF, q1 = imin(15, trunc_to_i8(t1)) & 0xFF;
+                    out[4 + j] = (uint8_t)(q0 | (q1 << 4));
+                }
+            }
+            if (FIVE) st32(out + 4, qh);
+        } else if constexpr (K == Simple::MXFP4) {
+            // upstream mxfp4.cpp:17-54
+            float amax = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = imin(31, cast_f32_to_i8_x86(v[i] * id + 16.5f)) & 0xFF;
-            const uint32_t qh = fifth_bits(q, lane8);
-            if (blk < nb && lane8 == 0) { st16(out, f32_to_half_bits(d)); st32(out + 2, qh); }
-            pack_nibbles(out + 6, q, lane8, blk < nb);
-        } else if constexpr (K == Simple::Q5_1) {
-            // upstream q5_1.cpp:18-68.  (uint8_t)(float) truncates; the operand is in [0.5, 31.5].
-            const float mn = group8_min(fminf(fminf(v[0], v[1]), fminf(v[2], v[3])));
-            const float mx = group8_max(fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3])));
-            const float d = (mx - mn) / 31.0f;
-            const float id = d ? 1.0f / d : 0.0f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = (int)(uint8_t)(int)((v[i] - mn) * id + 0.5f);
-            const uint32_t qh = fifth_bits(q, lane8);
-            if (blk < nb && lane8 == 0) { st16(out, f32_to_half_bits(d)); st16(out + 2, f32_to_half_bits(mn)); st32(out + 4, qh); }
-            pack_nibbles(out + 8, q, lane8, blk < nb);
-        } else {  // MXFP4, upstream mxfp4.cpp:17-54
-            const float amax = group8_max(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
+            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
             int e = 0;
             if (amax > 0.0f) {
                 // floorf(log2f(amax)) as the host libm computes it: true binade t, plus one when
@@ -204,60 +232,39 @@ __global__ void __launch_bounds__(kThreads) quant32_kernel(const float *__restri
                 e = bexp == 255 ? 0 : (fl - 2 + 127) & 0xFF;
             }
             const float d = e8m0_half_to_f32((uint8_t)e);
+            out[0] = (uint8_t)e;
+            pack_fp4<32>(x, amax, d, out + 1);
+        } else {
+            // NVFP4, upstream nvfp4.cpp:16-55: this thread's 32 elements are sub-blocks 2h and 2h+1 of
+            // a 64-element block; its 18 staged bytes are 2 scale bytes followed by 16 quant bytes.
 #pragma unroll
-            for (int i = 0; i < 4; ++i) q[i] = best_index_fp4(v[i], d);
-            if (blk < nb && lane8 == 0) out[0] = (uint8_t)e;
-            pack_nibbles(out + 1, q, lane8, blk < nb);
-        }
-    }
-    __syncthreads();
-    flush_tile(tile, gdst, nb * BYTES, threadIdx.x, kThreads);
-}
-
-// NVFP4: 64-element blocks, four 16-element sub-blocks each with a UE4M3 scale
-// (upstream nvfp4.cpp:16-55).  4 lanes per sub-block, 16 lanes per block, 2 blocks per warp.
-__global__ void __launch_bounds__(kThreads) quant_nvfp4_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
-                                                              int64_t nblocks) {
-    constexpr int BYTES = 36;
-    constexpr int BLOCKS_PER_ITER = kThreads / 16;  // 16
-    constexpr int ITERS = 4;
-    constexpr int TILE_BLOCKS = BLOCKS_PER_ITER * ITERS;  // 64 blocks = 4096 elements
-    __shared__ __align__(16) uint8_t stage[TILE_BLOCKS * BYTES + 32];
-    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
-    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
-    uint8_t *gdst = dst + b0 * BYTES;
-    uint8_t *tile = stage + (reinterpret_cast<uintptr_t>(gdst) & 15);
-    const int lane16 = threadIdx.x & 15, sub = lane16 >> 2, lane4 = lane16 & 3;
+            for (int sb = 0; sb < 2; ++sb) {
+                float amax = 0.0f;
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int blk = it * BLOCKS_PER_ITER + (threadIdx.x >> 4);
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (blk < nb) {
-            const float4 t = __ldcs(reinterpret_cast<const float4 *>(src + (b0 + blk) * 64) + lane16);
-            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-        }
-        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-        amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, 2));
-        const uint8_t ue = f32_to_ue4m3(amax / 6.0f);
-        const float d = ue4m3_half_to_f32(ue);
-        int q[4], partner[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) q[i] = best_index_fp4(v[i], d);
-        // element j (lanes 0,1 of the sub-block) pairs with element j+8 (lanes 2,3)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) partner[i] = __shfl_xor_sync(kFull, q[i], 2);
-        if (blk < nb) {
-            uint8_t *out = tile + blk * BYTES;
-            if (lane4 == 0) out[sub] = ue;
-            if (lane4 < 2) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) out[4 + sub * 8 + lane4 * 4 + i] = (uint8_t)(q[i] | (partner[i] << 4));
+                for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(x[16 * sb + j]));
+                const uint8_t ue = f32_to_ue4m3(amax / 6.0f);
+                const float d = ue4m3_half_to_f32(ue);
+                out[sb] = ue;
+                pack_fp4<16>(x + 16 * sb, amax, d, out + 2 + 8 * sb);
             }
         }
     }
     __syncthreads();
-    flush_tile(tile, gdst, nb * BYTES, threadIdx.x, kThreads);
+    if constexpr (K == Simple::NVFP4) {
+        // un-interleave: block b = runs 2b, 2b+1 -> d[0..1] d[2..3] qs[0..15] qs[16..31]
+        __shared__ __align__(16) uint8_t shuffled[kBlockThreads * BYTES + 32];
+        uint8_t *tile2 = shuffled + (reinterpret_cast<uintptr_t>(gdst) & 15);
+        for (int i = threadIdx.x; i < nr * BYTES; i += kBlockThreads) {
+            const int run = i / BYTES, o = i - run * BYTES;
+            const int blk = run >> 1, h = run & 1;
+            const int pos = o < 2 ? 2 * h + o : 4 + 16 * h + (o - 2);
+            tile2[blk * 36 + pos] = tile[i];
+        }
+        __syncthreads();
+        flush_tile(tile2, gdst, nr * BYTES, threadIdx.x, kBlockThreads);
+    } else {
+        flush_tile(tile, gdst, nr * BYTES, threadIdx.x, kBlockThreads);
+    }
 }
 
 // Q1_0: 128-element blocks, d = mean |x| with the sum taken in element order, one sign bit per
@@ -364,10 +371,11 @@ __global__ void __launch_bounds__(kThreads) store_kernel(const float *__restrict
 
 template <Simple K>
 cudaError_t launch32(const float *src, void *dst, int64_t nelems, const float *mx_steps, cudaStream_t stream) {
-    const int64_t nblocks = nelems / 32;
-    const int64_t grid = (nblocks + 127) / 128;
+    const int64_t nruns = nelems / 32;
+    const int64_t grid = (nruns + kBlockThreads - 1) / kBlockThreads;
     if (grid <= 0) return cudaSuccess;
-    quant32_kernel<K><<<(unsigned)grid, kThreads, 0, stream>>>(src, static_cast<uint8_t *>(dst), nblocks, mx_steps);
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    quant32_kernel<K><<<(unsigned)grid, kBlockThreads, 0, stream>>>(src, static_cast<uint8_t *>(dst), nruns, mx_steps);
     count_launch();
     return cudaGetLastError();
 }
@@ -388,6 +396,14 @@ cudaError_t launch_store(int type, const float *src, void *dst, int64_t nelems, 
     return cudaGetLastError();
 }
 
+// Counts the inputs (all 2^32 float bit patterns) for which the threshold form of the FP4 level
+// search differs from the 16-way scan at scale e.
+cudaError_t selftest_fp4(float e, unsigned long long *device_counter, cudaStream_t stream) {
+    selftest_fp4_kernel<<<148 * 8, 256, 0, stream>>>(e, device_counter);
+    count_launch();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_quantize_simple(int type, const float *src, void *dst, int64_t nelems, const float *mx_steps,
                                    cudaStream_t stream) {
     uint8_t *out = static_cast<uint8_t *>(dst);
@@ -398,13 +414,7 @@ cudaError_t launch_quantize_simple(int type, const float *src, void *dst, int64_
         case GGML_TYPE_Q5_0: return launch32<Simple::Q5_0>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_Q5_1: return launch32<Simple::Q5_1>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_MXFP4: return launch32<Simple::MXFP4>(src, dst, nelems, mx_steps, stream);
-        case GGML_TYPE_NVFP4: {
-            const int64_t nblocks = nelems / 64;
-            if (nblocks <= 0) return cudaSuccess;
-            quant_nvfp4_kernel<<<(unsigned)((nblocks + 63) / 64), kThreads, 0, stream>>>(src, out, nblocks);
-            count_launch();
-            return cudaGetLastError();
-        }
+        case GGML_TYPE_NVFP4: return launch32<Simple::NVFP4>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_Q1_0: {
             const int64_t nblocks = nelems / 128;
             if (nblocks <= 0) return cudaSuccess;

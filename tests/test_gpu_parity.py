@@ -164,3 +164,15 @@ def test_zero_rows_and_empty(gguf):
     out = gguf.quantize_rows(np.zeros((0, 256), np.float32), 12)
     assert out.shape == (0, 144)
     assert gguf.dequantize_rows(np.zeros((0, 144), np.uint8), 12).shape == (0, 256)
+
+
+def test_fp4_threshold_search_equals_the_scan_for_every_float():
+    """All 2^32 inputs at each scale: zero, the smallest and a mid E8M0 half-scale, UE4M3 scales with mantissa
+    bits (smallest subnormal, 1.875 * 2^-1, the largest), and a huge E8M0 scale."""
+    import ctypes
+    from libgguf_b200._native import lib
+    scales = [0.0, 2.0 ** -128, 2.0 ** -20, 0.5, 2.0 ** -10, 1.875 * 0.25, 224.0, 0.0068359375, 2.0 ** 100]
+    for e in scales:
+        bad = ctypes.c_uint64(123)
+        assert lib.libgguf_cuda_selftest_fp4(e, ctypes.byref(bad)) == 0
+        assert bad.value == 0, (e, bad.value)
