@@ -119,3 +119,45 @@ def plan_shards(tensors: list[tuple[int, int, int]], chunk_bytes: int = 128 << 2
     out = (ShardDesc * count)()
     lib.libgguf_cuda_pipeline_plan(descs, len(tensors), chunk_bytes, out, count)
     return [(s.tensor, s.row0, s.rows) for s in out]
+
+
+def assign_shards(shards: list[tuple[int, int, int]], widths: list[int], world: int) -> list[list[tuple[int, int, int]]]:
+    """Split a shard list over `world` processes (one per GPU) without any exchange: shards are taken in the given
+    (largest-first) order and each goes to the process with the fewest elements so far, lowest rank on ties.
+    Every process computes the same answer from the same plan, so no rank needs to talk to another.
+    `widths[t]` is n_per_row of tensor t."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    load = [0] * world
+    out: list[list[tuple[int, int, int]]] = [[] for _ in range(world)]
+    for shard in shards:
+        tensor, _, rows = shard
+        r = min(range(world), key=lambda i: (load[i], i))
+        out[r].append(shard)
+        load[r] += rows * widths[tensor]
+    return out
+
+
+def rank_batch(tensors, world: int, rank: int, chunk_bytes: int = 128 << 20):
+    """The slice of a conversion batch that process `rank` of `world` runs on its own GPU.
+    tensors: list of (qtype, src float32 [rows, n], imatrix or None, dst uint8 [rows * row_size]); the result has the
+    same form, with `src` and `dst` replaced by row-range views, and can be given to ConversionPipeline.quantize."""
+    shards = plan_shards([(q, s.shape[0], s.shape[1]) for q, s, _, _ in tensors], chunk_bytes)
+    mine = assign_shards(shards, [s.shape[1] for _, s, _, _ in tensors], world)[rank]
+    batch = []
+    for tensor, row0, rows in mine:
+        qtype, src, imatrix, dst = tensors[tensor]
+        rs = row_size(qtype, src.shape[1])
+        batch.append((qtype, src[row0:row0 + rows], imatrix, dst[row0 * rs:(row0 + rows) * rs]))
+    return batch
+
+
+def max_over_ranks(value: float, device=None) -> float:
+    """The slowest rank's `value` (a duration) when torch.distributed is initialised, else `value`."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return float(value)
+    t = torch.tensor([value], dtype=torch.float64, device=device if device is not None else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())

@@ -1071,12 +1071,426 @@ static void quant_iq4_superblock(int sbs, const float *x, uint8_t *y, const floa
 }
 
 /* ------------------------------------------------------------------------------------------- */
+/* IQ search tables.  upstream libgguf_iq_tables.cpp:36-417 (iq2xs_init_impl) and :487-666
+ * (iq3xs_init_impl): grid coordinates 2*code+1, lattice map, and for every lattice point that is
+ * not a codebook entry the codebook entries at the `nwant` smallest distinct squared distances,
+ * ordered by (distance, index). */
+typedef struct {
+    int grid_size, dims, bits;
+    uint8_t *grid;      /* grid_size * dims */
+    int *map;           /* map_size */
+    uint16_t *neighbours;
+} iq_table;
+
+static iq_table IQ_TABLES[6]; /* 0 2xxs, 1 2xs, 2 1s, 3 2s, 4 3xxs, 5 3s */
+
+static const iq_table *iq_table_get(int id) {
+    iq_table *t = &IQ_TABLES[id];
+    if (t->grid) return t;
+    static const uint16_t *const books[6] = {CB_IQ2XXS, CB_IQ2XS, CB_IQ1S, CB_IQ2S, CB_IQ3XXS, CB_IQ3S};
+    static const int sizes[6] = {256, 512, 2048, 1024, 256, 512};
+    static const int nwants[6] = {2, 2, 3, 1, 2, 3};
+    const int dims = id < 4 ? 8 : 4, bits = id < 4 ? 2 : 3, map_size = id < 4 ? 43692 : 4096, mask = (1 << bits) - 1;
+    const int gs = sizes[id], nwant = nwants[id];
+    t->grid_size = gs; t->dims = dims; t->bits = bits;
+    uint8_t *grid = (uint8_t *)malloc((size_t)gs * dims);
+    int *map = (int *)malloc(sizeof(int) * map_size);
+    for (int i = 0; i < map_size; ++i) map[i] = -1;
+    for (int g = 0; g < gs; ++g) {
+        for (int k = 0; k < dims; ++k) grid[g * dims + k] = (uint8_t)(2 * ((books[id][g] >> (bits * k)) & mask) + 1);
+        map[books[id][g]] = g;
+    }
+    int *d2 = (int *)malloc(sizeof(int) * gs);
+    size_t cap = 1 << 16, len = 0;
+    uint16_t *nb = (uint16_t *)malloc(cap * sizeof(uint16_t));
+    for (int i = 0; i < map_size; ++i) {
+        if (map[i] >= 0) continue;
+        int pos[8];
+        for (int k = 0; k < dims; ++k) pos[k] = 2 * ((i >> (bits * k)) & mask) + 1;
+        for (int g = 0; g < gs; ++g) {
+            int d = 0;
+            for (int k = 0; k < dims; ++k) d += (grid[g * dims + k] - pos[k]) * (grid[g * dims + k] - pos[k]);
+            d2[g] = d;
+        }
+        if (len + (size_t)gs + 1 > cap) { while (len + (size_t)gs + 1 > cap) cap *= 2; nb = (uint16_t *)realloc(nb, cap * sizeof(uint16_t)); }
+        map[i] = -((int)len + 1);
+        const size_t count_at = len++;
+        int have = 0, n = 0, last = -1;
+        while (have < nwant) { /* next smallest distinct distance, entries in index order */
+            int best = 1 << 30;
+            for (int g = 0; g < gs; ++g) if (d2[g] > last && d2[g] < best) best = d2[g];
+            if (best == 1 << 30) break;
+            for (int g = 0; g < gs; ++g) if (d2[g] == best) { nb[len++] = (uint16_t)g; ++n; }
+            last = best;
+            ++have;
+        }
+        nb[count_at] = (uint16_t)n;
+    }
+    free(d2);
+    t->map = map; t->neighbours = nb; t->grid = grid;
+    return t;
+}
+
+/* upstream libgguf_iq_tables.cpp:434-462 / :683-711 */
+static int iq_best_neighbour(const iq_table *t, const uint16_t *nb, const float *xval, const float *weight, float scale, int8_t *L) {
+    const int n = nb[0], D = t->dims;
+    float best_d2 = 3.402823466e+38f;
+    int best = -1;
+    for (int j = 1; j <= n; ++j) {
+        const uint8_t *pg = t->grid + nb[j] * D;
+        float d2 = 0;
+        for (int i = 0; i < D; ++i) { const float q = pg[i]; const float diff = scale * q - xval[i]; d2 += weight[i] * diff * diff; }
+        if (d2 < best_d2) { best_d2 = d2; best = nb[j]; }
+    }
+    const uint8_t *pg = t->grid + best * D;
+    for (int i = 0; i < D; ++i) L[i] = (int8_t)((pg[i] - 1) / 2);
+    return best;
+}
+
+/* upstream libgguf_iq_tables.cpp:714-781 (reachable part) */
+static int iq1_best_neighbour(const iq_table *t, const uint16_t *nb, const float *xval, const float *weight, float scale,
+                              const float *xg, int8_t *L) {
+    const int n = nb[0];
+    float best_score = 3.402823466e+38f;
+    int best = -1;
+    for (int j = 1; j <= n; ++j) {
+        const uint8_t *pg = t->grid + nb[j] * 8;
+        float d2 = 0;
+        for (int i = 0; i < 8; ++i) { const float q = xg[(pg[i] - 1) / 2]; const float diff = scale * q - xval[i]; d2 += weight[i] * diff * diff; }
+        if (d2 < best_score) { best_score = d2; best = nb[j]; }
+    }
+    const uint8_t *pg = t->grid + best * 8;
+    for (int i = 0; i < 8; ++i) L[i] = (int8_t)((pg[i] - 1) / 2);
+    return best;
+}
+
+/* One super-block of IQ2_XXS / IQ2_XS / IQ2_S / IQ3_XXS / IQ3_S.
+ * upstream iq2_xxs.cpp:4-224, iq2_xs.cpp:4-230, iq2_s.cpp:4-218, iq3_xxs.cpp:4-273, iq3_s.cpp:5-233. */
+static void quant_iq23_block(int type, const float *xbl, uint8_t *y, const float *qw_block) {
+    const int xxs2 = type == T_IQ2_XXS, xs2 = type == T_IQ2_XS, s2 = type == T_IQ2_S, xxs3 = type == T_IQ3_XXS, s3 = type == T_IQ3_S;
+    const int BS = (xs2 || s2) ? 16 : 32, GD = (xxs3 || s3) ? 4 : 8, BITS = GD == 8 ? 2 : 3, KMAXQ = GD == 8 ? 3 : 8;
+    const int NG = BS / GD, NS = BS / 8, NB = 256 / BS;
+    const int parity = xxs2 || xs2 || xxs3;
+    const int is_max = xxs2 ? 6 : xxs3 ? 15 : 9;
+    const float step = GD == 8 ? 0.1f : 0.2f;
+    const iq_table *t = iq_table_get(xxs2 ? 0 : xs2 ? 1 : s2 ? 3 : xxs3 ? 4 : 5);
+    int bytes, e_;
+    block_geometry(type, &e_, &bytes);
+    memset(y, 0, (size_t)bytes);
+    float scales[16];
+    float sumx2 = 0;
+    for (int i = 0; i < 256; ++i) sumx2 += xbl[i] * xbl[i];
+    const float sigma2 = (xxs2 || xs2) ? sumx2 / QK_K : 2 * sumx2 / QK_K;
+    float max_scale = 0;
+    int pos = 0; /* IQ3_S: payload slot, advanced only by blocks that are not skipped */
+    for (int ib = 0; ib < NB; ++ib) {
+        const float *xb = xbl + BS * ib;
+        float weight[32], waux[32], xval[32];
+        int8_t L[32], Laux[32];
+        uint8_t signs[4];
+        for (int i = 0; i < BS; ++i) {
+            if (qw_block) weight[i] = qw_block[BS * ib + i] * sqrtf(sigma2 + xb[i] * xb[i]);
+            else weight[i] = s2 ? 0.25f * sigma2 + xb[i] * xb[i] : xb[i] * xb[i];
+        }
+        for (int i = 0; i < BS; ++i) waux[i] = sqrtf(weight[i]);
+        for (int k = 0; k < NS; ++k) {
+            int nflip = 0;
+            uint8_t s = 0;
+            for (int i = 0; i < 8; ++i) {
+                if (xb[8 * k + i] >= 0) xval[8 * k + i] = xb[8 * k + i];
+                else { xval[8 * k + i] = -xb[8 * k + i]; ++nflip; s |= (uint8_t)(1 << i); }
+            }
+            if (parity) {
+                if (nflip % 2) {
+                    int imin = 0;
+                    float min = weight[8 * k] * xb[8 * k] * xb[8 * k];
+                    for (int i = 1; i < 8; ++i) { const float ax = weight[8 * k + i] * xb[8 * k + i] * xb[8 * k + i]; if (ax < min) { min = ax; imin = i; } }
+                    xval[8 * k + imin] = -xval[8 * k + imin];
+                    s ^= (uint8_t)(1 << imin);
+                }
+                s &= 127;
+            }
+            signs[k] = s;
+        }
+        float max = xval[0];
+        for (int i = 1; i < BS; ++i) max = max > xval[i] ? max : xval[i];
+        memset(L, 0, sizeof L);
+        int skipped = s3 ? !max : (max < ((s2 || xxs3) ? 1e-8f : 1e-15f));
+        float scale = 0, eff_max = max;
+        if (!skipped && xxs2) {
+            scale = make_qp_quants(32, KMAXQ + 1, xval, (uint8_t *)L, weight);
+            eff_max = scale * KMAXQ;
+            if (eff_max <= 0) { skipped = 1; memset(L, 0, sizeof L); }
+        }
+        if (skipped) { scales[ib] = 0; continue; }
+        float best = 0;
+        if (!xxs2) scale = max / (2 * KMAXQ - 1);
+        int on_grid[8], on_aux[8];
+        for (int k = 0; k < NG; ++k) on_grid[k] = !s3;
+        for (int is = -is_max; is <= is_max; ++is) {
+            const float id = (2 * KMAXQ - 1 + is * step) / eff_max;
+            const float this_scale = 1 / id;
+            for (int k = 0; k < NG; ++k) {
+                uint16_t u = 0;
+                for (int i = 0; i < GD; ++i) {
+                    const int l = nearest_int(0.5f * (id * xval[GD * k + i] - 1));
+                    Laux[GD * k + i] = (int8_t)IMAX(0, IMIN(KMAXQ - 1, l));
+                    u |= (uint16_t)(Laux[GD * k + i] << (BITS * i));
+                }
+                on_aux[k] = 1;
+                if (t->map[u] < 0) {
+                    on_aux[k] = 0;
+                    iq_best_neighbour(t, t->neighbours - t->map[u] - 1, xval + GD * k, waux + GD * k, this_scale, Laux + GD * k);
+                }
+            }
+            float sumqx = 0, sumq2 = 0;
+            for (int i = 0; i < BS; ++i) { const float w = weight[i], q = 2 * Laux[i] + 1; sumqx += w * xval[i] * q; sumq2 += w * q * q; }
+            if (sumq2 > 0 && sumqx * sumqx > best * sumq2) {
+                scale = sumqx / sumq2; best = scale * sumqx;
+                memcpy(L, Laux, (size_t)BS);
+                for (int k = 0; k < NG; ++k) on_grid[k] = on_aux[k];
+            }
+        }
+        int n_not = 0;
+        for (int k = 0; k < NG; ++k) if (!on_grid[k]) ++n_not;
+        if ((xxs2 ? 1 : n_not > 0) && scale > 0) {
+            const float id = 1 / scale;
+            for (int k = 0; k < NG; ++k) {
+                if (!(xxs2 || s3) && on_grid[k]) continue;
+                uint16_t u = 0;
+                int8_t Lr[8];
+                for (int i = 0; i < GD; ++i) {
+                    const int l = IMAX(0, IMIN(KMAXQ - 1, nearest_int(0.5f * (id * xval[GD * k + i] - 1))));
+                    u |= (uint16_t)(l << (BITS * i));
+                    Lr[i] = (int8_t)l;
+                }
+                int g = t->map[u];
+                if (xs2 || s2) {
+                    if (g < 0) iq_best_neighbour(t, t->neighbours - g - 1, xval + GD * k, waux + GD * k, scale, Lr);
+                    memcpy(L + GD * k, Lr, (size_t)GD);
+                } else {
+                    if (g < 0) g = iq_best_neighbour(t, t->neighbours - g - 1, xval + GD * k, waux + GD * k, scale, Lr);
+                    for (int i = 0; i < GD; ++i) L[GD * k + i] = (int8_t)((t->grid[g * GD + i] - 1) / 2);
+                }
+            }
+            float sumqx = 0, sumq2 = 0;
+            for (int i = 0; i < BS; ++i) { const float w = weight[i], q = 2 * L[i] + 1; sumqx += w * xval[i] * q; sumq2 += w * q * q; }
+            if (sumq2 > 0) scale = sumqx / sumq2;
+        }
+        if (scale < 0) {
+            scale = -scale;
+            for (int k = 0; k < NS; ++k) signs[k] = (uint8_t)(parity ? (~signs[k]) & 127 : ~signs[k]);
+        }
+        int gi[8];
+        for (int k = 0; k < NG; ++k) {
+            uint16_t u = 0;
+            for (int i = 0; i < GD; ++i) u |= (uint16_t)(L[GD * k + i] << (BITS * i));
+            gi[k] = t->map[u] < 0 ? 0 : t->map[u];
+        }
+        if (xxs2) {
+            uint32_t w0 = 0, w1 = 0;
+            for (int k = 0; k < 4; ++k) { w0 |= (uint32_t)gi[k] << (8 * k); w1 |= (uint32_t)signs[k] << (7 * k); }
+            wr32(y + 2 + 8 * ib, w0);
+            wr32(y + 2 + 8 * ib + 4, w1);
+        } else if (xs2) {
+            for (int k = 0; k < 2; ++k) wr16(y + 2 + 2 * (2 * ib + k), (uint16_t)(gi[k] | (signs[k] << 9)));
+        } else if (s2) {
+            for (int k = 0; k < 2; ++k) {
+                const int i8 = 2 * ib + k;
+                y[2 + i8] = (uint8_t)(gi[k] & 255);
+                y[66 + i8 / 4] |= (uint8_t)((gi[k] >> 8) << (2 * (i8 % 4)));
+                y[2 + 32 + i8] = signs[k];
+            }
+        } else if (xxs3) {
+            for (int k = 0; k < 8; ++k) y[2 + 8 * ib + k] = (uint8_t)gi[k];
+            wr32(y + 66 + 4 * ib, (uint32_t)signs[0] | ((uint32_t)signs[1] << 7) | ((uint32_t)signs[2] << 14) | ((uint32_t)signs[3] << 21));
+        } else {
+            for (int k = 0; k < 8; ++k) {
+                y[2 + 8 * pos + k] = (uint8_t)(gi[k] & 255);
+                y[66 + ib] |= (uint8_t)((gi[k] >> 8) << k);
+            }
+            for (int k = 0; k < 4; ++k) y[74 + 4 * pos + k] = signs[k];
+            ++pos;
+        }
+        scales[ib] = scale;
+        max_scale = max_scale > scale ? max_scale : scale;
+    }
+    if (!max_scale) {
+        if (xxs2 || xs2 || xxs3) memset(y, 0, (size_t)bytes);
+        return;
+    }
+    const float d = max_scale / 31;
+    wr16(y, f2h(s2 ? d * 0.9875f : xxs3 ? d * 1.0125f : s3 ? d * 1.033f : d));
+    const float id = 1 / d;
+    for (int ib = 0; ib < NB; ++ib) {
+        const int l = IMAX(0, IMIN(15, nearest_int(0.5f * (id * scales[ib] - 1))));
+        if (xxs2) { const uint32_t w1 = rd32(y + 2 + 8 * ib + 4) | ((uint32_t)l << 28); wr32(y + 2 + 8 * ib + 4, w1); }
+        else if (xxs3) { const uint32_t w = rd32(y + 66 + 4 * ib) | ((uint32_t)l << 28); wr32(y + 66 + 4 * ib, w); }
+        else {
+            uint8_t *sc = y + (xs2 ? 66 : s2 ? 74 : 106) + ib / 2;
+            if (ib % 2 == 0) *sc = (uint8_t)l; else *sc |= (uint8_t)(l << 4);
+        }
+    }
+}
+
+static int cmp_pair_value(const void *a, const void *b) {
+    const float l = *(const float *)a, r = *(const float *)b;
+    return l < r ? -1 : l > r ? 1 : 0;
+}
+
+/* One super-block of IQ1_S (32-element blocks) or IQ1_M (16-element blocks).
+ * upstream iq1_s.cpp:6-204, iq1_m.cpp:4-318.  The sort must keep equal values in index order
+ * (what upstream's qsort does in the C library it is built against); an insertion sort is used. */
+static void quant_iq1_block(int is_m, const float *xbl, uint8_t *y, const float *qw_block) {
+    const int BS = is_m ? 16 : 32, NB = 256 / BS, NG = BS / 8;
+    const iq_table *t = iq_table_get(2);
+    const float x_p[3] = {-1 + 0.125f, 0.125f, 1 + 0.125f}, x_m[3] = {-1 - 0.125f, -0.125f, 1 - 0.125f};
+    static const uint8_t masks[4] = {0x00, 0x80, 0x08, 0x88};
+    memset(y, 0, is_m ? 56 : 50);
+    float scales[16];
+    int shifts[16];
+    float sumx2 = 0;
+    for (int i = 0; i < 256; ++i) sumx2 += xbl[i] * xbl[i];
+    const float sigma2 = 2 * sumx2 / QK_K;
+    float max_scale = 0;
+    (void)cmp_pair_value;
+    for (int ib = 0; ib < NB; ++ib) {
+        const float *xb = xbl + BS * ib;
+        float weight[32];
+        int8_t L[32];
+        for (int i = 0; i < BS; ++i) weight[i] = qw_block ? qw_block[BS * ib + i] * sqrtf(sigma2 + xb[i] * xb[i]) : xb[i] * xb[i];
+        float max = fabsf(xb[0]);
+        for (int i = 1; i < BS; ++i) max = max > fabsf(xb[i]) ? max : fabsf(xb[i]);
+        scales[ib] = 0;
+        shifts[ib] = is_m ? 0 : 1;
+        if (max < (is_m ? 1e-7f : 1e-12f)) continue;
+        int idx[32];
+        float val[32];
+        for (int j = 0; j < BS; ++j) {
+            const float v = xb[j];
+            int p = j - 1;
+            while (p >= 0 && val[p] > v) { val[p + 1] = val[p]; idx[p + 1] = idx[p]; --p; }
+            val[p + 1] = v; idx[p + 1] = j;
+        }
+        float best_score = -3.402823466e+38f, scale = max;
+        int besti1 = -1, besti2 = -1, best_k = is_m ? -1 : 0;
+        if (!is_m) {
+            float sumx[33], sumw[33];
+            sumx[0] = sumw[0] = 0;
+            for (int j = 0; j < BS; ++j) { const int i = idx[j]; sumx[j + 1] = sumx[j] + weight[i] * xb[i]; sumw[j + 1] = sumw[j] + weight[i]; }
+            for (int i1 = 0; i1 <= BS; ++i1)
+                for (int i2 = i1; i2 <= BS; ++i2) {
+                    float sumqx = (sumx[i1] - sumx[0]) * x_p[0] + (sumx[i2] - sumx[i1]) * x_p[1] + (sumx[BS] - sumx[i2]) * x_p[2];
+                    float sumq2 = (sumw[i1] - sumw[0]) * x_p[0] * x_p[0] + (sumw[i2] - sumw[i1]) * x_p[1] * x_p[1] + (sumw[BS] - sumw[i2]) * x_p[2] * x_p[2];
+                    if (sumq2 > 0 && sumqx * sumqx > best_score * sumq2) { scale = sumqx / sumq2; best_score = scale * sumqx; besti1 = i1; besti2 = i2; best_k = 1; }
+                    sumqx = (sumx[i1] - sumx[0]) * x_m[0] + (sumx[i2] - sumx[i1]) * x_m[1] + (sumx[BS] - sumx[i2]) * x_m[2];
+                    sumq2 = (sumw[i1] - sumw[0]) * x_m[0] * x_m[0] + (sumw[i2] - sumw[i1]) * x_m[1] * x_m[1] + (sumw[BS] - sumw[i2]) * x_m[2] * x_m[2];
+                    if (sumq2 > 0 && sumqx * sumqx > best_score * sumq2) { scale = sumqx / sumq2; best_score = scale * sumqx; besti1 = i1; besti2 = i2; best_k = -1; }
+                }
+            if (besti1 < 0 || besti2 < 0 || best_k == 0) continue;
+        } else {
+            for (int i1 = 0; i1 <= BS; ++i1)
+                for (int i2 = i1; i2 <= BS; ++i2) {
+                    float sqx[4] = {0, 0, 0, 0}, sq2[4] = {0, 0, 0, 0};
+                    for (int j = 0; j < BS; ++j) {
+                        const int i = idx[j], lv = j < i1 ? 0 : (j < i2 ? 1 : 2), lo = i < BS / 2;
+                        const float ap = weight[i] * x_p[lv] * xb[i], am = weight[i] * x_m[lv] * xb[i];
+                        const float bp = weight[i] * x_p[lv] * x_p[lv], bm = weight[i] * x_m[lv] * x_m[lv];
+                        sqx[0] += ap; sqx[1] += lo ? ap : am; sqx[2] += lo ? am : ap; sqx[3] += am;
+                        sq2[0] += bp; sq2[1] += lo ? bp : bm; sq2[2] += lo ? bm : bp; sq2[3] += bm;
+                    }
+                    for (int k = 0; k < 4; ++k)
+                        if (sq2[k] > 0 && sqx[k] * sqx[k] > best_score * sq2[k]) { scale = sqx[k] / sq2[k]; best_score = scale * sqx[k]; besti1 = i1; besti2 = i2; best_k = k; }
+                }
+            if (besti1 < 0 || besti2 < 0 || best_k < 0) continue;
+        }
+        for (int j = 0; j < BS; ++j) L[idx[j]] = (int8_t)(j < besti1 ? 0 : (j < besti2 ? 1 : 2));
+        if (scale < 0) {
+            for (int j = 0; j < BS; ++j) L[j] = (int8_t)(2 - L[j]);
+            scale = -scale;
+            best_k = is_m ? 3 - best_k : -best_k;
+        }
+        int all_on_grid = 1, index[4];
+        for (int k = 0; k < NG; ++k) {
+            const int plus = is_m ? (k == 0 ? best_k < 2 : best_k % 2 == 0) : best_k == 1;
+            const float *xx = plus ? x_p : x_m;
+            uint16_t u = 0;
+            for (int j = 0; j < 8; ++j) u |= (uint16_t)(L[8 * k + j] << (2 * j));
+            int g = t->map[u];
+            if (g < 0) { all_on_grid = 0; g = iq1_best_neighbour(t, t->neighbours - g - 1, xb + 8 * k, weight + 8 * k, scale, xx, L + 8 * k); }
+            index[k] = g;
+        }
+        if (!all_on_grid) {
+            float sumqx = 0, sumq2 = 0;
+            for (int k = 0; k < NG; ++k) {
+                const int plus = is_m ? (k == 0 ? best_k < 2 : best_k % 2 == 0) : best_k == 1;
+                const float *xx = plus ? x_p : x_m;
+                const uint8_t *pg = t->grid + index[k] * 8;
+                for (int j = 0; j < 8; ++j) { const float w = weight[8 * k + j], q = xx[(pg[j] - 1) / 2]; sumqx += w * q * xb[8 * k + j]; sumq2 += w * q * q; }
+            }
+            if (sumqx > 0 && sumq2 > 0) scale = sumqx / sumq2;
+        }
+        if (!is_m) {
+            uint16_t h = 0;
+            for (int k = 0; k < 4; ++k) { y[2 + 4 * ib + k] = (uint8_t)(index[k] & 255); h |= (uint16_t)((index[k] >> 8) << (3 * k)); }
+            wr16(y + 34 + 2 * ib, h);
+        } else {
+            y[2 * ib] = (uint8_t)(index[0] & 255);
+            y[2 * ib + 1] = (uint8_t)(index[1] & 255);
+            y[32 + ib] = (uint8_t)((index[0] >> 8) | ((index[1] >> 8) << 4));
+        }
+        scales[ib] = scale;
+        shifts[ib] = best_k;
+        max_scale = max_scale > scale ? max_scale : scale;
+    }
+    if (!max_scale) return;
+    float d = max_scale / 15;
+    const float id = 1 / d;
+    if (!is_m) {
+        wr16(y, f2h(d * 1.125f));
+        for (int ib = 0; ib < NB; ++ib) {
+            int l = IMAX(0, IMIN(7, nearest_int(0.5f * (id * scales[ib] - 1))));
+            if (shifts[ib] == -1) l |= 8;
+            wr16(y + 34 + 2 * ib, (uint16_t)(rd16(y + 34 + 2 * ib) | (l << 12)));
+        }
+        return;
+    }
+    uint16_t sc[4] = {0, 0, 0, 0};
+    float sumqx_f = 0, sumq2_f = 0;
+    for (int ib = 0; ib < NB; ++ib) {
+        const int l = IMAX(0, IMIN(7, nearest_int(0.5f * (id * scales[ib] - 1))));
+        sc[ib / 4] |= (uint16_t)(l << (3 * (ib % 4)));
+        y[32 + ib] |= masks[shifts[ib]];
+        const float *xb = xbl + BS * ib;
+        for (int k = 0; k < 2; ++k) {
+            const int plus = k == 0 ? shifts[ib] < 2 : shifts[ib] % 2 == 0;
+            const float *xx = plus ? x_p : x_m;
+            const uint8_t *pg = t->grid + 8 * (y[2 * ib + k] + ((y[32 + ib] << (8 - 4 * k)) & 0x700));
+            for (int j = 0; j < 8; ++j) {
+                const float w = qw_block ? qw_block[BS * ib + 8 * k + j] * sqrtf(sigma2 + xb[8 * k + j] * xb[8 * k + j]) : xb[8 * k + j] * xb[8 * k + j];
+                const float q = xx[(pg[j] - 1) / 2] * (2 * l + 1);
+                sumqx_f += w * q * xb[8 * k + j];
+                sumq2_f += w * q * q;
+            }
+        }
+    }
+    if (sumq2_f > 0) d = sumqx_f / sumq2_f;
+    const uint16_t s = f2h(d * 1.1125f);
+    sc[0] |= (uint16_t)((s & 0x000f) << 12);
+    sc[1] |= (uint16_t)((s & 0x00f0) << 8);
+    sc[2] |= (uint16_t)((s & 0x0f00) << 4);
+    sc[3] |= (uint16_t)(s & 0xf000);
+    for (int k = 0; k < 4; ++k) wr16(y + 48 + 2 * k, sc[k]);
+}
+
+/* ------------------------------------------------------------------------------------------- */
 int gguf_oracle_quantize_supported(int type) {
     switch (type) {
         case T_F32: case T_F16: case T_BF16:
         case T_Q4_0: case T_Q4_1: case T_Q5_0: case T_Q5_1: case T_Q8_0: case T_Q1_0: case T_MXFP4: case T_NVFP4:
         case T_TQ1_0: case T_TQ2_0: case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K:
         case T_IQ4_NL: case T_IQ4_XS:
+        case T_IQ2_XXS: case T_IQ2_XS: case T_IQ2_S: case T_IQ3_XXS: case T_IQ3_S: case T_IQ1_S: case T_IQ1_M:
             return 1;
         default:
             return 0;
@@ -1109,6 +1523,7 @@ size_t gguf_oracle_quantize_chunk(int type, const float *src, void *dst, int64_t
             } else if (type == T_Q4_0 || type == T_Q5_0) quant_q4_0_q5_0(x, y, k, type == T_Q5_0);
             else quant_q4_1_q5_1(x, y, k, type == T_Q5_1);
             break;
+        case T_IQ2_XXS: case T_IQ2_XS: case T_IQ2_S: case T_IQ3_XXS: case T_IQ3_S: case T_IQ1_S: case T_IQ1_M:
         case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: case T_IQ4_XS: case T_IQ4_NL: {
             int e, b;
             block_geometry(type, &e, &b);
@@ -1123,6 +1538,8 @@ size_t gguf_oracle_quantize_chunk(int type, const float *src, void *dst, int64_t
                     else if (type == T_Q6_K) quant_q6k_block(xb, yb, qw);
                     else if (type == T_IQ4_XS) quant_iq4_superblock(256, xb, yb, qw);
                     else if (type == T_IQ4_NL) quant_iq4_superblock(32, xb, yb, qw);
+                    else if (type == T_IQ1_S || type == T_IQ1_M) quant_iq1_block(type == T_IQ1_M, xb, yb, qw);
+                    else if (type == T_IQ2_XXS || type == T_IQ2_XS || type == T_IQ2_S || type == T_IQ3_XXS || type == T_IQ3_S) quant_iq23_block(type, xb, yb, qw);
                     else quant_q4k_q5k_block(xb, yb, qw, type == T_Q5_K);
                 }
         } break;
