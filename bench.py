@@ -322,50 +322,67 @@ def main() -> None:
 
 def run_e2e(torch, lib, enc, rows, device_index, world, dist, device, steps):
     """h2d(encoded, pinned) -> dequantize_rows -> d2h(fp16/bf16, pinned) for the 12 decodes of a step,
-    through libgguf_cuda_* with a library context.  Timed with host wall clock around a final
-    event synchronize; max over ranks."""
-    ctx = ctypes.c_void_p()
-    if lib.libgguf_cuda_context_create(device_index, ctypes.byref(ctx)) != 0:
-        return None
-
-    def chk(st):
-        if st != 0:
-            raise RuntimeError(lib.libgguf_cuda_last_error(ctx).decode())
-
+    through libgguf_cuda_* with two library contexts used alternately (each owns a stream, a device
+    input/output buffer and a pinned result buffer), so that one decode's upload overlaps the
+    previous decode's download the way the converter's two slots do.  Timed with the host wall
+    clock around a final event synchronize on both contexts; max over ranks."""
+    NCTX = 2
     max_enc = max(t.numel() for t in enc.values())
     out_bytes = rows * WIDTH * 2
-    d_in, d_out = ctypes.c_void_p(), ctypes.c_void_p()
-    chk(lib.libgguf_cuda_buffer_create(ctx, max_enc, ctypes.byref(d_in)))
-    chk(lib.libgguf_cuda_buffer_create(ctx, out_bytes, ctypes.byref(d_out)))
-    h_out = ctypes.c_void_p()
-    chk(lib.libgguf_cuda_host_buffer_create(ctx, out_bytes, ctypes.byref(h_out)))
+
+    class Slot:
+        pass
+
+    slots = []
+    for _ in range(NCTX):
+        sl = Slot()
+        sl.ctx = ctypes.c_void_p()
+        if lib.libgguf_cuda_context_create(device_index, ctypes.byref(sl.ctx)) != 0:
+            return None
+        sl.d_in, sl.d_out, sl.h_out, sl.ev = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+        slots.append(sl)
+
+    def chk(sl, st):
+        if st != 0:
+            raise RuntimeError(lib.libgguf_cuda_last_error(sl.ctx).decode())
+
+    for sl in slots:
+        chk(sl, lib.libgguf_cuda_buffer_create(sl.ctx, max_enc, ctypes.byref(sl.d_in)))
+        chk(sl, lib.libgguf_cuda_buffer_create(sl.ctx, out_bytes, ctypes.byref(sl.d_out)))
+        chk(sl, lib.libgguf_cuda_host_buffer_create(sl.ctx, out_bytes, ctypes.byref(sl.h_out)))
+        chk(sl, lib.libgguf_cuda_event_create(sl.ctx, ctypes.byref(sl.ev)))
+    first = slots[0]
     h_in = {}
     for name, t in enc.items():
         hb = ctypes.c_void_p()
-        chk(lib.libgguf_cuda_host_buffer_create(ctx, t.numel(), ctypes.byref(hb)))
+        chk(first, lib.libgguf_cuda_host_buffer_create(first.ctx, t.numel(), ctypes.byref(hb)))
         host_copy = t.cpu().numpy()  # keep the array alive while memmove reads it
         ctypes.memmove(lib.libgguf_cuda_host_buffer_data(hb), host_copy.ctypes.data, host_copy.nbytes)
         del host_copy
         h_in[name] = hb
-    ev = ctypes.c_void_p()
-    chk(lib.libgguf_cuda_event_create(ctx, ctypes.byref(ev)))
     h2d = d2h = 0
 
     def step():
         nonlocal h2d, d2h
         h2d = d2h = 0
+        k = 0
         for dt in (1, 2):
             for name, qtype, _, _ in SWEEP:
+                sl = slots[k % NCTX]
+                if k >= NCTX:  # the slot's previous result has to be on the host before its buffers are reused
+                    chk(sl, lib.libgguf_cuda_event_synchronize(sl.ctx, sl.ev))
                 n = enc[name].numel()
-                chk(lib.libgguf_cuda_buffer_resize_discard(ctx, d_in, n))
-                chk(lib.libgguf_cuda_h2d(ctx, d_in, 0, lib.libgguf_cuda_host_buffer_data(h_in[name]), n))
-                chk(lib.libgguf_cuda_dequantize_rows(ctx, lib.libgguf_cuda_buffer_data(d_in), qtype, rows, WIDTH, dt,
-                                                     lib.libgguf_cuda_buffer_data(d_out)))
-                chk(lib.libgguf_cuda_d2h(ctx, lib.libgguf_cuda_host_buffer_data(h_out), d_out, 0, out_bytes))
+                chk(sl, lib.libgguf_cuda_buffer_resize_discard(sl.ctx, sl.d_in, n))
+                chk(sl, lib.libgguf_cuda_h2d(sl.ctx, sl.d_in, 0, lib.libgguf_cuda_host_buffer_data(h_in[name]), n))
+                chk(sl, lib.libgguf_cuda_dequantize_rows(sl.ctx, lib.libgguf_cuda_buffer_data(sl.d_in), qtype, rows, WIDTH, dt,
+                                                         lib.libgguf_cuda_buffer_data(sl.d_out)))
+                chk(sl, lib.libgguf_cuda_d2h(sl.ctx, lib.libgguf_cuda_host_buffer_data(sl.h_out), sl.d_out, 0, out_bytes))
+                chk(sl, lib.libgguf_cuda_event_record(sl.ctx, sl.ev))
                 h2d += n
                 d2h += out_bytes
-        chk(lib.libgguf_cuda_event_record(ctx, ev))
-        chk(lib.libgguf_cuda_event_synchronize(ctx, ev))
+                k += 1
+        for sl in slots:
+            chk(sl, lib.libgguf_cuda_event_synchronize(sl.ctx, sl.ev))
 
     step()
     if dist is not None:
@@ -379,15 +396,16 @@ def run_e2e(torch, lib, enc, rows, device_index, world, dist, device, steps):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t.item())
     algo = 2 * sum(enc[name].numel() + out_bytes for name, *_ in SWEEP)
-    lib.libgguf_cuda_event_destroy(ctx, ev)
     for hb in h_in.values():
-        lib.libgguf_cuda_host_buffer_destroy(ctx, hb)
-    lib.libgguf_cuda_host_buffer_destroy(ctx, h_out)
-    lib.libgguf_cuda_buffer_destroy(ctx, d_in)
-    lib.libgguf_cuda_buffer_destroy(ctx, d_out)
-    lib.libgguf_cuda_context_destroy(ctx)
+        lib.libgguf_cuda_host_buffer_destroy(first.ctx, hb)
+    for sl in slots:
+        lib.libgguf_cuda_event_destroy(sl.ctx, sl.ev)
+        lib.libgguf_cuda_host_buffer_destroy(sl.ctx, sl.h_out)
+        lib.libgguf_cuda_buffer_destroy(sl.ctx, sl.d_in)
+        lib.libgguf_cuda_buffer_destroy(sl.ctx, sl.d_out)
+        lib.libgguf_cuda_context_destroy(sl.ctx)
     return {"value": world * algo * steps / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "steps": steps, "api": "libgguf_cuda_h2d + libgguf_cuda_dequantize_rows + libgguf_cuda_d2h, pinned host buffers"}
+            "steps": steps, "api": "libgguf_cuda_h2d + libgguf_cuda_dequantize_rows + libgguf_cuda_d2h, pinned host buffers, 2 contexts alternating"}
 
 
 if __name__ == "__main__":

@@ -125,6 +125,11 @@ LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
  * 2^32 float bit patterns at block scale `scale` on the current device (about a second) and stores how many
  * inputs disagree (the quantizers rely on it being 0).  Blocking. */
 LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches);
+/* Same, for the forms the quantizers actually run.  mode 0: as above.  mode 1: the MXFP4 form, built on the hardware
+ * E2M1 conversion (`scale` must be 2^(e-128) with integer 0 <= e <= 252).  mode 2: the NVFP4 form, a binary search
+ * over the midpoints.  Modes 1 and 2 compare only the inputs the quantizers route there (finite, |x| <= 2^20 * scale).
+ * `fallbacks` (may be null) is reserved and receives 0. */
+LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4_mode(float scale, int mode, uint64_t *mismatches, uint64_t *fallbacks);
 
 /* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,
  * csrc/quantize_gguf.cpp:1732-1931 and :2072-2146; the pool itself has no upstream counterpart) ----

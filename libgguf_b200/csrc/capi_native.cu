@@ -1,5 +1,6 @@
 // Device-pointer C ABI (include/libgguf_cuda_native.h): contexts, events, grow-only buffers,
 // async copies and the row quantize / dequantize entry points.
+#include <math.h>
 #include <limits>
 #include <new>
 #include <string>
@@ -32,7 +33,7 @@ struct libgguf_cuda_event {
 using namespace gguf;
 
 namespace gguf {
-cudaError_t selftest_fp4(float e, unsigned long long *device_counter, cudaStream_t stream);
+cudaError_t selftest_fp4(float e, int mode, int ebyte, unsigned long long *device_counters, cudaStream_t stream);
 int64_t static_scratch_max_rows();
 cudaError_t launch_quantize_legacy_weighted_static(int type, const float *src, const float *qw, void *dst, int64_t nrows,
                                                    int64_t n_per_row, cudaStream_t stream);
@@ -369,20 +370,32 @@ int libgguf_cuda_quantize_weighted_rows_static(const float *device_input, const 
     return ok(nullptr);
 }
 
-int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches) {
+int libgguf_cuda_selftest_fp4_mode(float scale, int mode, uint64_t *mismatches, uint64_t *fallbacks) {
     if (!mismatches) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "mismatches must not be null");
-    unsigned long long *counter = nullptr;
-    cudaError_t error = cudaMalloc((void **)&counter, sizeof(unsigned long long));
+    if (mode < 0 || mode > 2) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "mode must be 0, 1 or 2");
+    int ebyte = 0;
+    if (mode == 1) {
+        int exponent = 0;
+        const bool power_of_two = scale > 0.f && frexpf(scale, &exponent) == 0.5f;
+        ebyte = exponent - 1 + 128;  // scale = 0.5 * 2^exponent
+        if (!power_of_two || ebyte > 252 || ebyte < 0)
+            return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "mode 1 needs a power-of-two scale 2^(e-128), e <= 252");
+    }
+    unsigned long long *counters = nullptr;
+    cudaError_t error = cudaMalloc((void **)&counters, 2 * sizeof(unsigned long long));
     if (error != cudaSuccess) return cuda_fail(nullptr, error);
-    error = cudaMemset(counter, 0, sizeof(unsigned long long));
-    if (error == cudaSuccess) error = selftest_fp4(scale, counter, nullptr);
-    unsigned long long host = 0;
-    if (error == cudaSuccess) error = cudaMemcpy(&host, counter, sizeof(host), cudaMemcpyDeviceToHost);
-    cudaFree(counter);
+    error = cudaMemset(counters, 0, 2 * sizeof(unsigned long long));
+    if (error == cudaSuccess) error = selftest_fp4(scale, mode, ebyte, counters, nullptr);
+    unsigned long long host[2] = {0, 0};
+    if (error == cudaSuccess) error = cudaMemcpy(host, counters, sizeof(host), cudaMemcpyDeviceToHost);
+    cudaFree(counters);
     if (error != cudaSuccess) return cuda_fail(nullptr, error);
-    *mismatches = host;
+    *mismatches = host[0];
+    if (fallbacks) *fallbacks = host[1];
     return ok(nullptr);
 }
+
+int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches) { return libgguf_cuda_selftest_fp4_mode(scale, 0, mismatches, nullptr); }
 
 int libgguf_cuda_prepare_qtype(int64_t qtype) {
     if (qtype < 0 || qtype >= GGML_TYPE_COUNT) return fail(nullptr, LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE, "unsupported type");

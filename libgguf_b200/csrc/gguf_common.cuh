@@ -120,6 +120,8 @@ GGUF_HD float ue4m3_half_to_f32(uint8_t x) {
     if (x == 0 || x == 0x7F) return 0.0f;
     const int exp = (x >> 3) & 0xF;
     const int man = x & 0x7;
+    // normal codes: (1 + man/8) * 2^(exp-7) * 0.5 written directly as float bits
+    if (exp != 0) return bits_to_f32(((uint32_t)(exp + 119) << 23) | ((uint32_t)man << 20));
     float raw;
     if (exp == 0) {
         raw = (float)man * bits_to_f32((127u - 9u) << 23);

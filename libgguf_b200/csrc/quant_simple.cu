@@ -2,11 +2,12 @@
 // (the paths taken when no importance weights are given; the weighted legacy variants live
 // with the K-quant search code).
 //
-// 32-element types: every lane loads one float4 (16 B), 8 lanes cover a block, a warp covers
-// 4 blocks (512 B of input per warp load).  Block extrema are order-free and are reduced with
-// shuffles inside the 8-lane group; the one place where the upstream loop is order sensitive --
-// "first element with the largest magnitude" in Q4_0 / Q5_0 -- is reduced on (|v|, index) pairs.
-// Each CTA assembles its encoded blocks in shared memory and writes them out as 16-byte vectors.
+// 32-element types: a CTA stages 128 runs of 32 floats in shared memory with coalesced 16-byte
+// loads, then every thread encodes one run from registers, serially and in upstream's element
+// order, and the encoded tile is written out as 16-byte vectors.  The encoders are written to
+// keep the instruction count per element low (the kernels are issue-bound long before they are
+// memory-bound): rounding by directed-rounding adds of 2^23 instead of conversions, FP4 levels
+// by the hardware E2M1 conversion wrapped so that it reproduces upstream's scan exactly.
 #include <float.h>
 #include <math.h>
 
@@ -20,6 +21,7 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr unsigned kFull = 0xffffffffu;
+constexpr float kInfinity = __builtin_huge_valf();
 
 // The 16-way nearest-level scan of the FP4 formats (upstream libgguf_common.h:321-335):
 // first index with the smallest |level*e - x|.
@@ -53,37 +55,105 @@ GGUF_D int best_index_fp4(float x, float e) {
     return fp4_thresholds_valid(fabsf(x), e) ? best_index_fp4_thresholds(x, e) : best_index_fp4_scan(x, e);
 }
 
-// Packs the levels of N elements (element j low nibble, element j + N/2 high nibble of byte j).  The
-// threshold form is valid for the whole group when it is valid for the group's largest magnitude; the
-// scan runs as a rolled loop so that its code exists once per kernel.
+// ---- FP4 levels by the hardware conversion ----------------------------------------------------
+// cvt.rn.satfinite.e2m1x2.f32 rounds to the nearest E2M1 value {0,.5,1,1.5,2,3,4,6} (saturating),
+// ties to even; upstream's scan picks the nearest of {0,1,2,3,4,6,8,12}*e with ties to the smaller
+// magnitude, and never emits the code of -0.  The two agree wherever the scaled input is not an
+// exact tie, so the wrappers below keep exact ties away from the instruction.
+//
+// Four bytes of codes: byte k = code(hi[k]) << 4 | code(lo[k]).
+GGUF_D uint32_t cvt_e2m1x8(const float *lo, const float *hi) {
+    uint32_t r;
+    asm("{\n"
+        ".reg .b8 b0, b1, b2, b3;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %1, %2;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %3, %4;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %5, %6;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %7, %8;\n"
+        "mov.b32 %0, {b0, b1, b2, b3};\n"
+        "}"
+        : "=r"(r)
+        : "f"(hi[0]), "f"(lo[0]), "f"(hi[1]), "f"(lo[1]), "f"(hi[2]), "f"(lo[2]), "f"(hi[3]), "f"(lo[3]));
+    return r;
+}
+// Code 8 (-0) -> 0 in each of the eight nibbles: the scan returns the first best index, which is 0.
+GGUF_D uint32_t drop_negative_zero(uint32_t w) {
+    const uint32_t mag = w & 0x77777777u;
+    const uint32_t nonzero = (mag + 0x77777777u) & 0x88888888u;  // bit 3 of a nibble set iff its magnitude is not 0
+    return mag | (w & nonzero);
+}
+
+// Power-of-two scale (MXFP4), e = 2^(ebyte-128) being the value of level 1.  x * 2^(127-ebyte) is
+// exact, and multiplying by (1 - 2^-24) with rounding toward zero steps a float to its predecessor
+// in magnitude; "predecessor | 1" is x itself when x's last mantissa bit is 1 and the predecessor
+// when it is 0.  Every tie has a zero last bit, so ties move just below themselves (-> smaller
+// magnitude, as the scan does) and no other value crosses a tie.
+// scale_rz = 2^(127-ebyte) * (1 - 2^-24), exactly representable for ebyte <= 252.
+GGUF_D float mx_scale_rz(int ebyte) { return __uint_as_float(((uint32_t)(254 - ebyte) << 23) - 1u); }
+GGUF_D float mx_nudge(float x, float scale_rz) { return __uint_as_float(__float_as_uint(__fmul_rz(x, scale_rz)) | 1u); }
+
+// Any scale (NVFP4): the same answer as best_index_fp4_thresholds by a three-step binary search over
+// the seven midpoints t[k] = {0.5,1.5,2.5,3.5,5,7,10}[k] * e (exact products), which costs fewer
+// instructions than counting.  Returns the 4-bit code.
+struct Fp4Midpoints { float t[7]; };
+GGUF_D Fp4Midpoints fp4_midpoints(float e) {
+    return {{0.5f * e, 1.5f * e, 2.5f * e, 3.5f * e, 5.f * e, 7.f * e, 10.f * e}};
+}
+GGUF_D uint32_t fp4_code_bsearch(float x, const Fp4Midpoints &k) {
+    const float m = fabsf(x);
+    const bool p2 = m > k.t[3];
+    const float mid = p2 ? k.t[5] : k.t[1], up = p2 ? k.t[6] : k.t[2], down = p2 ? k.t[4] : k.t[0];
+    uint32_t idx = p2 ? 4u : 0u;
+    const bool p1 = m > mid;
+    if (p1) idx += 2u;
+    if (m > (p1 ? up : down)) idx += 1u;
+    // sign bit, except on level 0: (idx + 7) & 8 is 8 exactly when idx >= 1
+    return idx | ((__float_as_uint(x) >> 28) & (idx + 7u) & 8u);
+}
+// Codes of N elements, element j in the low and j + N/2 in the high nibble of byte j.
 template <int N>
-GGUF_D void pack_fp4(const float *x, float amax, float e, uint8_t *out) {
-    if (fp4_thresholds_valid(amax, e)) {
+GGUF_D void pack_fp4_bsearch(const float *x, float e, uint32_t *words) {
+    const Fp4Midpoints k = fp4_midpoints(e);
 #pragma unroll
-        for (int j = 0; j < N / 2; ++j)
-            out[j] = (uint8_t)(best_index_fp4_thresholds(x[j], e) | (best_index_fp4_thresholds(x[j + N / 2], e) << 4));
-    } else {
-        // x is a register array: select by comparison instead of indexing it dynamically
-#pragma unroll 1
-        for (int j = 0; j < N / 2; ++j) {
-            float lo = 0.f, hi = 0.f;
+    for (int w = 0; w < N / 8; ++w) {
+        uint32_t word = 0;
 #pragma unroll
-            for (int k = 0; k < N / 2; ++k) {
-                if (k == j) { lo = x[k]; hi = x[k + N / 2]; }
-            }
-            out[j] = (uint8_t)(best_index_fp4_scan(lo, e) | (best_index_fp4_scan(hi, e) << 4));
+        for (int i = 0; i < 4; ++i) {
+            word += fp4_code_bsearch(x[4 * w + i], k) << (8 * i);
+            word += fp4_code_bsearch(x[4 * w + i + N / 2], k) << (8 * i + 4);
         }
+        words[w] = word;
     }
 }
 
-__global__ void selftest_fp4_kernel(float e, unsigned long long *mismatches) {
+// mode 0: threshold search against the scan.  mode 1: power-of-two-scale hardware path (e is
+// 2^(ebyte-128), ebyte <= 252).  mode 2: binary search over the midpoints.  Modes 1 and 2 only look at the
+// inputs the quantizers send down those paths (|x| <= 2^20 * e).
+__global__ void selftest_fp4_kernel(float e, int mode, int ebyte, unsigned long long *mismatches, unsigned long long *fallbacks) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    unsigned long long bad = 0;
+    unsigned long long bad = 0, fell = 0;
+    const float scale_rz = mx_scale_rz(ebyte);
     for (uint64_t bits = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; bits < (1ull << 32); bits += stride) {
         const float x = __uint_as_float((uint32_t)bits);
-        if (best_index_fp4(x, e) != best_index_fp4_scan(x, e)) ++bad;
+        const int want = best_index_fp4_scan(x, e);
+        if (mode == 0) {
+            if (best_index_fp4(x, e) != want) ++bad;
+            continue;
+        }
+        if (!(fabsf(x) < kInfinity) || !fp4_thresholds_valid(fabsf(x), e)) continue;
+        float lo[4] = {x, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+        if (mode == 1) {
+            lo[0] = mx_nudge(x, scale_rz);
+            if ((int)(drop_negative_zero(cvt_e2m1x8(lo, hi)) & 0xFu) != want) ++bad;
+        } else {
+            float xs[8] = {x, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            uint32_t word;
+            pack_fp4_bsearch<8>(xs, e, &word);
+            if ((int)(word & 0xFu) != want) ++bad;
+        }
     }
     if (bad) atomicAdd(mismatches, bad);
+    if (fell) atomicAdd(fallbacks, fell);
 }
 
 enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4, NVFP4 };
@@ -116,154 +186,372 @@ GGUF_D int round_half_away(float v) {
 
 constexpr int kBlockThreads = 128;   // one thread per 32 elements
 constexpr int kRowStride = 36;       // floats per staged 32-element run: 16-byte aligned rows, conflict-free LDS.128
+constexpr float kInf = kInfinity;
 
-// 32-element types (and NVFP4 as two 16-element sub-blocks per thread).  The CTA stages
-// 128 x 32 floats in shared memory with coalesced 16-byte loads; then every thread encodes its own
-// 32 elements from registers, serially and in upstream's element order (so "first element with
-// the largest magnitude" and the like need no cross-lane exchange); the encoded tile is written
-// out as 16-byte vectors.
-// `mx_steps` : for MXFP4, table of the smallest float in each binade [2^t, 2^(t+1)), t = -149..127,
-// for which the host libm's floorf(log2f(x)) already returns t+1 (+inf bits if it never does).
+// Three-input extrema (sm_100): max(|a|,|b|,|c|) returning NaN when any input is NaN, and the
+// plain three-input max / min, which skip NaN inputs like upstream's `if (v > max)` loops do.
+GGUF_D float amax3_nan(float a, float b, float c) {
+    float d;
+    asm("max.NaN.abs.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+GGUF_D float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+GGUF_D float min3(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// max |x[0..N)|, NaN if any element is NaN
+template <int N>
+GGUF_D float amax_nan(const float *x) {
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < N; j += 2) m = amax3_nan(m, x[j], x[j + 1]);
+    return m;
+}
+
+// floor(v) for 0 <= v < 2^23 in the low mantissa bits of the result: the sum v + 2^23 is rounded down.
+GGUF_D uint32_t floor_bits(float v) { return __float_as_uint(__fadd_rd(v, 8388608.f)); }
+// low bytes of a and b -> 16 bits
+GGUF_D uint32_t pack2(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x0040); }
+
+// `nhalf` 16-bit units to a shared-memory address that is 2-byte aligned when `even` is set.
+template <int NHALF>
+GGUF_D void emit_halves(uint8_t *out, const uint32_t (&h)[NHALF], bool even) {
+    if (even) {
+#pragma unroll
+        for (int i = 0; i < NHALF; ++i) reinterpret_cast<uint16_t *>(out)[i] = (uint16_t)h[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < NHALF; ++i) st16(out + 2 * i, (uint16_t)h[i]);
+    }
+}
+
+// MXFP4 scale byte: (uint8_t)(floorf(log2f(amax)) - 2 + 127) as the x86 build computes it.
+// `mx_steps`: per binade [2^t, 2^(t+1)), t = -149..127, the smallest float for which the host libm's
+// floorf(log2f(x)) already returns t+1 (+inf bits if it never does).
+GGUF_D int mxfp4_scale_byte(float amax, const float *__restrict__ mx_steps) {
+    if (!(amax > 0.0f)) return 0;
+    const uint32_t bits = f32_to_bits(amax);
+    const int bexp = (int)(bits >> 23);  // 255 (inf) converts to 0x80000000 on x86: low byte 0
+    const int t = bexp ? bexp - 127 : (31 - __clz((int)(bits & 0x7fffffu))) - 149;
+    const int fl = (t >= -149 && t <= 127 && amax >= mx_steps[t + 149]) ? t + 1 : t;
+    return bexp == 255 ? 0 : (fl - 2 + 127) & 0xFF;
+}
+
+// The encoders as upstream writes them, element by element from the staged run in shared memory,
+// rolled loops, byte stores.  They serve every input the fast encoders decline (non-finite values,
+// scales whose reciprocal overflows, sign-of-zero and first-of-equal-extrema questions).
+template <Simple K>
+__device__ __noinline__ void encode_exact(const float *x, uint8_t *out, const float *__restrict__ mx_steps) {
+    if constexpr (K == Simple::Q8_0) {
+        // upstream q8_0.cpp:16-43; MAX(a, b) = a > b ? a : b forgets the running maximum at a NaN
+        float amax = 0.0f;
+#pragma unroll 1
+        for (int j = 0; j < 32; ++j) { const float a = fabsf(x[j]); amax = amax > a ? amax : a; }
+        const float d = amax / 127.0f;
+        const float id = d ? 1.0f / d : 0.0f;
+        st16(out, f32_to_half_bits(d));
+#pragma unroll 1
+        for (int j = 0; j < 32; ++j) {
+            const float v = x[j] * id;
+            // (int8_t)roundf(v): out-of-range and NaN convert to INT_MIN, low byte 0
+            out[2 + j] = fabsf(v) < 2147483648.f ? (uint8_t)(int8_t)round_half_away(v) : (uint8_t)0;
+        }
+    } else if constexpr (K == Simple::Q4_0 || K == Simple::Q5_0) {
+        // upstream q4_0.cpp:16-58, q5_0.cpp:18-65
+        constexpr bool FIVE = K == Simple::Q5_0;
+        float amax = 0.0f, vmax = 0.0f;
+#pragma unroll 1
+        for (int j = 0; j < 32; ++j) {
+            if (amax < fabsf(x[j])) { amax = fabsf(x[j]); vmax = x[j]; }
+        }
+        const float d = vmax / (FIVE ? -16.0f : -8.0f);
+        const float id = d ? 1.0f / d : 0.0f;
+        st16(out, f32_to_half_bits(d));
+        uint32_t qh = 0;
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) {
+            const int q0 = imin(FIVE ? 31 : 15, trunc_to_i8(x[j] * id + (FIVE ? 16.5f : 8.5f))) & 0xFF;
+            const int q1 = imin(FIVE ? 31 : 15, trunc_to_i8(x[j + 16] * id + (FIVE ? 16.5f : 8.5f))) & 0xFF;
+            if (FIVE) {
+                out[6 + j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
+                qh |= (uint32_t)((q0 & 0x10) >> 4) << j;
+                qh |= (uint32_t)((q1 & 0x10) >> 4) << (j + 16);
+            } else {
+                out[2 + j] = (uint8_t)(q0 | (q1 << 4));
+            }
+        }
+        if (FIVE) st32(out + 2, qh);
+    } else if constexpr (K == Simple::Q4_1 || K == Simple::Q5_1) {
+        // upstream q4_1.cpp:16-57, q5_1.cpp:18-68
+        constexpr bool FIVE = K == Simple::Q5_1;
+        float mn = FLT_MAX, mx = -FLT_MAX;
+#pragma unroll 1
+        for (int j = 0; j < 32; ++j) {
+            if (x[j] < mn) mn = x[j];
+            if (x[j] > mx) mx = x[j];
+        }
+        const float d = (mx - mn) / (FIVE ? 31.0f : 15.0f);
+        const float id = d ? 1.0f / d : 0.0f;
+        st16(out, f32_to_half_bits(d));
+        st16(out + 2, f32_to_half_bits(mn));
+        uint32_t qh = 0;
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) {
+            const float t0 = (x[j] - mn) * id + 0.5f, t1 = (x[j + 16] - mn) * id + 0.5f;
+            if (FIVE) {
+                // (uint8_t)(float): truncation through int32, low byte
+                const int q0 = (fabsf(t0) < 2147483648.f ? __float2int_rz(t0) : (int)0x80000000) & 0xFF;
+                const int q1 = (fabsf(t1) < 2147483648.f ? __float2int_rz(t1) : (int)0x80000000) & 0xFF;
+                out[8 + j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
+                qh |= (uint32_t)((q0 & 0x10) >> 4) << j;
+                qh |= (uint32_t)((q1 & 0x10) >> 4) << (j + 16);
+            } else {
+                const int q0 = imin(15, trunc_to_i8(t0)) & 0xFF, q1 = imin(15, trunc_to_i8(t1)) & 0xFF;
+                out[4 + j] = (uint8_t)(q0 | (q1 << 4));
+            }
+        }
+        if (FIVE) st32(out + 4, qh);
+    } else if constexpr (K == Simple::MXFP4) {
+        // upstream mxfp4.cpp:17-54
+        float amax = 0.0f;
+#pragma unroll 1
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
+        const int e = mxfp4_scale_byte(amax, mx_steps);
+        const float d = e8m0_half_to_f32((uint8_t)e);
+        out[0] = (uint8_t)e;
+#pragma unroll 1
+        for (int j = 0; j < 16; ++j) out[1 + j] = (uint8_t)(best_index_fp4(x[j], d) | (best_index_fp4(x[j + 16], d) << 4));
+    }
+}
+
+// One 16-element NVFP4 sub-block the way upstream writes it (nvfp4.cpp:28-54).
+__device__ __noinline__ void encode_exact_nvfp4(const float *x, uint8_t *scale_byte, uint8_t *qs) {
+    float amax = 0.0f;
+#pragma unroll 1
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(x[j]));
+    const uint8_t ue = f32_to_ue4m3(amax / 6.0f);
+    const float d = ue4m3_half_to_f32(ue);
+    *scale_byte = ue;
+#pragma unroll 1
+    for (int j = 0; j < 8; ++j) qs[j] = (uint8_t)(best_index_fp4(x[j], d) | (best_index_fp4(x[j + 8], d) << 4));
+}
+
+// 16-byte asynchronous copy global -> shared (LDGSTS), bypassing L1 and the register file.
+GGUF_D void cp_async16(void *smem, const void *gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+GGUF_D void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+GGUF_D void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// 32-element types (and NVFP4 as two 16-element sub-blocks per thread).  Persistent CTAs walk the
+// tiles (128 runs of 32 floats) with a stride of the grid size.  A tile is staged in shared memory
+// by coalesced 16-byte asynchronous copies, one tile ahead of the one being encoded, so the copy of
+// tile i+1 is in flight while every thread encodes its own 32 elements of tile i from registers; the
+// encoded tile is written out as 16-byte vectors.
 template <Simple K>
 __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
                                                                int64_t nruns, const float *__restrict__ mx_steps) {
     constexpr int BYTES = SimpleGeom<K>::BYTES;
-    __shared__ __align__(16) float xin[kBlockThreads * kRowStride];
+    __shared__ __align__(16) float xbuf[2][kBlockThreads * kRowStride];
     __shared__ __align__(16) uint8_t stage[kBlockThreads * BYTES + 32];
 
-    const int64_t r0 = (int64_t)blockIdx.x * kBlockThreads;
+    const int64_t ntiles = (nruns + kBlockThreads - 1) / kBlockThreads;
+    const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15);  // a tile starts a multiple of 16 bytes into dst
+    uint8_t *tile = stage + mis;
+    const bool even = (mis & 1) == 0, word_aligned = (mis & 3) == 0;
+
+    auto prefetch = [&](int64_t t, float *xin) {
+        const int64_t r0 = t * kBlockThreads;
+        const int nr = (int)(nruns - r0 < kBlockThreads ? nruns - r0 : kBlockThreads);
+        const float4 *g4 = reinterpret_cast<const float4 *>(src + r0 * 32);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const int i = k * kBlockThreads + threadIdx.x;  // float4 index inside the tile
+            if (i < nr * 8) cp_async16(xin + (i >> 3) * kRowStride + (i & 7) * 4, g4 + i);
+        }
+        cp_async_commit();
+    };
+
+    int64_t t = blockIdx.x;
+    if (t < ntiles) prefetch(t, xbuf[0]);
+    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
+    float *xin = xbuf[it & 1];
+    const int64_t tnext = t + gridDim.x;
+    if (tnext < ntiles) {
+        prefetch(tnext, xbuf[(it + 1) & 1]);
+        cp_async_wait<1>();
+    } else {
+        cp_async_wait<0>();
+    }
+    __syncthreads();  // tile t is in xin; every thread is done with the previous tile's stage
+    const int64_t r0 = t * kBlockThreads;
     const int nr = (int)(nruns - r0 < kBlockThreads ? nruns - r0 : kBlockThreads);
     uint8_t *gdst = dst + r0 * BYTES;
-    uint8_t *tile = stage + (reinterpret_cast<uintptr_t>(gdst) & 15);
-    const float4 *g4 = reinterpret_cast<const float4 *>(src + r0 * 32);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const int i = k * kBlockThreads + threadIdx.x;  // float4 index inside the tile
-        if (i < nr * 8) *reinterpret_cast<float4 *>(xin + (i >> 3) * kRowStride + (i & 7) * 4) = __ldcs(g4 + i);
-    }
-    __syncthreads();
     if (threadIdx.x < nr) {
+        const float *xrow = xin + threadIdx.x * kRowStride;
         float x[32];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const float4 v = *reinterpret_cast<const float4 *>(xin + threadIdx.x * kRowStride + 4 * k);
+            const float4 v = *reinterpret_cast<const float4 *>(xrow + 4 * k);
             x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
         }
         uint8_t *out = tile + threadIdx.x * BYTES;
         if constexpr (K == Simple::Q8_0) {
-            // upstream q8_0.cpp:16-43
-            float amax = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
+            const float amax = amax_nan<32>(x);
             const float d = amax / 127.0f;
             const float id = d ? 1.0f / d : 0.0f;
-            st16(out, f32_to_half_bits(d));
+            if (amax < kInf && id < kInf) {
+                // |x * id| <= 127.00002: roundf(v) = sign(v) * floor(|v| + 0.5); the first sum rounded down
+                // has the same floor as the exact sum.
+                uint32_t h[17];
+                h[0] = f32_to_half_bits(d);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) out[2 + j] = (uint8_t)(int8_t)round_half_away(x[j] * id);
-        } else if constexpr (K == Simple::Q4_0 || K == Simple::Q5_0) {
-            // upstream q4_0.cpp:16-58, q5_0.cpp:18-65
-            constexpr bool FIVE = K == Simple::Q5_0;
-            float amax = 0.0f, vmax = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (amax < fabsf(x[j])) { amax = fabsf(x[j]); vmax = x[j]; }
+                for (int j = 0; j < 32; j += 2) {
+                    const float v0 = x[j] * id, v1 = x[j + 1] * id;
+                    int q0 = (int)floor_bits(__fadd_rd(fabsf(v0), 0.5f)), q1 = (int)floor_bits(__fadd_rd(fabsf(v1), 0.5f));
+                    if (v0 < 0.f) q0 = -q0;
+                    if (v1 < 0.f) q1 = -q1;
+                    h[1 + j / 2] = pack2((uint32_t)q0, (uint32_t)q1);
+                }
+                emit_halves(out, h, even);
+            } else {
+                encode_exact<K>(xrow, out, mx_steps);
             }
+        } else if constexpr (K == Simple::Q4_0 || K == Simple::Q5_0) {
+            constexpr bool FIVE = K == Simple::Q5_0;
+            // the element of largest magnitude is the largest or the smallest element; when both have that
+            // magnitude (or all are zero) upstream takes the first one, which the exact encoder finds
+            float hi = -kInf, lo = kInf;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) { hi = max3(hi, x[j], x[j + 1]); lo = min3(lo, x[j], x[j + 1]); }
+            const float vmax = hi > -lo ? hi : lo;
             const float d = vmax / (FIVE ? -16.0f : -8.0f);
             const float id = d ? 1.0f / d : 0.0f;
-            st16(out, f32_to_half_bits(d));
-            uint32_t qh = 0;
+            if (hi != -lo && fabsf(id) < kInf) {
+                // x * id + 8.5 lies in [0.49, 16.51] (NaN for a NaN element, which upstream stores as 0):
+                // (int8_t) truncation = floor, MIN(15, .) = the upper clamp
+                constexpr float OFF = FIVE ? 16.5f : 8.5f, TOP = FIVE ? 31.75f : 15.75f;
+                constexpr int HEAD = FIVE ? 3 : 1;
+                uint32_t h[HEAD + 8];
+                h[0] = f32_to_half_bits(d);
+                uint32_t qh = 0;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int q0 = imin(FIVE ? 31 : 15, trunc_to_i8(x[j] * id + (FIVE ? 16.5f : 8.5f))) & 0xFF;
-                const int q1 = imin(FIVE ? 31 : 15, trunc_to_i8(x[j + 16] * id + (FIVE ? 16.5f : 8.5f))) & 0xFF;
-                if (FIVE) {
-                    out[6 + j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
-                    qh |= (uint32_t)((q0 & 0x10) >> 4) << j;
-                    qh |= (uint32_t)((q1 & 0x10) >> 4) << (j + 16);
-                } else {
-                    out[2 + j] = (uint8_t)(q0 | (q1 << 4));
+                for (int j = 0; j < 16; j += 2) {
+                    uint32_t b[2];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const uint32_t a0 = floor_bits(fminf(fmaxf(x[j + k] * id + OFF, 0.f), TOP));
+                        const uint32_t a1 = floor_bits(fminf(fmaxf(x[j + k + 16] * id + OFF, 0.f), TOP));
+                        if (FIVE) {
+                            qh |= ((a0 >> 4) & 1u) << (j + k);
+                            qh |= ((a1 >> 4) & 1u) << (j + k + 16);
+                            b[k] = (a0 & 0xFu) + (a1 << 4);
+                        } else {
+                            b[k] = a0 + (a1 << 4);  // only the low byte is kept
+                        }
+                    }
+                    h[HEAD + j / 2] = pack2(b[0], b[1]);
                 }
+                if (FIVE) { h[1] = qh & 0xFFFFu; h[2] = qh >> 16; }
+                emit_halves(out, h, even);
+            } else {
+                encode_exact<K>(xrow, out, mx_steps);
             }
-            if (FIVE) st32(out + 2, qh);
         } else if constexpr (K == Simple::Q4_1 || K == Simple::Q5_1) {
-            // upstream q4_1.cpp:16-57, q5_1.cpp:18-68
             constexpr bool FIVE = K == Simple::Q5_1;
-            float mn = FLT_MAX, mx = -FLT_MAX;
+            float mx = -FLT_MAX, mn = FLT_MAX;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (x[j] < mn) mn = x[j];
-                if (x[j] > mx) mx = x[j];
-            }
+            for (int j = 0; j < 32; j += 2) { mx = max3(mx, x[j], x[j + 1]); mn = min3(mn, x[j], x[j + 1]); }
             const float d = (mx - mn) / (FIVE ? 31.0f : 15.0f);
             const float id = d ? 1.0f / d : 0.0f;
-            st16(out, f32_to_half_bits(d));
-            st16(out + 2, f32_to_half_bits(mn));
-            uint32_t qh = 0;
+            // a zero extremum may be +0 or -0 depending on which came first: left to the exact encoder
+            if (mn != 0.f && mx != 0.f && id < kInf) {
+                constexpr float TOP = FIVE ? 31.75f : 15.75f;
+                constexpr int HEAD = FIVE ? 4 : 2;
+                uint32_t h[HEAD + 8];
+                h[0] = f32_to_half_bits(d);
+                h[1] = f32_to_half_bits(mn);
+                uint32_t qh = 0;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float t0 = (x[j] - mn) * id + 0.5f, t1 = (x[j + 16] - mn) * id + 0.5f;
-                if (FIVE) {
-                    // (uint8_t)(float): truncation through int32, low byte
-                    const int q0 = (fabsf(t0) < 2147483648.f ? __float2int_rz(t0) : (int)0x80000000) & 0xFF;
-                    const int q1 = (fabsf(t1) < 2147483648.f ? __float2int_rz(t1) : (int)0x80000000) & 0xFF;
-                    out[8 + j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
-                    qh |= (uint32_t)((q0 & 0x10) >> 4) << j;
-                    qh |= (uint32_t)((q1 & 0x10) >> 4) << (j + 16);
-                } else {
-                    const int q0 = imin(15, trunc_to_i8(t0)) & 0xFF, q1 = imin(15, trunc_to_i8(t1)) & 0xFF;
-                    out[4 + j] = (uint8_t)(q0 | (q1 << 4));
+                for (int j = 0; j < 16; j += 2) {
+                    uint32_t b[2];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const uint32_t a0 = floor_bits(fminf(fmaxf((x[j + k] - mn) * id + 0.5f, 0.f), TOP));
+                        const uint32_t a1 = floor_bits(fminf(fmaxf((x[j + k + 16] - mn) * id + 0.5f, 0.f), TOP));
+                        if (FIVE) {
+                            qh |= ((a0 >> 4) & 1u) << (j + k);
+                            qh |= ((a1 >> 4) & 1u) << (j + k + 16);
+                            b[k] = (a0 & 0xFu) + (a1 << 4);
+                        } else {
+                            b[k] = a0 + (a1 << 4);
+                        }
+                    }
+                    h[HEAD + j / 2] = pack2(b[0], b[1]);
                 }
+                if (FIVE) { h[2] = qh & 0xFFFFu; h[3] = qh >> 16; }
+                emit_halves(out, h, even);
+            } else {
+                encode_exact<K>(xrow, out, mx_steps);
             }
-            if (FIVE) st32(out + 4, qh);
         } else if constexpr (K == Simple::MXFP4) {
-            // upstream mxfp4.cpp:17-54
-            float amax = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
-            int e = 0;
-            if (amax > 0.0f) {
-                // floorf(log2f(amax)) as the host libm computes it: true binade t, plus one when
-                // amax has reached the per-binade step recorded by the host.
-                const uint32_t bits = f32_to_bits(amax);
-                const int bexp = (int)(bits >> 23);  // 255 (inf) converts to 0x80000000 on x86: low byte 0
-                const int t = bexp ? bexp - 127 : (31 - __clz((int)(bits & 0x7fffffu))) - 149;
-                const int fl = (t >= -149 && t <= 127 && amax >= mx_steps[t + 149]) ? t + 1 : t;
-                // (uint8_t)(float): x86 converts through int32 and keeps the low byte.
-                e = bexp == 255 ? 0 : (fl - 2 + 127) & 0xFF;
-            }
+            const float amax = amax_nan<32>(x);
+            const int e = mxfp4_scale_byte(amax, mx_steps);
             const float d = e8m0_half_to_f32((uint8_t)e);
-            out[0] = (uint8_t)e;
-            pack_fp4<32>(x, amax, d, out + 1);
+            if (amax < kInf && e <= 252 && fp4_thresholds_valid(amax, d)) {
+                const float scale_rz = mx_scale_rz(e);
+                out[0] = (uint8_t)e;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    float lo[4], hi[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { lo[i] = mx_nudge(x[4 * w + i], scale_rz); hi[i] = mx_nudge(x[4 * w + i + 16], scale_rz); }
+                    st32(out + 1 + 4 * w, drop_negative_zero(cvt_e2m1x8(lo, hi)));
+                }
+            } else {
+                encode_exact<K>(xrow, out, mx_steps);
+            }
         } else {
-            // NVFP4, upstream nvfp4.cpp:16-55: this thread's 32 elements are sub-blocks 2h and 2h+1 of
-            // a 64-element block; its 18 staged bytes are 2 scale bytes followed by 16 quant bytes.
+            // NVFP4, upstream nvfp4.cpp:16-55: this thread's 32 elements are sub-blocks 2h and 2h+1 of the
+            // 64-element block blk, whose 36 bytes are 4 scale bytes followed by 4 x 8 quant bytes.
+            uint8_t *blk = tile + (threadIdx.x >> 1) * 36;
+            const int h = threadIdx.x & 1;
 #pragma unroll
             for (int sb = 0; sb < 2; ++sb) {
-                float amax = 0.0f;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(x[16 * sb + j]));
-                const uint8_t ue = f32_to_ue4m3(amax / 6.0f);
-                const float d = ue4m3_half_to_f32(ue);
-                out[sb] = ue;
-                pack_fp4<16>(x + 16 * sb, amax, d, out + 2 + 8 * sb);
+                const float *xs = x + 16 * sb;
+                uint8_t *scale_byte = blk + 2 * h + sb, *qs = blk + 4 + 16 * h + 8 * sb;
+                const float amax = amax_nan<16>(xs);
+                bool done = false;
+                if (amax < kInf) {
+                    const uint8_t ue = f32_to_ue4m3(amax / 6.0f);
+                    const float d = ue4m3_half_to_f32(ue);
+                    uint32_t words[2];
+                    if (fp4_thresholds_valid(amax, d)) {
+                        pack_fp4_bsearch<16>(xs, d, words);
+                        *scale_byte = ue;
+                        if (word_aligned) {
+                            reinterpret_cast<uint32_t *>(qs)[0] = words[0];
+                            reinterpret_cast<uint32_t *>(qs)[1] = words[1];
+                        } else {
+                            st32(qs, words[0]);
+                            st32(qs + 4, words[1]);
+                        }
+                        done = true;
+                    }
+                }
+                if (!done) encode_exact_nvfp4(xrow + 16 * sb, scale_byte, qs);
             }
         }
     }
     __syncthreads();
-    if constexpr (K == Simple::NVFP4) {
-        // un-interleave: block b = runs 2b, 2b+1 -> d[0..1] d[2..3] qs[0..15] qs[16..31]
-        __shared__ __align__(16) uint8_t shuffled[kBlockThreads * BYTES + 32];
-        uint8_t *tile2 = shuffled + (reinterpret_cast<uintptr_t>(gdst) & 15);
-        for (int i = threadIdx.x; i < nr * BYTES; i += kBlockThreads) {
-            const int run = i / BYTES, o = i - run * BYTES;
-            const int blk = run >> 1, h = run & 1;
-            const int pos = o < 2 ? 2 * h + o : 4 + 16 * h + (o - 2);
-            tile2[blk * 36 + pos] = tile[i];
-        }
-        __syncthreads();
-        flush_tile(tile2, gdst, nr * BYTES, threadIdx.x, kBlockThreads);
-    } else {
-        flush_tile(tile, gdst, nr * BYTES, threadIdx.x, kBlockThreads);
+    flush_tile(tile, gdst, nr * BYTES, threadIdx.x, kBlockThreads);
     }
 }
 
@@ -372,9 +660,17 @@ __global__ void __launch_bounds__(kThreads) store_kernel(const float *__restrict
 template <Simple K>
 cudaError_t launch32(const float *src, void *dst, int64_t nelems, const float *mx_steps, cudaStream_t stream) {
     const int64_t nruns = nelems / 32;
-    const int64_t grid = (nruns + kBlockThreads - 1) / kBlockThreads;
-    if (grid <= 0) return cudaSuccess;
-    if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const int64_t ntiles = (nruns + kBlockThreads - 1) / kBlockThreads;
+    if (ntiles <= 0) return cudaSuccess;
+    // persistent CTAs: as many as can be resident (5 per SM by shared memory), fewer for small inputs
+    static const int resident = [] {
+        int dev = 0, sms = 148, per_sm = 5;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant32_kernel<K>, kBlockThreads, 0);
+        return sms * (per_sm > 0 ? per_sm : 1);
+    }();
+    const int64_t grid = ntiles < resident ? ntiles : resident;
     quant32_kernel<K><<<(unsigned)grid, kBlockThreads, 0, stream>>>(src, static_cast<uint8_t *>(dst), nruns, mx_steps);
     count_launch();
     return cudaGetLastError();
@@ -396,10 +692,10 @@ cudaError_t launch_store(int type, const float *src, void *dst, int64_t nelems, 
     return cudaGetLastError();
 }
 
-// Counts the inputs (all 2^32 float bit patterns) for which the threshold form of the FP4 level
-// search differs from the 16-way scan at scale e.
-cudaError_t selftest_fp4(float e, unsigned long long *device_counter, cudaStream_t stream) {
-    selftest_fp4_kernel<<<148 * 8, 256, 0, stream>>>(e, device_counter);
+// Counts the inputs (all 2^32 float bit patterns) for which a fast form of the FP4 level search
+// differs from the 16-way scan at scale e; counters[0] = mismatches, counters[1] = fallbacks.
+cudaError_t selftest_fp4(float e, int mode, int ebyte, unsigned long long *device_counters, cudaStream_t stream) {
+    selftest_fp4_kernel<<<148 * 8, 256, 0, stream>>>(e, mode, ebyte, device_counters, device_counters + 1);
     count_launch();
     return cudaGetLastError();
 }

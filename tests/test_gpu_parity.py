@@ -176,3 +176,54 @@ def test_fp4_threshold_search_equals_the_scan_for_every_float():
         bad = ctypes.c_uint64(123)
         assert lib.libgguf_cuda_selftest_fp4(e, ctypes.byref(bad)) == 0
         assert bad.value == 0, (e, bad.value)
+
+
+def test_hardware_fp4_conversion_paths_equal_the_scan_for_every_float():
+    """The MXFP4 form (power-of-two scales, smallest to largest it is used for) and the NVFP4 form (UE4M3 scales with
+    and without mantissa bits) over all 2^32 inputs."""
+    import ctypes
+    from libgguf_b200._native import lib
+    for e in (2.0 ** -128, 2.0 ** -127, 2.0 ** -126, 2.0 ** -20, 0.5, 1.0, 2.0 ** 100, 2.0 ** 124):
+        bad = ctypes.c_uint64(123)
+        assert lib.libgguf_cuda_selftest_fp4_mode(e, 1, ctypes.byref(bad), None) == 0
+        assert bad.value == 0, (e, bad.value)
+    assert lib.libgguf_cuda_selftest_fp4_mode(3.0, 1, ctypes.byref(bad), None) != 0  # not a power of two
+    for e in (2.0 ** -10, 7 * 2.0 ** -10, 2.0 ** -7, 1.875 * 0.25, 0.5, 1.125, 224.0, 0.0068359375):
+        bad, fell = ctypes.c_uint64(123), ctypes.c_uint64(123)
+        assert lib.libgguf_cuda_selftest_fp4_mode(e, 2, ctypes.byref(bad), ctypes.byref(fell)) == 0
+        assert bad.value == 0, (e, bad.value)
+
+
+def _edge_rows(width=256):
+    """Blocks that leave the fast encoders: signed zeros, equal-magnitude extrema, denormal scales whose
+    reciprocal overflows, exact FP4 ties, infinities, and (last rows) NaN."""
+    rng = np.random.default_rng(11)
+    rows = []
+    z = np.zeros(width, np.float32); z[1::2] = -0.0; rows.append(z)
+    z = np.zeros(width, np.float32); z[0::3] = -0.0; z[5::7] = 1.25; rows.append(z)            # min is a zero
+    z = np.zeros(width, np.float32); z[0::3] = -0.0; z[5::7] = -1.25; z[2] = 0.0; rows.append(z)  # max is a zero
+    z = rng.standard_normal(width).astype(np.float32); z[3::32] = 4.0; z[9::32] = -4.0; rows.append(z)   # +a before -a
+    z = rng.standard_normal(width).astype(np.float32); z[3::32] = -4.0; z[9::32] = 4.0; rows.append(z)   # -a before +a
+    rows.append((rng.standard_normal(width) * 1e-42).astype(np.float32))
+    rows.append((rng.standard_normal(width) * 1e-38).astype(np.float32))
+    rows.append((rng.standard_normal(width) * 1e37).astype(np.float32))
+    ties = np.array([0.5, 1.5, 2.5, 3.5, 5.0, 7.0, 10.0, -0.5, -1.5, -2.5, -3.5, -5.0, -7.0, -10.0, 12.0, -12.0], np.float32)
+    for scale in (1.0, 0.25, 1.125, 0.0068359375):
+        z = np.tile(ties * np.float32(scale), width // 16).astype(np.float32)
+        rows.append(z)
+        rows.append(np.nextafter(z, np.float32(np.inf)).astype(np.float32))
+        rows.append(np.nextafter(z, np.float32(-np.inf)).astype(np.float32))
+    z = rng.standard_normal(width).astype(np.float32); z[7] = np.inf; z[40] = -np.inf; z[100] = np.inf; z[101] = -np.inf; rows.append(z)
+    finite = len(rows)
+    z = rng.standard_normal(width).astype(np.float32); z[5] = np.nan; z[63] = np.nan; z[64] = np.nan; z[200:232] = np.nan; rows.append(z)
+    z = rng.standard_normal(width).astype(np.float32) * 3; z[0] = 9.0; z[1] = np.nan; z[2] = 0.5; z[33] = -np.nan; z[34] = np.inf; rows.append(z)
+    return np.ascontiguousarray(np.stack(rows)), finite
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "MXFP4", "NVFP4"])
+def test_edge_blocks_of_the_32_element_types(gguf, checker, name):
+    qtype = inputs.QTYPES[name]
+    x, finite = _edge_rows()
+    got, want = gguf.quantize_rows(x, qtype), checker.quantize_rows(x, qtype)
+    for r in range(x.shape[0]):
+        assert np.array_equal(got[r], want[r]), (name, r, "finite" if r < finite else "with NaN")
