@@ -126,9 +126,10 @@ LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
  * inputs disagree (the quantizers rely on it being 0).  Blocking. */
 LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches);
 /* Same, for the forms the quantizers actually run.  mode 0: as above.  mode 1: the MXFP4 form, built on the hardware
- * E2M1 conversion (`scale` must be 2^(e-128) with integer 0 <= e <= 252).  mode 2: the NVFP4 form, a binary search
- * over the midpoints.  Modes 1 and 2 compare only the inputs the quantizers route there (finite, |x| <= 2^20 * scale).
- * `fallbacks` (may be null) is reserved and receives 0. */
+ * E2M1 conversion (`scale` must be 2^(e-128) with integer 0 <= e <= 252).  mode 2: the NVFP4 form, two hardware
+ * conversions bracketing the quotient; inputs whose two conversions differ (a tie lies within 2^-21 of the quotient)
+ * are redone by the exact search in the quantizer and are counted in `fallbacks` (may be null) here instead of being
+ * compared.  Modes 1 and 2 look only at the inputs the quantizers route there (finite, |x| <= 2^20 * scale). */
 LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4_mode(float scale, int mode, uint64_t *mismatches, uint64_t *fallbacks);
 
 /* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,

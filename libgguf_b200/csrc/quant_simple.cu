@@ -92,9 +92,41 @@ GGUF_D uint32_t drop_negative_zero(uint32_t w) {
 GGUF_D float mx_scale_rz(int ebyte) { return __uint_as_float(((uint32_t)(254 - ebyte) << 23) - 1u); }
 GGUF_D float mx_nudge(float x, float scale_rz) { return __uint_as_float(__float_as_uint(__fmul_rz(x, scale_rz)) | 1u); }
 
-// Any scale (NVFP4): the same answer as best_index_fp4_thresholds by a three-step binary search over
-// the seven midpoints t[k] = {0.5,1.5,2.5,3.5,5,7,10}[k] * e (exact products), which costs fewer
-// instructions than counting.  Returns the 4-bit code.
+// Any scale (NVFP4): the quotient x / (2e) is bracketed by two products that lie strictly on either
+// side of it (relative distance 2^-21, far above the error of the approximate reciprocal, about 2^-23,
+// and of the product).  The
+// scan's answer is monotone in the quotient and equals the conversion away from ties, so where both
+// ends convert to the same code that code is the answer; where they differ (a tie lies between the
+// ends, in practice: the input is a tie) the element is redone by the exact search.
+struct Fp4Bracket { float lo, hi; };
+GGUF_D Fp4Bracket fp4_bracket(float e) {
+    float inv;
+    asm("rcp.approx.f32 %0, %1;" : "=f"(inv) : "f"(e + e));  // e >= 2^-10: no denormal in or out
+    return {inv * 0.99999952316284179688f, inv * 1.00000047683715820312f};  // 1 -+ 2^-21
+}
+// bit 4n set when nibble n of v is not zero
+GGUF_D uint32_t nonzero_nibbles(uint32_t v) {
+    v |= v >> 1;
+    v |= v >> 2;
+    return v & 0x11111111u;
+}
+// Codes of elements x[0..3] (low nibbles) and y[0..3] (high nibbles) of four bytes; `undecided` gets
+// bit 4n set for every nibble n whose two conversions differ.
+GGUF_D uint32_t fp4_word_bracketed(const float *x, const float *y, const Fp4Bracket &k, uint32_t &undecided) {
+    float lo_a[4], hi_a[4], lo_b[4], hi_b[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        lo_a[i] = x[i] * k.lo;
+        hi_a[i] = y[i] * k.lo;
+        lo_b[i] = x[i] * k.hi;
+        hi_b[i] = y[i] * k.hi;
+    }
+    const uint32_t a = cvt_e2m1x8(lo_a, hi_a), b = cvt_e2m1x8(lo_b, hi_b);
+    undecided = nonzero_nibbles(a ^ b);
+    return drop_negative_zero(a);
+}
+// Any scale: the same answer as best_index_fp4_thresholds by a three-step binary search over the
+// seven midpoints t[k] = {0.5,1.5,2.5,3.5,5,7,10}[k] * e (exact products).  Returns the 4-bit code.
 struct Fp4Midpoints { float t[7]; };
 GGUF_D Fp4Midpoints fp4_midpoints(float e) {
     return {{0.5f * e, 1.5f * e, 2.5f * e, 3.5f * e, 5.f * e, 7.f * e, 10.f * e}};
@@ -110,24 +142,28 @@ GGUF_D uint32_t fp4_code_bsearch(float x, const Fp4Midpoints &k) {
     // sign bit, except on level 0: (idx + 7) & 8 is 8 exactly when idx >= 1
     return idx | ((__float_as_uint(x) >> 28) & (idx + 7u) & 8u);
 }
-// Codes of N elements, element j in the low and j + N/2 in the high nibble of byte j.
-template <int N>
-GGUF_D void pack_fp4_bsearch(const float *x, float e, uint32_t *words) {
+// Redoes the undecided elements of a 16-element sub-block whose 8 code bytes are in shared memory.
+// x: the sub-block's elements (shared memory); mask: bit 4n of `lo` / `hi` set for nibble n of the first /
+// second four bytes (byte n/2, high half when n is odd; the high halves hold elements 8..15).
+// Only valid scales reach this function (fp4_thresholds_valid).
+__device__ __noinline__ void fp4_fix_subblock(const float *x, uint8_t *bytes, uint32_t lo, uint32_t hi, float e) {
     const Fp4Midpoints k = fp4_midpoints(e);
-#pragma unroll
-    for (int w = 0; w < N / 8; ++w) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            word += fp4_code_bsearch(x[4 * w + i], k) << (8 * i);
-            word += fp4_code_bsearch(x[4 * w + i + N / 2], k) << (8 * i + 4);
+#pragma unroll 1
+    for (int w = 0; w < 2; ++w) {
+        uint32_t undecided = w ? hi : lo;
+        while (undecided) {
+            const int n = (__ffs((int)undecided) - 1) >> 2;
+            undecided &= undecided - 1;
+            const uint32_t code = fp4_code_bsearch(x[4 * w + (n >> 1) + 8 * (n & 1)], k);
+            uint8_t &byte = bytes[4 * w + (n >> 1)];
+            byte = (n & 1) ? (uint8_t)((byte & 0x0F) | (code << 4)) : (uint8_t)((byte & 0xF0) | code);
         }
-        words[w] = word;
     }
 }
 
 // mode 0: threshold search against the scan.  mode 1: power-of-two-scale hardware path (e is
-// 2^(ebyte-128), ebyte <= 252).  mode 2: binary search over the midpoints.  Modes 1 and 2 only look at the
+// 2^(ebyte-128), ebyte <= 252).  mode 2: bracketed hardware path; inputs it leaves to the
+// exact search are counted in `fallbacks`, not compared.  Modes 1 and 2 only look at the
 // inputs the quantizers send down those paths (|x| <= 2^20 * e).
 __global__ void selftest_fp4_kernel(float e, int mode, int ebyte, unsigned long long *mismatches, unsigned long long *fallbacks) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
@@ -147,16 +183,17 @@ __global__ void selftest_fp4_kernel(float e, int mode, int ebyte, unsigned long 
             if ((int)(drop_negative_zero(cvt_e2m1x8(lo, hi)) & 0xFu) != want) ++bad;
         } else {
             float xs[8] = {x, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            uint32_t word;
-            pack_fp4_bsearch<8>(xs, e, &word);
-            if ((int)(word & 0xFu) != want) ++bad;
+            uint32_t undecided;
+            const uint32_t word = fp4_word_bracketed(xs, xs + 4, fp4_bracket(e), undecided);
+            if (undecided & 1u) ++fell;
+            else if ((int)(word & 0xFu) != want) ++bad;
         }
     }
     if (bad) atomicAdd(mismatches, bad);
     if (fell) atomicAdd(fallbacks, fell);
 }
 
-enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4, NVFP4 };
+enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4, NVFP4, Q1_0 };
 
 template <Simple K> struct SimpleGeom;
 template <> struct SimpleGeom<Simple::Q8_0> { static constexpr int BYTES = 34; };   // bytes per 32 elements
@@ -166,6 +203,9 @@ template <> struct SimpleGeom<Simple::Q5_0> { static constexpr int BYTES = 22; }
 template <> struct SimpleGeom<Simple::Q5_1> { static constexpr int BYTES = 24; };
 template <> struct SimpleGeom<Simple::MXFP4> { static constexpr int BYTES = 17; };
 template <> struct SimpleGeom<Simple::NVFP4> { static constexpr int BYTES = 18; };  // half of a 64-element block
+// Q1_0: a 128-element block (18 bytes) is four runs; BYTES is not used for it
+template <> struct SimpleGeom<Simple::Q1_0> { static constexpr int BYTES = 0; };
+template <Simple K> constexpr int kBytesPer4Runs = K == Simple::Q1_0 ? 18 : 4 * SimpleGeom<K>::BYTES;
 
 GGUF_D void st16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }
 GGUF_D void st32(uint8_t *p, uint32_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); p[2] = (uint8_t)(v >> 16); p[3] = (uint8_t)(v >> 24); }
@@ -360,7 +400,8 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
                                                                int64_t nruns, const float *__restrict__ mx_steps) {
     constexpr int BYTES = SimpleGeom<K>::BYTES;
     __shared__ __align__(16) float xbuf[2][kBlockThreads * kRowStride];
-    __shared__ __align__(16) uint8_t stage[kBlockThreads * BYTES + 32];
+    constexpr int BYTES4 = kBytesPer4Runs<K>;
+    __shared__ __align__(16) uint8_t stage[kBlockThreads / 4 * BYTES4 + 32];
 
     const int64_t ntiles = (nruns + kBlockThreads - 1) / kBlockThreads;
     const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(dst) & 15);  // a tile starts a multiple of 16 bytes into dst
@@ -393,8 +434,8 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
     __syncthreads();  // tile t is in xin; every thread is done with the previous tile's stage
     const int64_t r0 = t * kBlockThreads;
     const int nr = (int)(nruns - r0 < kBlockThreads ? nruns - r0 : kBlockThreads);
-    uint8_t *gdst = dst + r0 * BYTES;
-    if (threadIdx.x < nr) {
+    uint8_t *gdst = dst + r0 / 4 * BYTES4;   // r0 is a multiple of 128
+    if (K == Simple::Q1_0 || threadIdx.x < nr) {
         const float *xrow = xin + threadIdx.x * kRowStride;
         float x[32];
 #pragma unroll
@@ -403,7 +444,36 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
             x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
         }
         uint8_t *out = tile + threadIdx.x * BYTES;
-        if constexpr (K == Simple::Q8_0) {
+        if constexpr (K == Simple::Q1_0) {
+            // upstream q1_0.cpp:16-55: d = (sum of |x| over the 128 elements, added in element order) / 128, one
+            // bit per element (x >= 0).  The block's four runs sit in four neighbouring lanes; the sum is
+            // handed from lane to lane, every lane adding its 32 magnitudes to what it receives.
+            // Rows past the end of a short last tile hold stale data and are computed but not stored
+            // (all 32 lanes take part in the shuffles).
+            const int lane = threadIdx.x & 31, part = threadIdx.x & 3;
+            float total = 0.f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                float t = __shfl_sync(kFull, total, (lane & ~3) | ((p + 3) & 3));
+                if (p == 0) t = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) t += fabsf(x[j]);
+                if (part == p) total = t;
+            }
+            uint32_t bits = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) bits |= (x[j] >= 0.0f ? 1u : 0u) << j;
+            if (threadIdx.x < nr) {
+                uint8_t *blk = tile + (threadIdx.x >> 2) * 18;
+                if (even) {
+                    reinterpret_cast<uint16_t *>(blk + 2 + 4 * part)[0] = (uint16_t)bits;
+                    reinterpret_cast<uint16_t *>(blk + 2 + 4 * part)[1] = (uint16_t)(bits >> 16);
+                } else {
+                    st32(blk + 2 + 4 * part, bits);
+                }
+                if (part == 3) st16(blk, f32_to_half_bits(total / 128.0f));
+            }
+        } else if constexpr (K == Simple::Q8_0) {
             const float amax = amax_nan<32>(x);
             const float d = amax / 127.0f;
             const float id = d ? 1.0f / d : 0.0f;
@@ -532,9 +602,11 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
                 if (amax < kInf) {
                     const uint8_t ue = f32_to_ue4m3(amax / 6.0f);
                     const float d = ue4m3_half_to_f32(ue);
-                    uint32_t words[2];
                     if (fp4_thresholds_valid(amax, d)) {
-                        pack_fp4_bsearch<16>(xs, d, words);
+                        const Fp4Bracket k = fp4_bracket(d);
+                        uint32_t undecided[2], words[2];
+#pragma unroll
+                        for (int w = 0; w < 2; ++w) words[w] = fp4_word_bracketed(xs + 4 * w, xs + 4 * w + 8, k, undecided[w]);
                         *scale_byte = ue;
                         if (word_aligned) {
                             reinterpret_cast<uint32_t *>(qs)[0] = words[0];
@@ -543,6 +615,7 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
                             st32(qs, words[0]);
                             st32(qs + 4, words[1]);
                         }
+                        if (undecided[0] | undecided[1]) fp4_fix_subblock(xrow + 16 * sb, qs, undecided[0], undecided[1], d);
                         done = true;
                     }
                 }
@@ -551,39 +624,54 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
         }
     }
     __syncthreads();
-    flush_tile(tile, gdst, nr * BYTES, threadIdx.x, kBlockThreads);
+    flush_tile(tile, gdst, nr * BYTES4 / 4, threadIdx.x, kBlockThreads);
     }
 }
 
-// Q1_0: 128-element blocks, d = mean |x| with the sum taken in element order, one sign bit per
-// element (upstream q1_0.cpp:16-55).  One warp per block: lanes publish |x| to shared memory,
-// lane 0 adds them in order, sign bits come from ballots.
-__global__ void __launch_bounds__(kThreads) quant_q1_0_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
-                                                             int64_t nblocks) {
-    __shared__ float absx[kThreads / 32][128];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t blk = (int64_t)blockIdx.x * (kThreads / 32) + warp;
-    if (blk >= nblocks) return;
-    const float *x = src + blk * 128;
-    uint8_t *out = dst + blk * 18;
-    uint32_t sign_words[4];
+// lroundf(x * id) + 1.  With a finite id the product lies in [-1, 1] (or is NaN, which upstream's
+// conversion turns into digit 1) and rounding half away from zero is two comparisons; the library
+// call is kept for blocks whose scale is so small that 1 / d overflows.
+template <bool FINITE>
+GGUF_D int trit(float x, float id) {
+    const float v = x * id;
+    if (FINITE) return 1 + (v >= 0.5f ? 1 : 0) - (v <= -0.5f ? 1 : 0);
+    return (int)lroundf(v) + 1;
+}
+
+template <bool TQ1, bool FINITE>
+GGUF_D void ternary_pack(const float *xb, uint8_t *out, int lane, float d, float id) {
+    if constexpr (TQ1) {
+        {   // 32 bytes, 5 trits each, elements n*32 + lane
+            int q = 0;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float v = x[k * 32 + lane];
-        absx[warp][k * 32 + lane] = fabsf(v);
-        sign_words[k] = __ballot_sync(kFull, v >= 0.0f);
+            for (int n = 0; n < 5; ++n) q = (q * 3 + trit<FINITE>(xb[n * 32 + lane], id)) & 0xFF;
+            out[lane] = (uint8_t)((q * 256 + 242) / 243);
+        }
+        if (lane < 16) {  // 16 bytes, elements 160 + n*16 + lane
+            int q = 0;
+#pragma unroll
+            for (int n = 0; n < 5; ++n) q = (q * 3 + trit<FINITE>(xb[160 + n * 16 + lane], id)) & 0xFF;
+            out[32 + lane] = (uint8_t)((q * 256 + 242) / 243);
+        }
+        if (lane < 4) {  // 4 bytes, 4 trits each, elements 240 + m*4 + lane, then one more *3
+            int q = 0;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) q = (q * 3 + trit<FINITE>(xb[240 + m * 4 + lane], id)) & 0xFF;
+            q = (q * 3) & 0xFF;
+            out[48 + lane] = (uint8_t)((q * 256 + 242) / 243);
+        }
+        if (lane == 0) st16(out + 52, f32_to_half_bits(d));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            int q = 0;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) q += (trit<FINITE>(xb[j * 128 + n * 32 + lane], id) & 3) << (2 * n);
+            out[j * 32 + lane] = (uint8_t)q;
+        }
+        if (lane == 0) st16(out + 64, f32_to_half_bits(d));
     }
-    __syncwarp();
-    if (lane == 0) {
-        float sum_abs = 0.0f;
-        for (int j = 0; j < 128; ++j) sum_abs += absx[warp][j];
-        st16(out, f32_to_half_bits(sum_abs / 128.0f));
-    }
-    if (lane < 16) out[2 + lane] = (uint8_t)(sign_words[lane >> 2] >> (8 * (lane & 3)));
 }
-
-// lroundf(v) for |v| <= 1 results in {-1,0,1}; kept as the library call for exact tie behaviour.
-GGUF_D int trit(float v, float id) { return (int)lroundf(v * id) + 1; }
 
 // TQ1_0 / TQ2_0: 256-element blocks, d = max |x| (upstream tq1_0.cpp:16-98, tq2_0.cpp:16-53).
 // One warp per block; the block is staged in shared memory because each output byte mixes
@@ -610,38 +698,8 @@ __global__ void __launch_bounds__(kThreads) quant_ternary_kernel(const float *__
     __syncwarp();
     const float d = amax;
     const float id = d ? 1.0f / d : 0.0f;
-    const float *xb = xs[warp];
-    if constexpr (TQ1) {
-        {   // 32 bytes, 5 trits each, elements n*32 + lane
-            int q = 0;
-#pragma unroll
-            for (int n = 0; n < 5; ++n) q = (q * 3 + trit(xb[n * 32 + lane], id)) & 0xFF;
-            out[lane] = (uint8_t)((q * 256 + 242) / 243);
-        }
-        if (lane < 16) {  // 16 bytes, elements 160 + n*16 + lane
-            int q = 0;
-#pragma unroll
-            for (int n = 0; n < 5; ++n) q = (q * 3 + trit(xb[160 + n * 16 + lane], id)) & 0xFF;
-            out[32 + lane] = (uint8_t)((q * 256 + 242) / 243);
-        }
-        if (lane < 4) {  // 4 bytes, 4 trits each, elements 240 + m*4 + lane, then one more *3
-            int q = 0;
-#pragma unroll
-            for (int m = 0; m < 4; ++m) q = (q * 3 + trit(xb[240 + m * 4 + lane], id)) & 0xFF;
-            q = (q * 3) & 0xFF;
-            out[48 + lane] = (uint8_t)((q * 256 + 242) / 243);
-        }
-        if (lane == 0) st16(out + 52, f32_to_half_bits(d));
-    } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            int q = 0;
-#pragma unroll
-            for (int n = 0; n < 4; ++n) q += (trit(xb[j * 128 + n * 32 + lane], id) & 3) << (2 * n);
-            out[j * 32 + lane] = (uint8_t)q;
-        }
-        if (lane == 0) st16(out + 64, f32_to_half_bits(d));
-    }
+    if (id < kInfinity) ternary_pack<TQ1, true>(xs[warp], out, lane, d, id);
+    else ternary_pack<TQ1, false>(xs[warp], out, lane, d, id);
 }
 
 // Plain storage types: fp32 copy, fp16 and bf16 conversion with upstream's rounding and NaN
@@ -711,13 +769,7 @@ cudaError_t launch_quantize_simple(int type, const float *src, void *dst, int64_
         case GGML_TYPE_Q5_1: return launch32<Simple::Q5_1>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_MXFP4: return launch32<Simple::MXFP4>(src, dst, nelems, mx_steps, stream);
         case GGML_TYPE_NVFP4: return launch32<Simple::NVFP4>(src, dst, nelems, nullptr, stream);
-        case GGML_TYPE_Q1_0: {
-            const int64_t nblocks = nelems / 128;
-            if (nblocks <= 0) return cudaSuccess;
-            quant_q1_0_kernel<<<(unsigned)((nblocks + 7) / 8), kThreads, 0, stream>>>(src, out, nblocks);
-            count_launch();
-            return cudaGetLastError();
-        }
+        case GGML_TYPE_Q1_0: return launch32<Simple::Q1_0>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_TQ1_0:
         case GGML_TYPE_TQ2_0: {
             const int64_t nblocks = nelems / 256;

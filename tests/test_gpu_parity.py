@@ -192,6 +192,7 @@ def test_hardware_fp4_conversion_paths_equal_the_scan_for_every_float():
         bad, fell = ctypes.c_uint64(123), ctypes.c_uint64(123)
         assert lib.libgguf_cuda_selftest_fp4_mode(e, 2, ctypes.byref(bad), ctypes.byref(fell)) == 0
         assert bad.value == 0, (e, bad.value)
+        assert fell.value < 2000, (e, fell.value)  # a few bit patterns around each of the 14 signed ties
 
 
 def _edge_rows(width=256):
