@@ -825,6 +825,8 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
     const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
     const int nvec = (nb * D::BYTES + 15) >> 4;
     uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+    grid_dependents_may_launch();
+    grid_dependency_wait();
 #pragma unroll
     for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
         const int i = k * kThreads + tid;
@@ -866,10 +868,10 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
     const int aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
     if constexpr (Fast<TYPE>::kEnabled) {
         if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-            dequant_fast_kernel<TYPE, OutT><<<(unsigned)grid, kThreads, 0, stream>>>(static_cast<const uint8_t *>(src),
-                                                                                   static_cast<OutT *>(dst), nblocks);
+            const cudaError_t launched = launch_overlapped(dequant_fast_kernel<TYPE, OutT>, (unsigned)grid, kThreads, stream,
+                                                           static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks);
             count_launch();
-            return cudaGetLastError();
+            return launched != cudaSuccess ? launched : cudaGetLastError();
         }
     }
     dequant_tile_kernel<TYPE, OutT><<<(unsigned)grid, kThreads, 0, stream>>>(static_cast<const uint8_t *>(src),

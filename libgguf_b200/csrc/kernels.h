@@ -15,6 +15,32 @@ bool quantize_supported(int type);
 
 // Launch accounting (exposed through libgguf_cuda_kernel_launch_count).
 void count_launch();
+
+#ifdef __CUDACC__
+// Programmatic dependent launch.  A kernel started with launch_overlapped() may become resident while
+// the previous kernel of the stream is still draining; it must call grid_dependency_wait() before its
+// first access to global memory (the call returns once the previous kernel has completed and its
+// writes are visible, or at once when there is nothing to wait for), so stream order is kept.
+// grid_dependents_may_launch() tells the scheduler that the kernel after this one may start to be
+// placed on SMs as they become free.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(block);
+    config.dynamicSmemBytes = 0;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 uint64_t launch_count();
 
 }  // namespace gguf

@@ -421,6 +421,8 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
     };
 
     int64_t t = blockIdx.x;
+    grid_dependents_may_launch();
+    grid_dependency_wait();
     if (t < ntiles) prefetch(t, xbuf[0]);
     for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
     float *xin = xbuf[it & 1];
@@ -729,9 +731,10 @@ cudaError_t launch32(const float *src, void *dst, int64_t nelems, const float *m
         return sms * (per_sm > 0 ? per_sm : 1);
     }();
     const int64_t grid = ntiles < resident ? ntiles : resident;
-    quant32_kernel<K><<<(unsigned)grid, kBlockThreads, 0, stream>>>(src, static_cast<uint8_t *>(dst), nruns, mx_steps);
+    const cudaError_t launched = launch_overlapped(quant32_kernel<K>, (unsigned)grid, kBlockThreads, stream, src,
+                                                   static_cast<uint8_t *>(dst), nruns, mx_steps);
     count_launch();
-    return cudaGetLastError();
+    return launched != cudaSuccess ? launched : cudaGetLastError();
 }
 
 }  // namespace
