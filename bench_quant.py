@@ -74,6 +74,8 @@ def run(args, torch, dist, lib, ops, device, rank, world):
     wl = args.workload
     if wl == "convert":
         return run_convert(args, torch, dist, lib, device, rank, world, hbm)
+    if wl == "dequant_all":
+        return run_dequant_all(args, torch, lib, ops, device, rank, world, hbm, peak_kind)
     shapes = {"q4k_roundtrip": (4096, 4096, "normal", ["Q4_K"], False),
               "kquant": (14336, 4096, "normal", ["Q8_0", "Q6_K", "Q5_K", "Q4_K", "Q3_K", "Q2_K"], False),
               "legacy": (14336, 4096, "normal", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q1_0", "TQ1_0", "TQ2_0", "IQ4_NL", "IQ4_XS"], False),
@@ -146,6 +148,49 @@ def run(args, torch, dist, lib, ops, device, rank, world):
             "config": {"workload": f"{wl} {rows}x{cols} {kind}{' +imatrix' if weighted else ''}: {','.join(types)}",
                        "l2": f"{NSETS} rotating input/output buffer sets per kernel"},
             "clocks": clocks, "gpu_launches": int(launches), "per_qtype": table, "peak_source": peak_kind}))
+
+
+def run_dequant_all(args, torch, lib, ops, device, rank, world, hbm, peak_kind):
+    """Decode throughput of every block type, 14336x4096 (or --rows) -> fp16, inputs resident in HBM."""
+    import bench
+    rows, cols = args.rows, 4096
+    stream = torch.cuda.current_stream(device)
+    g = torch.Generator(device=device)
+    g.manual_seed(0)
+    x = torch.randn((rows, cols), generator=g, device=device) * 0.02
+    im = (torch.randn(cols, generator=g, device=device) ** 2 + 0.1).contiguous()
+    table = {}
+    reps = max(1, args.steps)
+    launches0 = lib.libgguf_cuda_kernel_launch_count()
+    for name in sorted(CODE, key=lambda n: CODE[n]):
+        code, (bel, bby) = CODE[name], BLOCK[name]
+        enc = [ops.quantize(x, code, imatrix=im if name.startswith("IQ") else None)]
+        enc += [enc[0].clone() for _ in range(NSETS - 1)]
+        outs = [torch.empty((rows, cols), dtype=torch.float16, device=device) for _ in range(NSETS)]
+
+        def dequant(k):
+            st = lib.libgguf_cuda_dequantize_rows_on_stream(enc[k % NSETS].data_ptr(), code, rows, cols, 1,
+                                                            outs[k % NSETS].data_ptr(), stream.cuda_stream)
+            if st != 0:
+                raise RuntimeError(lib.libgguf_cuda_thread_last_error().decode())
+
+        for k in range(3):
+            dequant(k)
+        torch.cuda.synchronize()
+        ms = _time_launches(torch, stream, dequant, reps)
+        nbytes = enc[0].numel() + rows * cols * 2
+        table[name] = {"ms": round(ms, 4), "GB/s": round(nbytes / ms / 1e6, 1), "hbm_frac": round(nbytes / ms / 1e6 / hbm, 4)}
+        del enc, outs
+    if rank == 0:
+        print(json.dumps({"metric": "dequant GB/s per type", "value": statistics_mean([v["GB/s"] for v in table.values()]), "unit": "GB/s",
+                          "n_gpus": world, "steps": reps, "warmup": 3, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": f"dequant_all {rows}x{cols} -> fp16, {NSETS} rotating buffer sets"},
+                          "gpu_launches": int(lib.libgguf_cuda_kernel_launch_count() - launches0), "per_qtype": table, "peak_source": peak_kind}))
+
+
+def statistics_mean(values):
+    values = list(values)
+    return sum(values) / len(values)
 
 
 def run_convert(args, torch, dist, lib, device, rank, world, hbm):

@@ -540,6 +540,13 @@ GGUF_D void scale_min_words(int j, uint32_t s0, uint32_t s1, uint32_t s2, int &s
 template <int TYPE>
 struct Fast { static constexpr bool kEnabled = false; };
 
+// Elements one run() call decodes: 16, or 32 for the types whose bytes hold elements j and j + 16
+// (one 16-byte load then feeds both halves).
+template <class D, class = void>
+struct CallElems { static constexpr int value = 16; };
+template <class D>
+struct CallElems<D, decltype((void)D::CALL)> { static constexpr int value = D::CALL; };
+
 // Each Fast<T>: ELEMS/BYTES of a block, GROUP = elements sharing one constant pair,
 // prep(block, group index in block) and run(block, e0 (multiple of 16), constants, v[16]).
 template <>
@@ -636,27 +643,53 @@ struct Fast<GGML_TYPE_Q2_K> {
     }
 };
 
-// E2M1 magnitudes times two, as bytes of a 64-bit table indexed by PRMT; negative levels are
-// formed as 0 - m so that code 8 decodes to +0 like the int8 table entry does.
-GGUF_D float fp4_level(uint32_t nib) {
-    const uint32_t mag = __byte_perm(0x03020100u, 0x0C080604u, nib & 7u);
-    const float m = __uint_as_float(mag | 0x4B000000u) - kTwo23;
-    return (nib & 8u) ? 0.f - m : m;
+// Sixteen-entry byte table lookup for four 4-bit indices at once.  `nibs`: the indices in the low 16
+// bits; table entries 0..7 in the bytes of (lo0, lo1), 8..15 in (hi0, hi1).  Two permutes look the low
+// three index bits up in either half, a third picks per byte by the index's top bit.
+GGUF_D uint32_t lut16x4(uint32_t nibs, uint32_t lo0, uint32_t lo1, uint32_t hi0, uint32_t hi1) {
+    const uint32_t sel = nibs & 0x7777u;
+    const uint32_t a = __byte_perm(lo0, lo1, sel), b = __byte_perm(hi0, hi1, sel);
+    return __byte_perm(a, b, ((nibs >> 1) & 0x4444u) | 0x3210u);
+}
+// Table of sixteen int8 levels stored with an offset of 128 so that the bytes are unsigned.
+struct Lut16 { uint32_t lo0, lo1, hi0, hi1; };
+GGUF_HD constexpr uint32_t pack_levels(int a, int b, int c, int d) {
+    return (uint32_t)(a + 128) | ((uint32_t)(b + 128) << 8) | ((uint32_t)(c + 128) << 16) | ((uint32_t)(d + 128) << 24);
+}
+// E2M1 levels times two (code 8, "-0", decodes to 0 like the int8 table entry) and the IQ4 levels.
+GGUF_D constexpr Lut16 fp4_lut() { return {pack_levels(0, 1, 2, 3), pack_levels(4, 6, 8, 12), pack_levels(0, -1, -2, -3), pack_levels(-4, -6, -8, -12)}; }
+GGUF_D constexpr Lut16 iq4_lut() { return {pack_levels(-127, -104, -83, -65), pack_levels(-49, -35, -22, -10), pack_levels(1, 13, 25, 38),
+                           pack_levels(53, 69, 89, 113)}; }
+
+// 16 bytes of packed 4-bit codes, byte j = code(j) | code(j + HALF) << 4, through a level table:
+// v[j] = scale * level(code(j)) for j < 16 and v[HALF_OUT + j] for the high nibbles.
+// Word k, low half: codes of elements (4k, 4k+H, 4k+1, 4k+H+1); high half: (4k+2, 4k+H+2, 4k+3, 4k+H+3).
+template <int WORDS, int HIGH_AT>
+GGUF_D void lut_decode(const uint32_t *w, const Lut16 t, float scale, float *v) {
+    const float2 nb = make_float2(-(kTwo23 + 128.f), -(kTwo23 + 128.f)), sc = make_float2(scale, scale);
+#pragma unroll
+    for (int k = 0; k < WORDS; ++k) {
+        const uint32_t r0 = lut16x4(w[k], t.lo0, t.lo1, t.hi0, t.hi1), r1 = lut16x4(w[k] >> 16, t.lo0, t.lo1, t.hi0, t.hi1);
+        float2 lo01 = make_float2(magic_byte(r0, 0), magic_byte(r0, 2)), hi01 = make_float2(magic_byte(r0, 1), magic_byte(r0, 3));
+        float2 lo23 = make_float2(magic_byte(r1, 0), magic_byte(r1, 2)), hi23 = make_float2(magic_byte(r1, 1), magic_byte(r1, 3));
+        lo01 = __fmul2_rn(sc, __fadd2_rn(lo01, nb));
+        hi01 = __fmul2_rn(sc, __fadd2_rn(hi01, nb));
+        lo23 = __fmul2_rn(sc, __fadd2_rn(lo23, nb));
+        hi23 = __fmul2_rn(sc, __fadd2_rn(hi23, nb));
+        v[4 * k] = lo01.x; v[4 * k + 1] = lo01.y; v[4 * k + 2] = lo23.x; v[4 * k + 3] = lo23.y;
+        v[HIGH_AT + 4 * k] = hi01.x; v[HIGH_AT + 4 * k + 1] = hi01.y; v[HIGH_AT + 4 * k + 2] = hi23.x; v[HIGH_AT + 4 * k + 3] = hi23.y;
+    }
 }
 
 template <>
 struct Fast<GGML_TYPE_MXFP4> {
     static constexpr bool kEnabled = true;
-    static constexpr int ELEMS = 32, BYTES = 17, GROUP = 32;
+    static constexpr int ELEMS = 32, BYTES = 17, GROUP = 32, CALL = 32;
     static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(e8m0_half_to_f32(b[0]), 0.f); }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) {
         const uint4 q = lds16_any(b + 1);
-        const int sh = e0 ? 4 : 0;
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) v[4 * k + i] = fp4_level((w[k] >> (8 * i + sh)) & 0xFu) * c.x;
+        lut_decode<4, 16>(w, fp4_lut(), c.x, v);
     }
 };
 
@@ -666,15 +699,93 @@ struct Fast<GGML_TYPE_NVFP4> {
     static constexpr int ELEMS = 64, BYTES = 36, GROUP = 16;
     static GGUF_D float2 prep(const uint8_t *b, int g) { return make_float2(ue4m3_half_to_f32(b[g]), 0.f); }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
-        const uint32_t *w = reinterpret_cast<const uint32_t *>(b + 4 + (e0 >> 4) * 8);
-        const uint32_t q[2] = {w[0], w[1]};
+        const uint32_t *p = reinterpret_cast<const uint32_t *>(b + 4 + (e0 >> 4) * 8);
+        const uint32_t w[2] = {p[0], p[1]};
+        lut_decode<2, 8>(w, fp4_lut(), c.x, v);
+    }
+};
+
+// upstream dequant.cpp (iq4_nl): y[j] = d * kvalues[qs[j] & 0xf], y[j + 16] = d * kvalues[qs[j] >> 4]
+template <>
+struct Fast<GGML_TYPE_IQ4_NL> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 18, GROUP = 32, CALL = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) {
+        const uint4 q = lds16_any(b + 2);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        lut_decode<4, 16>(w, iq4_lut(), c.x, v);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_IQ4_XS> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 136, GROUP = 32, CALL = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int ib) {
+        const uint32_t scales_h = lds_u16(b + 2);
+        const int ls = ((b[4 + (ib >> 1)] >> (4 * (ib & 1))) & 0xF) | (((scales_h >> (2 * ib)) & 3) << 4);
+        return make_float2(half_hw(lds_u16(b)) * (float)(ls - 32), 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint4 q = lds16_a4(b + 8 + (e0 >> 5) * 16);  // 136-byte blocks: 8-byte aligned
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        lut_decode<4, 16>(w, iq4_lut(), c.x, v);
+    }
+};
+
+// Legacy 4/5-bit types: byte j holds elements j and j + 16.
+// Fifth bits of four consecutive elements (bits 0..3 of `bits`) moved to bit 4 of four bytes.
+GGUF_D uint32_t spread_bit4(uint32_t bits) { return (((bits & 0xFu) * 0x00204081u) & 0x01010101u) << 4; }
+
+template <bool FIVE, bool HAS_MIN>
+GGUF_D void legacy_run(const uint8_t *qs, uint32_t qh, float2 c, float *v) {
+    const uint4 q = lds16_any(qs);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    const float neg_bias = -(kTwo23 + (HAS_MIN ? 0.f : (FIVE ? 16.f : 8.f)));
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                v[4 * k + i] = fp4_level((q[k] >> (8 * i)) & 0xFu) * c.x;
-                v[8 + 4 * k + i] = fp4_level((q[k] >> (8 * i + 4)) & 0xFu) * c.x;
-            }
+    for (int k = 0; k < 4; ++k) {
+        uint32_t lo = w[k] & 0x0F0F0F0Fu, hi = (w[k] >> 4) & 0x0F0F0F0Fu;
+        if (FIVE) {
+            lo |= spread_bit4(qh >> (4 * k));
+            hi |= spread_bit4(qh >> (16 + 4 * k));
+        }
+        affine4<HAS_MIN>(lo, neg_bias, c, v + 4 * k);
+        affine4<HAS_MIN>(hi, neg_bias, c, v + 16 + 4 * k);
+    }
+}
+
+template <>
+struct Fast<GGML_TYPE_Q4_0> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 18, GROUP = 32, CALL = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) { legacy_run<false, false>(b + 2, 0, c, v); }
+};
+template <>
+struct Fast<GGML_TYPE_Q4_1> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 20, GROUP = 32, CALL = 32;
+    // x * d + m: affine4 subtracts its second constant
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), -half_hw(lds_u16(b + 2))); }
+    static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) { legacy_run<false, true>(b + 4, 0, c, v); }
+};
+template <>
+struct Fast<GGML_TYPE_Q5_0> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 22, GROUP = 32, CALL = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) {
+        legacy_run<true, false>(b + 6, lds_u16(b + 2) | (lds_u16(b + 4) << 16), c, v);
+    }
+};
+template <>
+struct Fast<GGML_TYPE_Q5_1> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 32, BYTES = 24, GROUP = 32, CALL = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), -half_hw(lds_u16(b + 2))); }
+    static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) {
+        legacy_run<true, true>(b + 8, *reinterpret_cast<const uint32_t *>(b + 4), c, v);
     }
 };
 
@@ -754,6 +865,8 @@ __global__ void __launch_bounds__(kThreads) dequant_tile_kernel(const uint8_t *_
     const uint4 *g16 = reinterpret_cast<const uint4 *>(gsrc - mis);
     const int nvec = (mis + nbytes + 15) >> 4;
     uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+    grid_dependents_may_launch();
+    grid_dependency_wait();
     for (int i = threadIdx.x; i < nvec; i += kThreads) s16[i] = __ldcs(g16 + i);
     __syncthreads();
 
@@ -813,9 +926,6 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
     constexpr int TILE_VECS = (TILE_BYTES + 15) / 16;
     constexpr int TILE_GROUPS = kTileElems / D::GROUP;
     constexpr int GROUPS_PER_BLOCK = D::ELEMS / D::GROUP;
-    constexpr int CHUNKS_PER_BLOCK = D::ELEMS / 16;
-    constexpr int CHUNKS_PER_THREAD = kTileElems / 16 / kThreads;  // 2
-    static_assert(kThreads % CHUNKS_PER_BLOCK == 0, "a thread keeps its position inside the block across iterations");
     __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 32];
     __shared__ float2 consts[TILE_GROUPS];
 
@@ -840,19 +950,24 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
         if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
     }
     __syncthreads();
-    // chunk c = u*kThreads + tid: position inside the block (e0) does not depend on u
-    const int e0 = (tid % CHUNKS_PER_BLOCK) * 16;
-    const int blk0 = tid / CHUNKS_PER_BLOCK;
+    // call c = u*kThreads + tid: position inside the block (e0) does not depend on u
+    constexpr int CALL = CallElems<D>::value;
+    constexpr int CALLS_PER_BLOCK = D::ELEMS / CALL;
+    constexpr int CALLS_PER_THREAD = kTileElems / CALL / kThreads;  // 2 or 1
+    static_assert(kThreads % CALLS_PER_BLOCK == 0, "a thread keeps its position inside the block across iterations");
+    const int e0 = (tid % CALLS_PER_BLOCK) * CALL;
+    const int blk0 = tid / CALLS_PER_BLOCK;
     OutT *out = dst + b0 * D::ELEMS + (int64_t)blk0 * D::ELEMS + e0;
     const uint8_t *bp = tile + blk0 * D::BYTES;
     const float2 *cp = consts + (blk0 * D::ELEMS + e0) / D::GROUP;
 #pragma unroll
-    for (int u = 0; u < CHUNKS_PER_THREAD; ++u) {
-        constexpr int BLOCK_STEP = kThreads / CHUNKS_PER_BLOCK;
+    for (int u = 0; u < CALLS_PER_THREAD; ++u) {
+        constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
         if (blk0 + u * BLOCK_STEP < nb) {
-            float v[16];
+            float v[CALL];
             D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
-            store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS, v);
+#pragma unroll
+            for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
         }
     }
 }
@@ -874,10 +989,10 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
             return launched != cudaSuccess ? launched : cudaGetLastError();
         }
     }
-    dequant_tile_kernel<TYPE, OutT><<<(unsigned)grid, kThreads, 0, stream>>>(static_cast<const uint8_t *>(src),
-                                                                           static_cast<OutT *>(dst), nblocks, aligned);
+    const cudaError_t launched = launch_overlapped(dequant_tile_kernel<TYPE, OutT>, (unsigned)grid, kThreads, stream,
+                                                   static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks, aligned);
     count_launch();
-    return cudaGetLastError();
+    return launched != cudaSuccess ? launched : cudaGetLastError();
 }
 
 // bf16 rows whose length is not a multiple of 8: scalar tail handled by a tiny kernel.
