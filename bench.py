@@ -206,6 +206,8 @@ def main() -> None:
     if args.workload != "dequant_sweep":
         import bench_quant
         bench_quant.run(args, torch, dist, lib, ops, device, rank, world)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     rows = args.rows

@@ -789,6 +789,256 @@ struct Fast<GGML_TYPE_Q5_1> {
     }
 };
 
+// ---- codebook types ----------------------------------------------------------------------------
+// A packed codebook entry holds eight 2-bit codes (IQ2, IQ1) or four 3-bit codes (IQ3).  The codes are
+// widened to 4-bit permute selectors and looked up in a level table held in registers.
+// eight 2-bit fields -> eight nibbles
+GGUF_D uint32_t widen_2bit(uint32_t c) {
+    c = (c | (c << 8)) & 0x00FF00FFu;
+    c = (c | (c << 4)) & 0x0F0F0F0Fu;
+    return (c | (c << 2)) & 0x33333333u;
+}
+// four 3-bit fields -> four nibbles
+GGUF_D uint32_t widen_3bit(uint32_t c) {
+    c = (c & 0x03Fu) | ((c << 2) & 0x3F00u);
+    return (c & 0x0707u) | ((c << 1) & 0x7070u);
+}
+// unaligned little-endian 32-bit value from a 2-byte aligned shared-memory address
+GGUF_D uint32_t lds_u32_a2(const uint8_t *p) { return lds_u16(p) | (lds_u16(p + 2) << 16); }
+// v[0..3] = scale * (byte_k(levels) + bias), sign of v[k] flipped when bit k of `signs` is set
+GGUF_D void emit4(uint32_t levels, uint32_t signs, float scale, float bias, float *v) {
+    const float2 nb = make_float2(-kTwo23, -kTwo23), sc = make_float2(scale, scale), bs = make_float2(bias, bias);
+    float2 a = __fadd2_rn(make_float2(magic_byte(levels, 0), magic_byte(levels, 1)), nb);
+    float2 b = __fadd2_rn(make_float2(magic_byte(levels, 2), magic_byte(levels, 3)), nb);
+    if (bias != 0.f) { a = __fadd2_rn(a, bs); b = __fadd2_rn(b, bs); }
+    a = __fmul2_rn(sc, a);
+    b = __fmul2_rn(sc, b);
+    v[0] = __uint_as_float(__float_as_uint(a.x) ^ ((signs << 31) & 0x80000000u));
+    v[1] = __uint_as_float(__float_as_uint(a.y) ^ ((signs << 30) & 0x80000000u));
+    v[2] = __uint_as_float(__float_as_uint(b.x) ^ ((signs << 29) & 0x80000000u));
+    v[3] = __uint_as_float(__float_as_uint(b.y) ^ ((signs << 28) & 0x80000000u));
+}
+// Eight values of a 2-bit grid point.  `table`: the levels of codes 0..3 in its bytes.
+GGUF_D void emit_grid2(uint32_t code, uint32_t table, uint32_t signs, float scale, float bias, float *v) {
+    const uint32_t sel = widen_2bit(code);
+    emit4(__byte_perm(table, 0, sel & 0xFFFFu), signs, scale, bias, v);
+    emit4(__byte_perm(table, 0, sel >> 16), signs >> 4, scale, bias, v + 4);
+}
+// Four values of a 3-bit grid point.  (t0, t1): the levels of codes 0..7.
+GGUF_D void emit_grid3(uint32_t code, uint32_t t0, uint32_t t1, uint32_t signs, float scale, float *v) {
+    emit4(__byte_perm(t0, t1, widen_3bit(code)), signs, scale, 0.f, v);
+}
+constexpr uint32_t kIq2Levels = 8u | (25u << 8) | (43u << 16);                       // upstream iq2xxs_grid bytes
+constexpr uint32_t kIq3xxsLevels0 = 4u | (12u << 8) | (20u << 16) | (28u << 24);     // upstream iq3xxs_grid bytes
+constexpr uint32_t kIq3xxsLevels1 = 36u | (44u << 8) | (52u << 16) | (62u << 24);
+constexpr uint32_t kIq3sLevels0 = 1u | (3u << 8) | (5u << 16) | (7u << 24);          // upstream iq3s_grid bytes
+constexpr uint32_t kIq3sLevels1 = 9u | (11u << 8) | (13u << 16) | (15u << 24);
+constexpr uint32_t kIq1Levels = 0u | (1u << 8) | (2u << 16);                         // grid value + 1
+
+template <>
+struct Fast<GGML_TYPE_IQ2_XXS> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 66, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int ib32) {
+        const uint32_t aux1 = lds_u32_a2(b + 2 + 8 * ib32 + 4);
+        return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)(aux1 >> 28)) * 0.25f, 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint8_t *q = b + 2 + 8 * (e0 >> 5);
+        const uint32_t aux1 = lds_u32_a2(q + 4);
+        const int l = (e0 >> 3) & 3;  // 0 or 2
+        const uint32_t pair = lds_u16(q + l);
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+            emit_grid2(__ldg(&k_codebook_IQ2XXS[(pair >> (8 * k)) & 0xFFu]), kIq2Levels,
+                       iq_signs_from_index((aux1 >> (7 * (l + k))) & 127), c.x, 0.f, v + 8 * k);
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_IQ2_XS> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 74, GROUP = 16;
+    static GGUF_D float2 prep(const uint8_t *b, int g16) {
+        const int sc = b[66 + (g16 >> 1)];
+        return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)((g16 & 1) ? (sc >> 4) : (sc & 0xF))) * 0.25f, 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t q = lds_u16(b + 2 + 2 * ((e0 >> 3) + k));
+            emit_grid2(__ldg(&k_codebook_IQ2XS[q & 511u]), kIq2Levels, iq_signs_from_index(q >> 9), c.x, 0.f, v + 8 * k);
+        }
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_IQ2_S> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 82, GROUP = 16;
+    static GGUF_D float2 prep(const uint8_t *b, int g16) {
+        const int sc = b[74 + (g16 >> 1)];
+        return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)((g16 & 1) ? (sc >> 4) : (sc & 0xF))) * 0.25f, 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int g = e0 >> 3, ib32 = g >> 2;
+        const uint32_t qh = b[66 + ib32];
+        const uint32_t low = lds_u16(b + 2 + g), signs = lds_u16(b + 2 + 32 + g);  // g is even
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 0x300u);
+            emit_grid2(__ldg(&k_codebook_IQ2S[idx]), kIq2Levels, (signs >> (8 * k)) & 0xFFu, c.x, 0.f, v + 8 * k);
+        }
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_IQ3_XXS> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 98, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int ib32) {
+        const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
+        return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)(aux >> 28)) * 0.5f, 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int g = e0 >> 3, ib32 = g >> 2;  // g even: grid points 2g .. 2g+3
+        const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
+        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t signs = iq_signs_from_index((aux >> (7 * ((g & 3) + k))) & 127);
+            emit_grid3(__ldg(&k_codebook_IQ3XXS[(idx >> (16 * k)) & 0xFFu]), kIq3xxsLevels0, kIq3xxsLevels1, signs, c.x, v + 8 * k);
+            emit_grid3(__ldg(&k_codebook_IQ3XXS[(idx >> (16 * k + 8)) & 0xFFu]), kIq3xxsLevels0, kIq3xxsLevels1, signs >> 4, c.x, v + 8 * k + 4);
+        }
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_IQ3_S> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 110, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int ib32) {
+        const int sc = b[106 + (ib32 >> 1)];
+        return make_float2(half_hw(lds_u16(b)) * (float)(1 + 2 * ((ib32 & 1) ? (sc >> 4) : (sc & 0xF))), 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int g = e0 >> 3, ib32 = g >> 2;
+        const uint32_t qh = b[66 + ib32];
+        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g), sg = lds_u16(b + 74 + g);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
+            const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
+            const uint32_t signs = (sg >> (8 * k)) & 0xFFu;
+            emit_grid3(__ldg(&k_codebook_IQ3S[i1]), kIq3sLevels0, kIq3sLevels1, signs, c.x, v + 8 * k);
+            emit_grid3(__ldg(&k_codebook_IQ3S[i2]), kIq3sLevels0, kIq3sLevels1, signs >> 4, c.x, v + 8 * k + 4);
+        }
+    }
+};
+
+// IQ1: value = dl * ((code - 1) + delta), delta = -+0.125; the constant pair holds dl and delta - 1.
+template <>
+struct Fast<GGML_TYPE_IQ1_S> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 50, GROUP = 32;
+    static GGUF_D float2 prep(const uint8_t *b, int ib) {
+        const uint32_t qh = lds_u16(b + 34 + 2 * ib);
+        return make_float2(half_hw(lds_u16(b)) * (float)(2 * ((qh >> 12) & 7) + 1), (qh & 0x8000u) ? -1.125f : -0.875f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int g = e0 >> 3, ib = g >> 2;
+        const uint32_t qh = lds_u16(b + 34 + 2 * ib), low = lds_u16(b + 2 + g);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
+            emit_grid2(__ldg(&k_codebook_IQ1S[idx]), kIq1Levels, 0u, c.x, c.y, v + 8 * k);
+        }
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_IQ1_M> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 56, GROUP = 16;
+    static GGUF_D float2 prep(const uint8_t *b, int g16) {
+        const uint32_t s0 = lds_u16(b + 48), s1 = lds_u16(b + 50), s2 = lds_u16(b + 52), s3 = lds_u16(b + 54);
+        const uint32_t dbits = (s0 >> 12) | ((s1 >> 8) & 0x00f0u) | ((s2 >> 4) & 0x0f00u) | (s3 & 0xf000u);
+        const int ib = g16 >> 1;
+        const uint32_t sc = lds_u16(b + 48 + 2 * (ib >> 1));
+        return make_float2(half_hw(dbits) * (float)(2 * ((sc >> (6 * (ib & 1) + 3 * (g16 & 1))) & 7) + 1), 0.f);
+    }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const int g = e0 >> 3;  // even: grid points g, g + 1 share the byte qh[g / 2]
+        const uint32_t qh = b[32 + (g >> 1)], low = lds_u16(b + g);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | ((qh << (k ? 4 : 8)) & 0x700u);
+            const float bias = (qh & (k ? 0x80u : 0x08u)) ? -1.125f : -0.875f;
+            emit_grid2(__ldg(&k_codebook_IQ1S[idx]), kIq1Levels, 0u, c.x, bias, v + 8 * k);
+        }
+    }
+};
+
+// ---- 1-bit and ternary types --------------------------------------------------------------------
+template <>
+struct Fast<GGML_TYPE_Q1_0> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 128, BYTES = 18, GROUP = 128;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), 0.f); }
+    // bit set: d, bit clear: -d
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint32_t clear = ~lds_u16(b + 2 + (e0 >> 3));
+        const uint32_t dbits = __float_as_uint(c.x);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(dbits ^ ((clear << (31 - i)) & 0x80000000u));
+    }
+};
+
+template <>
+struct Fast<GGML_TYPE_TQ2_0> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 66, GROUP = 256;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b + 64)), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const uint4 q = lds16_any(b + 32 * (e0 >> 7) + (e0 & 16));
+        affine16<false>(shr_and(q, 2 * ((e0 >> 5) & 3), 0x03030303u), -(kTwo23 + 1.f), c, v);
+    }
+};
+
+// TQ1_0: digit n of a byte is ((byte * 3^n) & 0xFF) * 3 >> 8.  Elements 0..159 take digit e/32 of byte
+// e%32, elements 160..239 digit (e-160)/16 of byte 32 + (e-160)%16, elements 240..255 digit (e-240)/4
+// of byte 48 + (e-240)%4.  Four bytes at a time: the even and the odd bytes are multiplied in 16-bit
+// lanes (255 * 81 < 2^15, so nothing crosses a lane).
+GGUF_D uint32_t tq1_digits(uint32_t w, uint32_t pow3) {
+    const uint32_t even = ((((w & 0x00FF00FFu) * pow3) & 0x00FF00FFu) * 3u >> 8) & 0x00030003u;
+    const uint32_t odd = (((((w >> 8) & 0x00FF00FFu) * pow3) & 0x00FF00FFu) * 3u >> 8) & 0x00030003u;
+    return even | (odd << 8);
+}
+template <>
+struct Fast<GGML_TYPE_TQ1_0> {
+    static constexpr bool kEnabled = true;
+    static constexpr int ELEMS = 256, BYTES = 54, GROUP = 256;
+    static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b + 52)), 0.f); }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+        const bool last = e0 >= 240;
+        const int n = e0 < 160 ? e0 >> 5 : (e0 - 160) >> 4;           // digit for the first two regions
+        const int at = e0 < 160 ? (e0 & 31) : (last ? 48 : 32);      // first source byte
+        const uint32_t p = n == 0 ? 1u : n == 1 ? 3u : n == 2 ? 9u : n == 3 ? 27u : 81u;
+        const uint4 q = lds16_any(b + at);  // 54-byte blocks: the 16 bytes stay inside the tile's padding
+        const uint32_t w[4] = {q.x, last ? q.x : q.y, last ? q.x : q.z, last ? q.x : q.w};
+        const uint32_t pw[4] = {last ? 1u : p, last ? 3u : p, last ? 9u : p, last ? 27u : p};
+        uint4 digits;
+        digits.x = tq1_digits(w[0], pw[0]);
+        digits.y = tq1_digits(w[1], pw[1]);
+        digits.z = tq1_digits(w[2], pw[2]);
+        digits.w = tq1_digits(w[3], pw[3]);
+        affine16<false>(digits, -(kTwo23 + 1.f), c, v);
+    }
+};
+
 // ---------------------------------------------------------------------------------------------
 template <class OutT>
 struct OutPack;
