@@ -178,6 +178,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dequant_sweep")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the weight matrix (smaller for profiling captures)")
+    ap.add_argument("--src-dtype", default="f32", choices=["f32", "f16", "bf16"],
+                    help="convert workload: dtype of the pinned source tensors (16-bit sources are widened on the GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()

@@ -193,6 +193,18 @@ def statistics_mean(values):
     return sum(values) / len(values)
 
 
+def as_numpy_source(torch, t):
+    """Pinned torch tensor -> the numpy view the pipeline takes (bfloat16 as uint16 bit patterns)."""
+    return t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
+
+
+def widened(torch, a, src_dtype):
+    t = torch.from_numpy(a)
+    if src_dtype == "bf16":
+        t = t.view(torch.bfloat16)
+    return t.float()
+
+
 def run_convert(args, torch, dist, lib, device, rank, world, hbm):
     """Whole-model conversion, pinned host fp32 in, pinned host blocks out.
     Plain `python bench.py --gpus N`: one process drives N GPUs through the in-process pool.
@@ -216,8 +228,9 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
             x = torch.randn((t.rows, t.cols), generator=g, device=device) * 0.02
             cols = torch.randperm(t.cols, generator=g, device=device)[: max(1, t.cols // 1000)]
             x[:, cols] *= 20
-            host = torch.empty((t.rows, t.cols), dtype=torch.float32).pin_memory()
-            host.copy_(x)
+            src_torch = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[args.src_dtype]
+            host = torch.empty((t.rows, t.cols), dtype=src_torch).pin_memory()
+            host.copy_(x.to(src_torch))
             sources[key] = host
             del x
     torch.cuda.synchronize()
@@ -225,10 +238,11 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
     for t in plan:
         o = torch.empty(t.rows * row_size(t.qtype, t.cols), dtype=torch.uint8).pin_memory()
         outs.append(o)
-        batch.append((t.qtype, sources[(t.rows, t.cols)].numpy(), None, o.numpy()))
+        batch.append((t.qtype, as_numpy_source(torch, sources[(t.rows, t.cols)]), None, o.numpy()))
     if per_process:
         batch = rank_batch(batch, world, rank)
-    in_bytes = sum(t.rows * t.cols * 4 for t in plan)
+    in_bytes = sum(t.rows * t.cols * 4 for t in plan)  # fp32-equivalent, whatever the source dtype
+    link_bytes = in_bytes if args.src_dtype == "f32" else in_bytes // 2
     out_bytes = sum(o.numel() for o in outs)
     times = []
     with ConversionPipeline(devices, slots=3, chunk_bytes=128 << 20) as pipe:
@@ -245,7 +259,7 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
     ok = True
     for q, s, _, d in batch[:: max(1, len(batch) // 4)]:
         rows = min(s.shape[0], 256)
-        ref = ops.quantize(torch.from_numpy(s[:rows]).to(device), q).cpu().numpy().reshape(-1)
+        ref = ops.quantize(widened(torch, s[:rows], args.src_dtype).to(device), q).cpu().numpy().reshape(-1)
         ok = ok and bool(np.array_equal(ref, d[: ref.size]))
     if per_process:
         flag = torch.tensor([int(ok)], device=device)
@@ -258,6 +272,7 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
         "warmup": 1, "ms_per_step": best * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": "convert Llama-3-8B-shaped set, Q4_K_M mix, pinned host in/out", "tensors": len(plan),
                                        "launch": "one process per GPU, shards assigned from the plan" if per_process else "one process, in-process GPU pool",
-                                       "source_bytes": in_bytes, "output_bytes": out_bytes,
+                                       "source_dtype": args.src_dtype, "source_bytes_fp32_equivalent": in_bytes,
+                                       "source_bytes_over_the_link": link_bytes, "output_bytes": out_bytes,
                                        "note": "layer sources shared by the 32 layers (one 0.87 GB layer + 2.1 GB embedding resident in pinned memory)"},
         "elements_per_s": in_bytes / 4 / best, "all_times_s": [round(x, 4) for x in times], "pipeline_rank0": stats, "spot_check_ok": ok}))

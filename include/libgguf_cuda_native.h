@@ -132,6 +132,17 @@ LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches
  * compared.  Modes 1 and 2 look only at the inputs the quantizers route there (finite, |x| <= 2^20 * scale). */
 LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4_mode(float scale, int mode, uint64_t *mismatches, uint64_t *fallbacks);
 
+/* Device-side source decode, no upstream counterpart (upstream widens 16-bit checkpoints on the CPU before the upload:
+ * csrc/quantize_gguf.cpp:1415-1442, :2106-2112).  `source_dtype` uses the LIBGGUF_CUDA_DEQUANTIZE_DTYPE_* codes:
+ * F16 or BF16 values are widened to fp32 exactly as the host code does (bf16: 16-bit shift; fp16: exact conversion).
+ * libgguf_cuda_quantize_rows_from_on_stream widens into `device_f32_scratch` (rows * n_per_row floats, 16-byte
+ * aligned; unused and may be NULL for an F32 source) and then quantizes like libgguf_cuda_quantize_f32_rows_on_stream. */
+LIBGGUF_CUDA_API int libgguf_cuda_widen_on_stream(const void *device_input, int source_dtype, float *device_output, int64_t count,
+                                                  void *stream);
+LIBGGUF_CUDA_API int libgguf_cuda_quantize_rows_from_on_stream(const void *device_input, int source_dtype, float *device_f32_scratch,
+                                                               const float *device_imatrix, void *device_output, int64_t qtype,
+                                                               int64_t rows, int64_t n_per_row, void *stream);
+
 /* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,
  * csrc/quantize_gguf.cpp:1732-1931 and :2072-2146; the pool itself has no upstream counterpart) ----
  * A batch of tensors (host memory, fp32 rows in, encoded rows out) is cut into shards of whole rows of at most
@@ -160,6 +171,13 @@ LIBGGUF_CUDA_API void libgguf_cuda_pipeline_destroy(libgguf_cuda_pipeline *pipe)
 LIBGGUF_CUDA_API const char *libgguf_cuda_pipeline_last_error(const libgguf_cuda_pipeline *pipe);
 LIBGGUF_CUDA_API int libgguf_cuda_pipeline_quantize(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc *tensors,
                                                     int n_tensors);
+/* Same with a source dtype per tensor (LIBGGUF_CUDA_DEQUANTIZE_DTYPE_* codes; NULL = all F32): `src` of a tensor with
+ * dtype F16 / BF16 points at rows x n_per_row 16-bit values, which cross the host link as they are and are widened
+ * on the GPU.  A shard is then at most chunk_bytes of source bytes. */
+LIBGGUF_CUDA_API int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc *tensors,
+                                                          const int32_t *source_dtypes, int n_tensors);
+LIBGGUF_CUDA_API int64_t libgguf_cuda_pipeline_plan_typed(const libgguf_cuda_tensor_desc *tensors, const int32_t *source_dtypes,
+                                                          int n_tensors, size_t chunk_bytes, libgguf_cuda_shard *out, int64_t max_out);
 /* The shard list the pipeline would use (largest first); returns the shard count, -1 on a bad descriptor.
  * Needs no GPU. */
 LIBGGUF_CUDA_API int64_t libgguf_cuda_pipeline_plan(const libgguf_cuda_tensor_desc *tensors, int n_tensors, size_t chunk_bytes,

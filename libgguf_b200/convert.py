@@ -18,6 +18,10 @@ from . import GGMLQuantizationType, row_size
 from ._native import ShardDesc, TensorDesc, lib
 
 
+# numpy dtype of a source array -> source dtype code of the C ABI (bfloat16 travels as uint16 bit patterns)
+SOURCE_DTYPES = {np.dtype(np.float32): 0, np.dtype(np.float16): 1, np.dtype(np.uint16): 2}
+
+
 @dataclass
 class PlannedTensor:
     name: str
@@ -70,9 +74,11 @@ class ConversionPipeline:
     def _descs(tensors):
         keep = []
         descs = (TensorDesc * len(tensors))()
-        for d, (qtype, src, imatrix, dst) in zip(descs, tensors):
-            if src.dtype != np.float32 or src.ndim != 2 or not src.flags.c_contiguous:
-                raise ValueError("src must be a C-contiguous 2-D float32 array")
+        dtypes = (ctypes.c_int32 * len(tensors))()
+        for i, (d, (qtype, src, imatrix, dst)) in enumerate(zip(descs, tensors)):
+            if src.dtype not in SOURCE_DTYPES or src.ndim != 2 or not src.flags.c_contiguous:
+                raise ValueError("src must be a C-contiguous 2-D array of float32, float16, or uint16 holding bfloat16 bits")
+            dtypes[i] = SOURCE_DTYPES[src.dtype]
             if dst.dtype != np.uint8 or not dst.flags.c_contiguous or not dst.flags.writeable:
                 raise ValueError("dst must be a writable C-contiguous uint8 array")
             rs = row_size(qtype, src.shape[1])
@@ -86,12 +92,13 @@ class ConversionPipeline:
                 keep.append(im)
             d.qtype, d.src, d.imatrix, d.dst = int(qtype), src.ctypes.data, (im.ctypes.data if im is not None else None), dst.ctypes.data
             d.rows, d.n_per_row = src.shape
-        return descs, keep
+        return descs, dtypes, keep
 
     def quantize(self, tensors) -> None:
-        """tensors: list of (qtype, src float32 [rows, n], imatrix or None, dst uint8 [rows * row_size])."""
-        descs, keep = self._descs(tensors)
-        status = lib.libgguf_cuda_pipeline_quantize(self._handle, descs, len(tensors))
+        """tensors: list of (qtype, src [rows, n], imatrix or None, dst uint8 [rows * row_size]).  `src` is float32, or
+        float16 / uint16-as-bfloat16, in which case the 16-bit values are uploaded as they are and widened on the GPU."""
+        descs, dtypes, keep = self._descs(tensors)
+        status = lib.libgguf_cuda_pipeline_quantize_typed(self._handle, descs, dtypes, len(tensors))
         if status != 0:
             raise RuntimeError(f"pipeline failed (status {status}): {lib.libgguf_cuda_pipeline_last_error(self._handle).decode()}")
 
@@ -108,16 +115,18 @@ class ConversionPipeline:
         return {"shards_per_device": list(shards), "seconds_per_device": list(secs), "requeued": requeued.value}
 
 
-def plan_shards(tensors: list[tuple[int, int, int]], chunk_bytes: int = 128 << 20) -> list[tuple[int, int, int]]:
-    """Shard list for tensors given as (qtype, rows, n_per_row); needs no GPU.  Returns (tensor, row0, rows)."""
+def plan_shards(tensors: list[tuple[int, int, int]], chunk_bytes: int = 128 << 20, source_dtypes=None) -> list[tuple[int, int, int]]:
+    """Shard list for tensors given as (qtype, rows, n_per_row); needs no GPU.  Returns (tensor, row0, rows).
+    source_dtypes: optional list of 0 (float32), 1 (float16), 2 (bfloat16); a shard holds at most chunk_bytes of source."""
     descs = (TensorDesc * len(tensors))()
     for d, (qtype, rows, n) in zip(descs, tensors):
         d.qtype, d.rows, d.n_per_row = int(qtype), rows, n
-    count = lib.libgguf_cuda_pipeline_plan(descs, len(tensors), chunk_bytes, None, 0)
+    dtypes = (ctypes.c_int32 * len(tensors))(*source_dtypes) if source_dtypes is not None else None
+    count = lib.libgguf_cuda_pipeline_plan_typed(descs, dtypes, len(tensors), chunk_bytes, None, 0)
     if count < 0:
         raise ValueError("bad tensor descriptor")
     out = (ShardDesc * count)()
-    lib.libgguf_cuda_pipeline_plan(descs, len(tensors), chunk_bytes, out, count)
+    lib.libgguf_cuda_pipeline_plan_typed(descs, dtypes, len(tensors), chunk_bytes, out, count)
     return [(s.tensor, s.row0, s.rows) for s in out]
 
 
@@ -142,7 +151,8 @@ def rank_batch(tensors, world: int, rank: int, chunk_bytes: int = 128 << 20):
     """The slice of a conversion batch that process `rank` of `world` runs on its own GPU.
     tensors: list of (qtype, src float32 [rows, n], imatrix or None, dst uint8 [rows * row_size]); the result has the
     same form, with `src` and `dst` replaced by row-range views, and can be given to ConversionPipeline.quantize."""
-    shards = plan_shards([(q, s.shape[0], s.shape[1]) for q, s, _, _ in tensors], chunk_bytes)
+    shards = plan_shards([(q, s.shape[0], s.shape[1]) for q, s, _, _ in tensors], chunk_bytes,
+                         [SOURCE_DTYPES[s.dtype] for _, s, _, _ in tensors])
     mine = assign_shards(shards, [s.shape[1] for _, s, _, _ in tensors], world)[rank]
     batch = []
     for tensor, row0, rows in mine:

@@ -333,6 +333,35 @@ int libgguf_cuda_quantize_f32_rows_on_stream(const float *device_input, const fl
                         reinterpret_cast<cudaStream_t>(stream));
 }
 
+int libgguf_cuda_widen_on_stream(const void *device_input, int source_dtype, float *device_output, int64_t count, void *stream) {
+    if (count < 0 || (count > 0 && (!device_input || !device_output)))
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "invalid widen arguments");
+    if (source_dtype != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F16 && source_dtype != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_BF16)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "source dtype must be F16 (1) or BF16 (2)");
+    if (reinterpret_cast<uintptr_t>(device_input) & 1 || reinterpret_cast<uintptr_t>(device_output) & 3)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "widen pointers must be aligned to their element size");
+    const cudaError_t error = launch_widen(source_dtype, device_input, device_output, count, reinterpret_cast<cudaStream_t>(stream));
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    return ok(nullptr);
+}
+
+int libgguf_cuda_quantize_rows_from_on_stream(const void *device_input, int source_dtype, float *device_f32_scratch,
+                                              const float *device_imatrix, void *device_output, int64_t qtype, int64_t rows,
+                                              int64_t n_per_row, void *stream) {
+    if (source_dtype == LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32)
+        return run_quantize(nullptr, static_cast<const float *>(device_input), device_imatrix, device_output, qtype, rows, n_per_row,
+                            reinterpret_cast<cudaStream_t>(stream));
+    if (rows < 0 || n_per_row <= 0) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "invalid quantize arguments");
+    if (rows > 0 && !device_f32_scratch)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "a 16-bit source needs an fp32 scratch buffer of rows * n_per_row floats");
+    if (reinterpret_cast<uintptr_t>(device_f32_scratch) & 15)
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "the fp32 scratch buffer must be 16-byte aligned");
+    const int status = libgguf_cuda_widen_on_stream(device_input, source_dtype, device_f32_scratch, rows * n_per_row, stream);
+    if (status != LIBGGUF_CUDA_STATUS_SUCCESS) return status;
+    return run_quantize(nullptr, device_f32_scratch, device_imatrix, device_output, qtype, rows, n_per_row,
+                        reinterpret_cast<cudaStream_t>(stream));
+}
+
 int libgguf_cuda_dequantize_rows(libgguf_cuda_context *ctx, const void *device_input, int64_t qtype, int64_t rows,
                                  int64_t n_per_row, int output_dtype, void *device_output) {
     if (!ctx) return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;

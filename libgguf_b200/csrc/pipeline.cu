@@ -47,9 +47,9 @@ struct Shard {
 struct Slot {
     cudaStream_t stream = nullptr;
     cudaEvent_t done = nullptr;
-    void *d_in = nullptr, *d_out = nullptr, *d_imatrix = nullptr;
+    void *d_in = nullptr, *d_out = nullptr, *d_imatrix = nullptr, *d_wide = nullptr;  // d_wide: fp32 copy of a 16-bit source shard
     void *h_in = nullptr, *h_out = nullptr;
-    size_t d_in_cap = 0, d_out_cap = 0, d_im_cap = 0, h_in_cap = 0, h_out_cap = 0;
+    size_t d_in_cap = 0, d_out_cap = 0, d_im_cap = 0, d_wide_cap = 0, h_in_cap = 0, h_out_cap = 0;
     bool busy = false;
     Shard shard;
     void *copy_out_to = nullptr;  // pageable destination waiting for the staged result
@@ -82,10 +82,12 @@ struct libgguf_cuda_pipeline {
 
 namespace {
 
-std::vector<Shard> plan_shards(const libgguf_cuda_tensor_desc *t, int n, size_t chunk_bytes) {
+size_t source_elem_size(const int32_t *dtypes, int i) { return dtypes && dtypes[i] != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32 ? 2 : 4; }
+
+std::vector<Shard> plan_shards(const libgguf_cuda_tensor_desc *t, const int32_t *dtypes, int n, size_t chunk_bytes) {
     std::vector<Shard> shards;
     for (int i = 0; i < n; ++i) {
-        const size_t in_row = (size_t)t[i].n_per_row * 4;
+        const size_t in_row = (size_t)t[i].n_per_row * source_elem_size(dtypes, i);
         const size_t out_row = libgguf_row_size((enum ggml_type)t[i].qtype, t[i].n_per_row);
         int64_t rows_per = (int64_t)(chunk_bytes / in_row);
         if (rows_per < 1) rows_per = 1;
@@ -106,6 +108,7 @@ std::vector<Shard> plan_shards(const libgguf_cuda_tensor_desc *t, int n, size_t 
 
 struct Batch {
     const libgguf_cuda_tensor_desc *tensors;
+    const int32_t *dtypes = nullptr;
     std::vector<char> src_pinned, dst_pinned;
     std::mutex lock;
     std::deque<Shard> queue;
@@ -193,7 +196,8 @@ void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
         if (!finish(s)) { ok = false; break; }
         const libgguf_cuda_tensor_desc &t = batch->tensors[cur.tensor];
         const size_t out_row = libgguf_row_size((enum ggml_type)t.qtype, t.n_per_row);
-        const char *src = (const char *)t.src + (size_t)cur.row0 * t.n_per_row * 4;
+        const size_t esz = source_elem_size(batch->dtypes, cur.tensor);
+        const char *src = (const char *)t.src + (size_t)cur.row0 * t.n_per_row * esz;
         char *dst = (char *)t.dst + (size_t)cur.row0 * out_row;
         const DeviceState *state = device_state_for((int)t.qtype, dev);
         ok = state && grow_dev(&s.d_in, &s.d_in_cap, cur.in_bytes) && grow_dev(&s.d_out, &s.d_out_cap, cur.out_bytes);
@@ -219,7 +223,13 @@ void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
             d_im = (const float *)s.d_imatrix;
         }
         if (e == cudaSuccess) e = cudaMemcpyAsync(s.d_in, h2d_from, cur.in_bytes, cudaMemcpyHostToDevice, s.stream);
-        if (e == cudaSuccess) e = launch_quantize((int)t.qtype, (const float *)s.d_in, d_im, s.d_out, cur.rows, t.n_per_row, state, s.stream);
+        const float *d_f32 = (const float *)s.d_in;
+        if (esz == 2) {
+            if (!grow_dev(&s.d_wide, &s.d_wide_cap, cur.in_bytes * 2)) { ok = false; err = "device allocation failed"; break; }
+            if (e == cudaSuccess) e = launch_widen(batch->dtypes[cur.tensor], s.d_in, (float *)s.d_wide, cur.rows * t.n_per_row, s.stream);
+            d_f32 = (const float *)s.d_wide;
+        }
+        if (e == cudaSuccess) e = launch_quantize((int)t.qtype, d_f32, d_im, s.d_out, cur.rows, t.n_per_row, state, s.stream);
         if (e == cudaSuccess) e = cudaMemcpyAsync(d2h_to, s.d_out, cur.out_bytes, cudaMemcpyDeviceToHost, s.stream);
         if (e == cudaSuccess) e = cudaEventRecord(s.done, s.stream);
         if (e != cudaSuccess) { err = cudaGetErrorString(e); cudaGetLastError(); ok = false; break; }
@@ -284,7 +294,7 @@ void libgguf_cuda_pipeline_destroy(libgguf_cuda_pipeline *pipe) {
         for (Slot &s : pipe->worker_slots[w]) {
             if (s.stream) { cudaStreamSynchronize(s.stream); cudaStreamDestroy(s.stream); }
             if (s.done) cudaEventDestroy(s.done);
-            cudaFree(s.d_in); cudaFree(s.d_out); cudaFree(s.d_imatrix);
+            cudaFree(s.d_in); cudaFree(s.d_out); cudaFree(s.d_imatrix); cudaFree(s.d_wide);
             cudaFreeHost(s.h_in); cudaFreeHost(s.h_out);
         }
     }
@@ -304,10 +314,22 @@ int libgguf_cuda_pipeline_inject_failure(libgguf_cuda_pipeline *pipe, int device
 
 int64_t libgguf_cuda_pipeline_plan(const libgguf_cuda_tensor_desc *tensors, int n_tensors, size_t chunk_bytes,
                                    libgguf_cuda_shard *out, int64_t max_out) {
-    if (!tensors || n_tensors < 0) return -1;
+    return libgguf_cuda_pipeline_plan_typed(tensors, nullptr, n_tensors, chunk_bytes, out, max_out);
+}
+
+static bool source_dtypes_valid(const int32_t *dtypes, int n) {
+    for (int i = 0; dtypes && i < n; ++i)
+        if (dtypes[i] != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32 && dtypes[i] != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F16 &&
+            dtypes[i] != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_BF16) return false;
+    return true;
+}
+
+int64_t libgguf_cuda_pipeline_plan_typed(const libgguf_cuda_tensor_desc *tensors, const int32_t *source_dtypes, int n_tensors,
+                                         size_t chunk_bytes, libgguf_cuda_shard *out, int64_t max_out) {
+    if (!tensors || n_tensors < 0 || !source_dtypes_valid(source_dtypes, n_tensors)) return -1;
     for (int i = 0; i < n_tensors; ++i)
         if (tensors[i].rows < 0 || tensors[i].n_per_row <= 0 || libgguf_row_size((enum ggml_type)tensors[i].qtype, tensors[i].n_per_row) == 0) return -1;
-    const std::vector<Shard> shards = plan_shards(tensors, n_tensors, chunk_bytes ? chunk_bytes : (size_t(128) << 20));
+    const std::vector<Shard> shards = plan_shards(tensors, source_dtypes, n_tensors, chunk_bytes ? chunk_bytes : (size_t(128) << 20));
     for (int64_t i = 0; i < (int64_t)shards.size() && out && i < max_out; ++i) {
         out[i].tensor = shards[i].tensor;
         out[i].row0 = shards[i].row0;
@@ -317,8 +339,17 @@ int64_t libgguf_cuda_pipeline_plan(const libgguf_cuda_tensor_desc *tensors, int 
 }
 
 int libgguf_cuda_pipeline_quantize(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc *tensors, int n_tensors) {
+    return libgguf_cuda_pipeline_quantize_typed(pipe, tensors, nullptr, n_tensors);
+}
+
+int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc *tensors,
+                                         const int32_t *source_dtypes, int n_tensors) {
     if (!pipe || !tensors || n_tensors < 0) return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;
     pipe->last_error.clear();
+    if (!source_dtypes_valid(source_dtypes, n_tensors)) {
+        pipe->last_error = "source dtype must be F32 (0), F16 (1) or BF16 (2)";
+        return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;
+    }
     for (int i = 0; i < n_tensors; ++i) {
         const libgguf_cuda_tensor_desc &t = tensors[i];
         if (!t.src || !t.dst || t.rows < 0 || t.n_per_row <= 0) {
@@ -337,13 +368,14 @@ int libgguf_cuda_pipeline_quantize(libgguf_cuda_pipeline *pipe, const libgguf_cu
     }
     Batch batch;
     batch.tensors = tensors;
+    batch.dtypes = source_dtypes;
     batch.src_pinned.resize(n_tensors);
     batch.dst_pinned.resize(n_tensors);
     for (int i = 0; i < n_tensors; ++i) {
         batch.src_pinned[i] = is_pinned(tensors[i].src);
         batch.dst_pinned[i] = is_pinned(tensors[i].dst);
     }
-    const std::vector<Shard> shards = plan_shards(tensors, n_tensors, pipe->chunk_bytes);
+    const std::vector<Shard> shards = plan_shards(tensors, source_dtypes, n_tensors, pipe->chunk_bytes);
     batch.queue.assign(shards.begin(), shards.end());
     batch.remaining = (int64_t)shards.size();
     batch.worker_failed.assign(pipe->devices.size(), 0);

@@ -76,3 +76,52 @@ def test_pipeline_rejects_bad_batches(gguf):
             pipe.quantize([(12, x, None, np.zeros(10, np.uint8))])
         with pytest.raises(RuntimeError, match="requires an imatrix"):
             pipe.quantize([(16, x, None, np.zeros(4 * 66, np.uint8))])
+
+
+@pytest.mark.parametrize("kind", ["float16", "bfloat16"])
+def test_sixteen_bit_sources_are_widened_on_the_gpu(gguf, kind):
+    """fp16 / bf16 source rows go through the pipeline as 16-bit values; the bytes must equal quantizing the
+    host-widened fp32 copy (what upstream's converter uploads)."""
+    from libgguf_b200.convert import ConversionPipeline
+    rng = np.random.default_rng(5)
+    batch, want = [], []
+    for qtype, rows, n in [(12, 300, 1024), (8, 77, 256), (14, 130, 512), (39, 33, 64), (2, 5, 32)]:
+        x = rng.standard_normal((rows, n), dtype=np.float32)
+        x[0, :4] = [0.0, -0.0, 65504.0, 6e-8]
+        if kind == "float16":
+            src = x.astype(np.float16)
+            wide = src.astype(np.float32)
+        else:
+            src = (x.view(np.uint32) >> 16).astype(np.uint16)  # truncated bf16 bit patterns
+            wide = (src.astype(np.uint32) << 16).view(np.float32)
+        dst = np.zeros(rows * gguf.row_size(qtype, n), dtype=np.uint8)
+        batch.append((qtype, np.ascontiguousarray(src), None, dst))
+        want.append(gguf.quantize_rows(wide, qtype).reshape(-1))
+    with ConversionPipeline([0], slots=2, chunk_bytes=64 << 10) as pipe:
+        pipe.quantize(batch)
+    for (_, _, _, dst), w in zip(batch, want):
+        assert np.array_equal(dst, w.view(np.uint8).reshape(-1))
+
+
+def test_widen_and_quantize_from_entry_points(gguf):
+    import ctypes
+    from libgguf_b200._native import lib
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((64, 512), dtype=np.float32)
+    half = torch.from_numpy(x.astype(np.float16)).cuda()
+    bf = torch.from_numpy(x).cuda().to(torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+    for code, t in ((1, half), (2, bf)):
+        wide = torch.empty(t.shape, dtype=torch.float32, device="cuda")
+        assert lib.libgguf_cuda_widen_on_stream(t.data_ptr(), code, wide.data_ptr(), t.numel(), stream) == 0
+        assert torch.equal(wide, t.float())
+        # one element past a 16-byte boundary: the scalar path
+        assert lib.libgguf_cuda_widen_on_stream(t.data_ptr() + 2, code, wide.data_ptr() + 4, t.numel() - 1, stream) == 0
+        assert torch.equal(wide.reshape(-1)[1:], t.float().reshape(-1)[1:])
+        out = torch.empty(64 * gguf.row_size(12, 512), dtype=torch.uint8, device="cuda")
+        scratch = torch.empty(t.shape, dtype=torch.float32, device="cuda")
+        assert lib.libgguf_cuda_quantize_rows_from_on_stream(t.data_ptr(), code, scratch.data_ptr(), None, out.data_ptr(), 12, 64, 512, stream) == 0
+        want = gguf.quantize_rows(t.float().cpu().numpy(), 12)
+        assert np.array_equal(out.cpu().numpy(), want.reshape(-1))
+    assert lib.libgguf_cuda_widen_on_stream(half.data_ptr(), 0, wide.data_ptr(), 8, stream) != 0
+    assert lib.libgguf_cuda_quantize_rows_from_on_stream(half.data_ptr(), 1, None, None, out.data_ptr(), 12, 64, 512, stream) != 0

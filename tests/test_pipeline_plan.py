@@ -40,3 +40,12 @@ def test_llama_plan_totals():
     assert q6 == 1_531_969_536 - 0 * 1  # output + half of attn_v and ffn_down
     shards = plan_shards([(t.qtype, t.rows, t.cols) for t in plan])
     assert sum(r * plan[t].cols for t, _, r in shards) == elems
+
+
+def test_sixteen_bit_sources_fit_twice_the_rows_per_shard():
+    wide = plan_shards([(12, 1024, 4096)], chunk_bytes=1 << 20)
+    narrow = plan_shards([(12, 1024, 4096)], chunk_bytes=1 << 20, source_dtypes=[2])
+    assert max(r for _, _, r in wide) == 64 and max(r for _, _, r in narrow) == 128
+    assert sum(r for _, _, r in narrow) == 1024
+    with pytest.raises(ValueError):
+        plan_shards([(12, 4, 256)], source_dtypes=[7])
