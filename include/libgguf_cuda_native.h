@@ -143,6 +143,15 @@ LIBGGUF_CUDA_API int libgguf_cuda_quantize_rows_from_on_stream(const void *devic
                                                                const float *device_imatrix, void *device_output, int64_t qtype,
                                                                int64_t rows, int64_t n_per_row, void *stream);
 
+/* The importance weights upstream derives from the data when a type requires them and the caller has none
+ * (csrc/_libgguf_module.cpp:1210-1242 compute_auto_imatrix; src/libgguf/__init__.py:186-189): for every column the sum of
+ * squares over the rows, added in row order in fp32.  device_imatrix[c] += sum_r rows[r][c]^2, so a matrix may be fed in
+ * row pieces in order, the first onto zeros.  libgguf_cuda_auto_imatrix does this for a host matrix (staged through the
+ * GPU selected like for the host-pointer chunk functions) and writes n_per_row floats; returns a libgguf_cuda_status. */
+LIBGGUF_CUDA_API int libgguf_cuda_accumulate_imatrix_on_stream(const float *device_rows, int64_t rows, int64_t n_per_row,
+                                                               float *device_imatrix, void *stream);
+LIBGGUF_CUDA_API int libgguf_cuda_auto_imatrix(const float *host_rows, int64_t rows, int64_t n_per_row, float *host_imatrix);
+
 /* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,
  * csrc/quantize_gguf.cpp:1732-1931 and :2072-2146; the pool itself has no upstream counterpart) ----
  * A batch of tensors (host memory, fp32 rows in, encoded rows out) is cut into shards of whole rows of at most

@@ -165,6 +165,22 @@ def dequantize_rows_raw(qtype: int | Any, src: Any, n_rows: int, n_per_row: int)
     return out.tobytes()
 
 
+def auto_imatrix(rows: np.ndarray) -> np.ndarray:
+    """Column sums of squares of a 2-D fp32 matrix, added in row order on the GPU: the importance weights upstream
+    derives from the data when a type needs them and none are given (upstream __init__.py:186-189, same bits as
+    np.sum(rows * rows, axis=0, dtype=np.float32))."""
+    rows = np.ascontiguousarray(rows, dtype=np.float32)
+    if rows.ndim != 2:
+        raise ValueError("auto_imatrix expects a two-dimensional array")
+    out = np.zeros(rows.shape[1], dtype=np.float32)
+    if rows.shape[1] == 0:
+        return out
+    status = _lib.libgguf_cuda_auto_imatrix(rows.ctypes.data, rows.shape[0], rows.shape[1], out.ctypes.data)
+    if status != 0:
+        raise RuntimeError(f"libgguf_cuda_auto_imatrix failed with status {status}")
+    return out
+
+
 def quantize_rows(data: np.ndarray, qtype: int | Any, imatrix: Any | None = None) -> np.ndarray:
     """fp32 array [..., n] -> uint8 array [..., bytes_per_row] (upstream __init__.py:171-196).
     Types that require importance weights get the column sums of squares when none are given."""
@@ -179,8 +195,7 @@ def quantize_rows(data: np.ndarray, qtype: int | Any, imatrix: Any | None = None
     if imatrix is not None:
         quant_weights = _validate_imatrix(imatrix, n_per_row)
     elif quantize_requires_imatrix(qtype_value):
-        quant_weights = np.ascontiguousarray(
-            np.sum((rows * rows).reshape((-1, n_per_row)), axis=0, dtype=np.float32), dtype=np.float32)
+        quant_weights = auto_imatrix(rows.reshape((-1, n_per_row)))
     else:
         quant_weights = None
     bytes_per_row = _validated_row_size(qtype_value, n_per_row, "quantize")
@@ -238,7 +253,7 @@ atexit.register(_lib.libgguf_quantize_free)
 __all__ = [
     "GGMLQuantizationType", "GGML_QUANT_SIZES", "QK_K",
     "dequantize_rows", "dequantize_rows_into_raw", "dequantize_rows_raw",
-    "quantize_requires_imatrix", "quantize_rows", "quantize_rows_into_raw", "quantize_rows_raw",
+    "auto_imatrix", "quantize_requires_imatrix", "quantize_rows", "quantize_rows_into_raw", "quantize_rows_raw",
     "quant_shape_from_byte_shape", "quant_shape_to_byte_shape",
     "row_size", "store_rows", "type_name", "type_size",
 ]

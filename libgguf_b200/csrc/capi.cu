@@ -297,3 +297,30 @@ extern "C" void libgguf_quantize_free(void) {
     if (have) cudaSetDevice(saved);
     cudaGetLastError();
 }
+
+// Column sums of squares of a host matrix, staged through the GPU in row pieces (order preserved).
+extern "C" int libgguf_cuda_auto_imatrix(const float *host_rows, int64_t rows, int64_t n_per_row, float *host_imatrix) {
+    if (rows < 0 || n_per_row <= 0 || !host_imatrix || (rows > 0 && !host_rows)) return 1;  // LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT
+    int dev = 0;
+    if (!pick_device(&dev) || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return 3; }  // LIBGGUF_CUDA_STATUS_CUDA_ERROR
+    HostCallStaging &st = g_staging[dev];
+    std::lock_guard<std::mutex> guard(st.lock);
+    if (!st.stream && cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); return 3; }
+    const size_t row_bytes = (size_t)n_per_row * 4;
+    int64_t piece = (int64_t)(kStageBytes / row_bytes);
+    if (piece < 1) piece = 1;
+    if (piece > rows) piece = rows > 0 ? rows : 1;
+    if (!grow(&st.d_in, &st.in_cap, (size_t)piece * row_bytes) || !grow((void **)&st.d_imatrix, &st.im_cap, row_bytes)) return 4;  // ALLOCATION_FAILED
+    cudaError_t e = cudaMemsetAsync(st.d_imatrix, 0, row_bytes, st.stream);
+    for (int64_t r = 0; r < rows && e == cudaSuccess; r += piece) {
+        const int64_t nr = rows - r < piece ? rows - r : piece;
+        e = cudaMemcpyAsync(st.d_in, host_rows + r * n_per_row, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, st.stream);
+        if (e == cudaSuccess) e = gguf::launch_sumsq_columns((const float *)st.d_in, nr, n_per_row, st.d_imatrix, st.stream);
+        // the staging buffer is reused by the next piece: wait for the kernel that reads it
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st.stream);
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_imatrix, st.d_imatrix, row_bytes, cudaMemcpyDeviceToHost, st.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st.stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return 3; }
+    return 0;
+}

@@ -333,6 +333,15 @@ int libgguf_cuda_quantize_f32_rows_on_stream(const float *device_input, const fl
                         reinterpret_cast<cudaStream_t>(stream));
 }
 
+int libgguf_cuda_accumulate_imatrix_on_stream(const float *device_rows, int64_t rows, int64_t n_per_row, float *device_imatrix,
+                                              void *stream) {
+    if (rows < 0 || n_per_row <= 0 || !device_imatrix || (rows > 0 && !device_rows))
+        return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "invalid imatrix accumulation arguments");
+    const cudaError_t error = launch_sumsq_columns(device_rows, rows, n_per_row, device_imatrix, reinterpret_cast<cudaStream_t>(stream));
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    return ok(nullptr);
+}
+
 int libgguf_cuda_widen_on_stream(const void *device_input, int source_dtype, float *device_output, int64_t count, void *stream) {
     if (count < 0 || (count > 0 && (!device_input || !device_output)))
         return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "invalid widen arguments");

@@ -13,6 +13,8 @@ cudaError_t launch_dequantize(int type, const void *src, void *dst, int64_t nele
 // True if launch_quantize has a kernel for this type.
 bool quantize_supported(int type);
 // fp16 (src_dtype 1) / bf16 (2) -> fp32, n values
+// acc[c] += sum over rows (in row order) of rows[r][c]^2
+cudaError_t launch_sumsq_columns(const float *rows, int64_t nrows, int64_t n, float *acc, cudaStream_t stream);
 cudaError_t launch_widen(int src_dtype, const void *src, float *dst, int64_t n, cudaStream_t stream);
 
 // Launch accounting (exposed through libgguf_cuda_kernel_launch_count).

@@ -148,6 +148,62 @@ bool wait_slot(Slot &s, int timeout_ms, std::string &err) {
     }
 }
 
+// Streams one tensor through the first GPU in row pieces and accumulates its column sums of squares in order.
+bool auto_imatrix_pass(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc &t, int dtype, float *out, std::string &err) {
+    const int dev = pipe->devices[0];
+    if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); err = "cannot select device " + std::to_string(dev); return false; }
+    const size_t esz = dtype != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32 ? 2 : 4;
+    const size_t row_bytes = (size_t)t.n_per_row * esz;
+    int64_t piece = (int64_t)(pipe->chunk_bytes / row_bytes);
+    if (piece < 1) piece = 1;
+    cudaStream_t stream = nullptr;
+    void *d_src[2] = {nullptr, nullptr}, *d_wide = nullptr, *h_stage[2] = {nullptr, nullptr};
+    float *d_acc = nullptr;
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    const bool pinned = is_pinned(t.src);
+    bool ok = cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaMalloc((void **)&d_acc, (size_t)t.n_per_row * 4) == cudaSuccess &&
+              cudaMemsetAsync(d_acc, 0, (size_t)t.n_per_row * 4, stream) == cudaSuccess;
+    for (int k = 0; k < 2 && ok; ++k) {
+        ok = cudaMalloc(&d_src[k], (size_t)piece * row_bytes) == cudaSuccess &&
+             cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming) == cudaSuccess &&
+             (pinned || cudaMallocHost(&h_stage[k], (size_t)piece * row_bytes) == cudaSuccess);
+    }
+    if (ok && esz == 2) ok = cudaMalloc(&d_wide, (size_t)piece * t.n_per_row * 4) == cudaSuccess;
+    int k = 0;
+    bool used[2] = {false, false};
+    for (int64_t r = 0; r < t.rows && ok; r += piece, k ^= 1) {
+        const int64_t nr = std::min<int64_t>(piece, t.rows - r);
+        if (used[k]) ok = cudaEventSynchronize(done[k]) == cudaSuccess;  // the piece that used this buffer has been consumed
+        if (!ok) break;
+        const char *src = (const char *)t.src + (size_t)r * row_bytes;
+        if (!pinned) { std::memcpy(h_stage[k], src, (size_t)nr * row_bytes); src = (const char *)h_stage[k]; }
+        ok = cudaMemcpyAsync(d_src[k], src, (size_t)nr * row_bytes, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+        const float *rows32 = (const float *)d_src[k];
+        if (ok && esz == 2) {
+            ok = launch_widen(dtype, d_src[k], (float *)d_wide, nr * t.n_per_row, stream) == cudaSuccess;
+            rows32 = (const float *)d_wide;
+        }
+        if (ok) ok = launch_sumsq_columns(rows32, nr, t.n_per_row, d_acc, stream) == cudaSuccess;
+        if (ok) ok = cudaEventRecord(done[k], stream) == cudaSuccess;
+        used[k] = true;
+    }
+    if (ok) ok = cudaMemcpyAsync(out, d_acc, (size_t)t.n_per_row * 4, cudaMemcpyDeviceToHost, stream) == cudaSuccess;
+    if (ok) ok = cudaStreamSynchronize(stream) == cudaSuccess;
+    if (!ok) { err = std::string("imatrix pass failed: ") + cudaGetErrorString(cudaGetLastError()); }
+    else cudaGetLastError();
+    if (stream) cudaStreamSynchronize(stream);
+    for (int j = 0; j < 2; ++j) {
+        if (done[j]) cudaEventDestroy(done[j]);
+        cudaFree(d_src[j]);
+        if (h_stage[j]) cudaFreeHost(h_stage[j]);
+    }
+    cudaFree(d_wide);
+    cudaFree(d_acc);
+    if (stream) cudaStreamDestroy(stream);
+    return ok;
+}
+
 void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
     const int dev = pipe->devices[widx];
     std::vector<Slot> &slots = pipe->worker_slots[widx];
@@ -361,11 +417,27 @@ int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libg
             pipe->last_error = "unsupported quantization type or row width";
             return LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE;
         }
-        if (libgguf_quantize_requires_imatrix((enum ggml_type)t.qtype) && !t.imatrix) {
-            pipe->last_error = "quantization type requires an imatrix";
-            return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;
-        }
     }
+    // Types that require importance weights and got none: derive them from the tensor itself (column sums of
+    // squares in row order, upstream _libgguf_module.cpp:1221-1242) in a first pass over that tensor on the
+    // first GPU, then quantize with them like with caller-supplied weights.
+    std::vector<libgguf_cuda_tensor_desc> with_auto;
+    std::vector<std::vector<float>> auto_weights;
+    for (int i = 0; i < n_tensors; ++i) {
+        if (!libgguf_quantize_requires_imatrix((enum ggml_type)tensors[i].qtype) || tensors[i].imatrix) continue;
+        if (with_auto.empty()) {
+            with_auto.assign(tensors, tensors + n_tensors);
+            auto_weights.resize(n_tensors);
+        }
+        auto_weights[i].assign((size_t)tensors[i].n_per_row, 0.f);
+        std::string err;
+        if (!auto_imatrix_pass(pipe, tensors[i], source_dtypes ? source_dtypes[i] : 0, auto_weights[i].data(), err)) {
+            pipe->last_error = err;
+            return LIBGGUF_CUDA_STATUS_CUDA_ERROR;
+        }
+        with_auto[i].imatrix = auto_weights[i].data();
+    }
+    if (!with_auto.empty()) tensors = with_auto.data();
     Batch batch;
     batch.tensors = tensors;
     batch.dtypes = source_dtypes;

@@ -50,7 +50,46 @@ __global__ void __launch_bounds__(kThreads) widen_kernel(const uint16_t *__restr
     }
 }
 
+// Importance weights that upstream derives from the data when a type needs them and none are given: for every
+// column the sum of squares over the rows, accumulated in row order in fp32 (upstream _libgguf_module.cpp:1210-1220
+// accumulate_imatrix_rows; the NumPy expression in upstream __init__.py:186-189 reduces in the same order).  The sum
+// of one column is a strictly sequential chain, so the parallelism is the row width; each thread keeps many loads in
+// flight.  `acc` is read and written: a matrix can be fed in pieces, first piece onto zeros.
+constexpr int kSumsqThreads = 64;
+__global__ void __launch_bounds__(kSumsqThreads) sumsq_columns_kernel(const float *__restrict__ rows, int64_t nrows, int64_t n,
+                                                                      float *__restrict__ acc) {
+    grid_dependents_may_launch();
+    grid_dependency_wait();
+    const int64_t c = (int64_t)blockIdx.x * kSumsqThreads + threadIdx.x;
+    if (c >= n) return;
+    float a = acc[c];
+    const float *p = rows + c;
+    int64_t r = 0;
+    constexpr int AHEAD = 32;
+    for (; r + AHEAD <= nrows; r += AHEAD) {
+        float v[AHEAD];
+#pragma unroll
+        for (int k = 0; k < AHEAD; ++k) v[k] = __ldcs(p + (r + k) * n);
+#pragma unroll
+        for (int k = 0; k < AHEAD; ++k) a += v[k] * v[k];
+    }
+    for (; r < nrows; ++r) {
+        const float v = p[r * n];
+        a += v * v;
+    }
+    acc[c] = a;
+}
+
 }  // namespace
+
+cudaError_t launch_sumsq_columns(const float *rows, int64_t nrows, int64_t n, float *acc, cudaStream_t stream) {
+    if (nrows <= 0 || n <= 0) return cudaSuccess;
+    const int64_t grid = (n + kSumsqThreads - 1) / kSumsqThreads;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const cudaError_t e = launch_overlapped(sumsq_columns_kernel, (unsigned)grid, kSumsqThreads, stream, rows, nrows, n, acc);
+    count_launch();
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
 
 // src_dtype: 1 fp16, 2 bf16 (the codes of LIBGGUF_CUDA_DEQUANTIZE_DTYPE_*).
 cudaError_t launch_widen(int src_dtype, const void *src, float *dst, int64_t n, cudaStream_t stream) {

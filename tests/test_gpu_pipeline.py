@@ -7,6 +7,18 @@ pytestmark = pytest.mark.gpu
 torch = pytest.importorskip("torch")
 
 
+@pytest.fixture(scope="module")
+def checker():
+    from oracle import reference
+    if reference.available("ref"):
+        return reference.load("ref")
+    import subprocess
+    from pathlib import Path
+    if not reference.available("port"):
+        subprocess.run(["make", "-C", str(Path(__file__).parents[1] / "oracle"), "oracle"], check=True, capture_output=True)
+    return reference.load("port")
+
+
 def _tensors(rng, pinned):
     specs = [(12, 300, 1024), (14, 130, 512), (8, 77, 256), (10, 64, 768), (18, 40, 512)]
     out = []
@@ -74,8 +86,40 @@ def test_pipeline_rejects_bad_batches(gguf):
     with ConversionPipeline([0]) as pipe:
         with pytest.raises(ValueError):
             pipe.quantize([(12, x, None, np.zeros(10, np.uint8))])
-        with pytest.raises(RuntimeError, match="requires an imatrix"):
-            pipe.quantize([(16, x, None, np.zeros(4 * 66, np.uint8))])
+
+
+@pytest.mark.parametrize("kind", ["float32", "float16"])
+def test_missing_importance_weights_are_derived_from_the_tensor(gguf, checker, kind):
+    """A type that requires an imatrix and gets none: the pipeline takes the column sums of squares of the whole
+    tensor (row order, like upstream) and quantizes with them, whatever the shard size."""
+    from libgguf_b200.convert import ConversionPipeline
+    rng = np.random.default_rng(9)
+    x = (rng.standard_normal((150, 512)) * 0.3).astype(np.float32)
+    src = x.astype(np.float16) if kind == "float16" else x
+    wide = src.astype(np.float32)
+    weights = np.sum(wide * wide, axis=0, dtype=np.float32)
+    assert np.array_equal(gguf.auto_imatrix(wide).view(np.uint32), weights.view(np.uint32))
+    for qtype in (16, 19):
+        dst = np.zeros(150 * gguf.row_size(qtype, 512), np.uint8)
+        with ConversionPipeline([0], slots=2, chunk_bytes=40 << 10) as pipe:
+            pipe.quantize([(qtype, src, None, dst)])
+        want = checker.quantize_rows(wide, qtype, weights)
+        assert np.array_equal(dst, np.ascontiguousarray(want).view(np.uint8).reshape(-1))
+        assert np.array_equal(gguf.quantize_rows(wide, qtype).reshape(-1), dst)
+
+
+def test_accumulate_imatrix_entry_point_continues_a_running_sum(gguf):
+    from libgguf_b200._native import lib
+    rng = np.random.default_rng(10)
+    x = rng.standard_normal((333, 200)).astype(np.float32)
+    want = np.sum(x * x, axis=0, dtype=np.float32)
+    d = torch.from_numpy(x).cuda()
+    acc = torch.zeros(200, dtype=torch.float32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    for r0, r1 in ((0, 100), (100, 101), (101, 333)):
+        assert lib.libgguf_cuda_accumulate_imatrix_on_stream(d[r0:r1].data_ptr(), r1 - r0, 200, acc.data_ptr(), stream) == 0
+    assert np.array_equal(acc.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    assert lib.libgguf_cuda_accumulate_imatrix_on_stream(d.data_ptr(), 1, 0, acc.data_ptr(), stream) != 0
 
 
 @pytest.mark.parametrize("kind", ["float16", "bfloat16"])
