@@ -15,6 +15,7 @@ Inputs live in HBM; every timed launch uses one of NSETS distinct input/output b
 from __future__ import annotations
 
 import json
+import os
 import statistics
 import time
 
@@ -193,6 +194,24 @@ def statistics_mean(values):
     return sum(values) / len(values)
 
 
+def bind_to_gpu_cpus(device_index):
+    """One process per GPU: run on the CPUs NVML lists as local to the GPU, so that the pinned buffers this process
+    allocates (first touch) sit on the memory node next to the GPU's PCIe root.  Returns the CPU list or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = [64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return allowed
+    except Exception:
+        return None
+    return None
+
+
 def as_numpy_source(torch, t):
     """Pinned torch tensor -> the numpy view the pipeline takes (bfloat16 as uint16 bit patterns)."""
     return t.view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.numpy()
@@ -214,6 +233,9 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
     from libgguf_b200 import row_size
     from libgguf_b200.convert import ConversionPipeline, llama3_8b_plan, max_over_ranks, rank_batch
     per_process = world > 1
+    affinity = None
+    if per_process and os.environ.get("LIBGGUF_BENCH_CPU_AFFINITY", "1") != "0":
+        affinity = bind_to_gpu_cpus(int(device.index or 0))
     ndev = world if per_process else min(args.gpus, torch.cuda.device_count())
     devices = [int(device.index or 0)] if per_process else list(range(ndev))
     plan = llama3_8b_plan()
@@ -275,4 +297,5 @@ def run_convert(args, torch, dist, lib, device, rank, world, hbm):
                                        "source_dtype": args.src_dtype, "source_bytes_fp32_equivalent": in_bytes,
                                        "source_bytes_over_the_link": link_bytes, "output_bytes": out_bytes,
                                        "note": "layer sources shared by the 32 layers (one 0.87 GB layer + 2.1 GB embedding resident in pinned memory)"},
-        "elements_per_s": in_bytes / 4 / best, "all_times_s": [round(x, 4) for x in times], "pipeline_rank0": stats, "spot_check_ok": ok}))
+        "elements_per_s": in_bytes / 4 / best, "all_times_s": [round(x, 4) for x in times], "pipeline_rank0": stats, "spot_check_ok": ok,
+        "cpu_affinity_rank0": (f"{affinity[0]}-{affinity[-1]} ({len(affinity)} cpus)" if affinity else None)}))

@@ -132,6 +132,10 @@ LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches
  * compared.  Modes 1 and 2 look only at the inputs the quantizers route there (finite, |x| <= 2^20 * scale). */
 LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4_mode(float scale, int mode, uint64_t *mismatches, uint64_t *fallbacks);
 
+/* Number of CUDA devices visible to the process (no upstream counterpart; the converter front end uses it to
+ * default to all GPUs). */
+LIBGGUF_CUDA_API int libgguf_cuda_device_count(int *count);
+
 /* Device-side source decode, no upstream counterpart (upstream widens 16-bit checkpoints on the CPU before the upload:
  * csrc/quantize_gguf.cpp:1415-1442, :2106-2112).  `source_dtype` uses the LIBGGUF_CUDA_DEQUANTIZE_DTYPE_* codes:
  * F16 or BF16 values are widened to fp32 exactly as the host code does (bf16: 16-bit shift; fp16: exact conversion).

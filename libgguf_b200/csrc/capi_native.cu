@@ -333,6 +333,14 @@ int libgguf_cuda_quantize_f32_rows_on_stream(const float *device_input, const fl
                         reinterpret_cast<cudaStream_t>(stream));
 }
 
+int libgguf_cuda_device_count(int *count) {
+    if (!count) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "count must not be null");
+    *count = 0;
+    const cudaError_t error = cudaGetDeviceCount(count);
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    return ok(nullptr);
+}
+
 int libgguf_cuda_accumulate_imatrix_on_stream(const float *device_rows, int64_t rows, int64_t n_per_row, float *device_imatrix,
                                               void *stream) {
     if (rows < 0 || n_per_row <= 0 || !device_imatrix || (rows > 0 && !device_rows))

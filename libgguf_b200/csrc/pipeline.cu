@@ -82,6 +82,9 @@ struct libgguf_cuda_pipeline {
 
 namespace {
 
+// F32 / F16 / BF16 as the target: plain storage conversion of the rows (upstream libgguf_storage.cpp:105-125)
+bool is_storage_type(int64_t qtype) { return qtype == GGML_TYPE_F32 || qtype == GGML_TYPE_F16 || qtype == GGML_TYPE_BF16; }
+
 size_t source_elem_size(const int32_t *dtypes, int i) { return dtypes && dtypes[i] != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32 ? 2 : 4; }
 
 std::vector<Shard> plan_shards(const libgguf_cuda_tensor_desc *t, const int32_t *dtypes, int n, size_t chunk_bytes) {
@@ -255,8 +258,9 @@ void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
         const size_t esz = source_elem_size(batch->dtypes, cur.tensor);
         const char *src = (const char *)t.src + (size_t)cur.row0 * t.n_per_row * esz;
         char *dst = (char *)t.dst + (size_t)cur.row0 * out_row;
-        const DeviceState *state = device_state_for((int)t.qtype, dev);
-        ok = state && grow_dev(&s.d_in, &s.d_in_cap, cur.in_bytes) && grow_dev(&s.d_out, &s.d_out_cap, cur.out_bytes);
+        const bool storage = is_storage_type(t.qtype);
+        const DeviceState *state = storage ? nullptr : device_state_for((int)t.qtype, dev);
+        ok = (storage || state) && grow_dev(&s.d_in, &s.d_in_cap, cur.in_bytes) && grow_dev(&s.d_out, &s.d_out_cap, cur.out_bytes);
         if (!ok) { err = "device allocation failed on device " + std::to_string(dev); break; }
         const void *h2d_from = src;
         if (!batch->src_pinned[cur.tensor]) {
@@ -285,7 +289,9 @@ void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
             if (e == cudaSuccess) e = launch_widen(batch->dtypes[cur.tensor], s.d_in, (float *)s.d_wide, cur.rows * t.n_per_row, s.stream);
             d_f32 = (const float *)s.d_wide;
         }
-        if (e == cudaSuccess) e = launch_quantize((int)t.qtype, d_f32, d_im, s.d_out, cur.rows, t.n_per_row, state, s.stream);
+        if (e == cudaSuccess)
+            e = storage ? launch_store((int)t.qtype, d_f32, s.d_out, cur.rows * t.n_per_row, s.stream)
+                        : launch_quantize((int)t.qtype, d_f32, d_im, s.d_out, cur.rows, t.n_per_row, state, s.stream);
         if (e == cudaSuccess) e = cudaMemcpyAsync(d2h_to, s.d_out, cur.out_bytes, cudaMemcpyDeviceToHost, s.stream);
         if (e == cudaSuccess) e = cudaEventRecord(s.done, s.stream);
         if (e != cudaSuccess) { err = cudaGetErrorString(e); cudaGetLastError(); ok = false; break; }
@@ -412,7 +418,7 @@ int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libg
             pipe->last_error = "invalid tensor descriptor";
             return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;
         }
-        if (t.qtype < 0 || t.qtype >= GGML_TYPE_COUNT || !quantize_supported((int)t.qtype) ||
+        if (t.qtype < 0 || t.qtype >= GGML_TYPE_COUNT || !(quantize_supported((int)t.qtype) || is_storage_type(t.qtype)) ||
             libgguf_row_size((enum ggml_type)t.qtype, t.n_per_row) == 0) {
             pipe->last_error = "unsupported quantization type or row width";
             return LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE;
