@@ -502,7 +502,10 @@ GGUF_D uint32_t lds_u16(const uint8_t *p) { return *reinterpret_cast<const uint1
 GGUF_D float half_hw(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 
 // Four quants in the bytes of w -> v[0..3] = scale * (byte - offset) [- minus], packed two-wide.
-// neg_bias = -(2^23 + offset).
+// neg_bias = -(2^23 + offset).  The assembler contracts a packed multiply that feeds a packed add into one
+// fused instruction even with explicit rounding modes; that is harmless here because the product
+// scale * level is exact for every type that has a second constant (an 11-bit fp16 scale times a
+// sub-scale of at most 6 bits times a level of at most 5 bits), so rounding once or twice is the same.
 template <bool HAS_MIN>
 GGUF_D void affine4(uint32_t w, float neg_bias, float2 c, float *v) {
     const float2 nb = make_float2(neg_bias, neg_bias), sc = make_float2(c.x, c.x), nm = make_float2(-c.y, -c.y);

@@ -44,6 +44,21 @@ GGUF_D float round_clamp(float v, float lo, float hi) {
     }
 }
 
+// Two-wide helpers for evaluating two candidates at once.  Only additions are issued as packed instructions: the
+// assembler contracts a packed multiply that feeds a packed add into one fused multiply-add even when both carry an
+// explicit rounding mode (unlike the scalar instructions), which would change the rounding of every product-sum here.
+// Products are therefore scalar multiplies, whose results the packed adds consume unfused.
+GGUF_D float2 mul2_unfused(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+GGUF_D float2 mul2_unfused(float a, float2 b) { return make_float2(__fmul_rn(a, b.x), __fmul_rn(a, b.y)); }
+GGUF_D float2 splat2(float a) { return make_float2(a, a); }
+// nearest integer of both lanes for |v| < 2^22, clamped to [lo, hi]
+GGUF_D float2 round_clamp2(float2 v, float lo, float hi) {
+    float2 r = __fadd2_rn(__fadd2_rn(v, splat2(kRoundMagic)), splat2(-kRoundMagic));
+    r.x = fminf(fmaxf(r.x, lo), hi);
+    r.y = fminf(fmaxf(r.y, lo), hi);
+    return r;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Affine search: levels 0..nmax, value = scale*level - the_min.
 // upstream libgguf_common.h:574-670 (make_qkx2_quants) and :688-785 (make_qkx3_quants); with
@@ -174,21 +189,31 @@ GGUF_D float search_scale_sym(const float (&x)[N], const float (&qw)[N], int nma
     float best_iscale = iscale;
     float scale = suml2 ? sumlx / suml2 : 0.0f;
     float best = scale * sumlx;
-    for (int is = -9; is <= 9; ++is) {
-        if (is == 0) continue;
-        iscale = -(fnmax + 0.1f * (float)is) / max;
-        sumlx = suml2 = 0;
+    // The 18 candidates is = -9..-1, 1..9 do not depend on one another (only the acceptance test looks at the
+    // running best), so two are evaluated at a time, their sums in the two lanes of packed adds (every lane
+    // rounded like the scalar instruction), and then offered in upstream's order.
+#pragma unroll 1
+    for (int pair = 0; pair < 9; ++pair) {
+        const int is_a = pair < 4 ? 2 * pair - 9 : (pair == 4 ? -1 : 2 * pair - 8);
+        const int is_b = pair < 4 ? is_a + 1 : (pair == 4 ? 1 : is_a + 1);
+        const float2 isc = make_float2(-(fnmax + 0.1f * (float)is_a) / max, -(fnmax + 0.1f * (float)is_b) / max);
+        float2 slx = make_float2(0.f, 0.f), sl2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < N; ++i) {
-            const float l = round_clamp<true>(iscale * x[i], lo, hi);
+            const float2 l = round_clamp2(mul2_unfused(x[i], isc), lo, hi);
             const float w = HAS_W ? qw[i] : x[i] * x[i];
-            sumlx += w * x[i] * l;
-            suml2 += w * l * l;
+            slx = __fadd2_rn(slx, mul2_unfused(w * x[i], l));
+            sl2 = __fadd2_rn(sl2, mul2_unfused(mul2_unfused(w, l), l));
         }
-        if (suml2 > 0 && sumlx * sumlx > best * suml2) {
-            best_iscale = iscale;
-            scale = sumlx / suml2;
-            best = scale * sumlx;
+        if (sl2.x > 0 && slx.x * slx.x > best * sl2.x) {
+            best_iscale = isc.x;
+            scale = slx.x / sl2.x;
+            best = scale * slx.x;
+        }
+        if (sl2.y > 0 && slx.y * slx.y > best * sl2.y) {
+            best_iscale = isc.y;
+            scale = slx.y / sl2.y;
+            best = scale * slx.y;
         }
     }
     // Levels of the accepted candidate, recomputed once instead of stored on every acceptance.
