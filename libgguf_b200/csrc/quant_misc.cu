@@ -90,17 +90,18 @@ __global__ void __launch_bounds__(kThreads) legacy_weighted_kernel(const float *
     }
 }
 
-// Nearest of the 16 non-linear levels, upstream's bisection with its tie rule
-// (upstream libgguf_common.h:301-317).  `val` is a shared-memory copy of the level table.
-GGUF_D int best_level(const float *val, float x) {
-    if (x <= val[0]) return 0;
-    if (x >= val[15]) return 15;
-    int ml = 0, mu = 15;
-    while (mu - ml > 1) {
-        const int mav = (ml + mu) / 2;
-        if (x < val[mav]) mu = mav; else ml = mav;
-    }
-    return x - val[mu - 1] < val[mu] - x ? mu - 1 : mu;
+// Nearest of the 16 non-linear levels with upstream's rule (libgguf_common.h:301-317): 0 at or below the first
+// level, 15 at or above the last (and for NaN), otherwise the bisection's bracket [val[m], val[m+1]) around x,
+// the lower level only when it is strictly closer.  The levels are integers, so the bracket of x is the bracket of
+// floor(x): `bracket[floor(x) + 127]` replaces the bisection (floor by one round-down add of 2^23 + 127).
+// `val`: shared-memory copy of the level table; `bracket`: 240 bytes, entry i = largest m <= 14 with val[m] <= i - 127.
+GGUF_D int best_level(const float *val, const uint8_t *bracket, float x) {
+    const float xc = fminf(fmaxf(x, -127.f), 112.5f);
+    const int m = bracket[__float_as_uint(__fadd_rd(xc, 8388735.f)) & 0xFF];
+    int best = (x - val[m] < val[m + 1] - x) ? m : m + 1;
+    if (x <= -127.f) best = 0;
+    if (!(x < 113.f)) best = 15;
+    return best;
 }
 
 // IQ4_NL (XS = false, blocks of 32 stand alone) and IQ4_XS (XS = true, 8 blocks per super-block
@@ -110,7 +111,13 @@ template <bool XS>
 __global__ void __launch_bounds__(kThreads) quant_iq4_kernel(const float *__restrict__ src, const float *__restrict__ qw,
                                                             uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row) {
     __shared__ float val[16];
+    __shared__ uint8_t bracket[240];
     if (threadIdx.x < 16) val[threadIdx.x] = (float)k_iq4nl_values[threadIdx.x];
+    for (int i = threadIdx.x; i < 240; i += kThreads) {
+        int m = 0;
+        for (int k = 1; k <= 14; ++k) if ((int)k_iq4nl_values[k] <= i - 127) m = k;
+        bracket[i] = (uint8_t)m;
+    }
     __syncthreads();
     const int lane = threadIdx.x & 31, j8 = lane & 7, gbase = lane & ~7;
     int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -157,7 +164,7 @@ __global__ void __launch_bounds__(kThreads) quant_iq4_kernel(const float *__rest
         float sumqx = 0, sumq2 = 0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-            const float q = val[best_level(val, id * x[j])];
+            const float q = val[best_level(val, bracket, id * x[j])];
             sumqx += w[j] * q * x[j];
             sumq2 += w[j] * q * q;
         }
@@ -168,7 +175,7 @@ __global__ void __launch_bounds__(kThreads) quant_iq4_kernel(const float *__rest
             sumqx = sumq2 = 0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const float q = val[best_level(val, id * x[j])];
+                const float q = val[best_level(val, bracket, id * x[j])];
                 sumqx += w[j] * q * x[j];
                 sumq2 += w[j] * q * q;
             }
@@ -185,7 +192,7 @@ __global__ void __launch_bounds__(kThreads) quant_iq4_kernel(const float *__rest
         uint8_t *out = dst + blk * 18;
         const float id = scale ? 1 / scale : 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) Lb[j] = (uint8_t)best_level(val, id * x[j]);
+        for (int j = 0; j < 32; ++j) Lb[j] = (uint8_t)best_level(val, bracket, id * x[j]);
         if (!active) return;
         st16(out, f32_to_half_bits(scale));
 #pragma unroll
@@ -209,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) quant_iq4_kernel(const float *__rest
         const float dl = d * (float)l;
         const float idl = dl ? 1 / dl : 0.f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) Lb[j] = (uint8_t)best_level(val, idl * x[j]);
+        for (int j = 0; j < 32; ++j) Lb[j] = (uint8_t)best_level(val, bracket, idl * x[j]);
         l += 32;
         // gather the 8 scale codes of the super-block
         int codes[8];
