@@ -7,8 +7,8 @@
 // candidate scales in which every group of 8 (or 4) magnitudes is rounded to the lattice and,
 // when the rounded point is not a codebook entry, replaced by the best of its precomputed
 // neighbours, the accept/reject chain on (sumqx, sumq2), the final re-projection, and the 4-bit
-// block scale against the super-block maximum.  The codebook (<= 8 KB) is staged in shared
-// memory once per CTA; the lattice map and neighbour lists stay in global memory (L2 resident).
+// block scale against the super-block maximum.  The codebook is staged in shared
+// memory as floats (<= 32 KB) once per CTA; the lattice map and neighbour lists stay in global memory (L2 resident).
 // upstream: csrc/quant/iq2_xxs.cpp:4-224, iq2_xs.cpp:4-230, iq2_s.cpp:4-218, iq3_xxs.cpp:4-273,
 // iq3_s.cpp:5-233, csrc/common/libgguf_iq_tables.cpp:434-462 and :683-711.
 #include <float.h>
@@ -22,7 +22,7 @@ namespace gguf {
 namespace {
 
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kThreads = 128;
+constexpr int kThreads = 64;
 
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
@@ -53,6 +53,15 @@ template <> struct Traits<GGML_TYPE_IQ3_S> {
 
 GGUF_D void st16(uint8_t *p, uint32_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }
 GGUF_D void st32(uint8_t *p, uint32_t v) { st16(p, v); st16(p + 2, v >> 16); }
+
+// Levels are kept one byte each, four per register.
+template <int NW>
+GGUF_D int lget(const uint32_t (&L)[NW], int i) { return (int)((L[i >> 2] >> (8 * (i & 3))) & 0xFFu); }
+template <int NW>
+GGUF_D void lset(uint32_t (&L)[NW], int i, int v) {
+    const int sh = 8 * (i & 3);
+    L[i >> 2] = (L[i >> 2] & ~(0xFFu << sh)) | ((uint32_t)v << sh);
+}
 
 template <int N>
 GGUF_D void load_group(const float *p, float (&x)[N]) {
@@ -137,26 +146,35 @@ GGUF_D float qp_quants_reg(int nmax, const float (&x)[N], int (&L)[N], const flo
 // sum_i w[i] * (scale*q[i] - x[i])^2 with the terms added in coordinate order.  Writes the
 // winner's levels to L[0..GD) and returns its codebook index.
 template <int GD>
-GGUF_D int best_neighbour(const uint16_t *__restrict__ nb, const uint8_t *grid, const float *xv, const float *wv, float scale,
+GGUF_D int best_neighbour(const uint16_t *__restrict__ nb, const float *gridf, const float *xv, const float *wv, float scale,
                           int *L) {
     const int n = __ldg(nb);
     float best_d2 = FLT_MAX;
     int best = -1;
+    int g_next = __ldg(nb + 1);  // the index of the next entry is fetched while the current one is evaluated
     for (int j = 1; j <= n; ++j) {
-        const int g = __ldg(nb + j);
-        const uint8_t *pg = grid + g * GD;
+        const int g = g_next;
+        g_next = __ldg(nb + (j < n ? j + 1 : j));
+        float q[GD];
+#pragma unroll
+        for (int v = 0; v < GD / 4; ++v) {
+            const float4 t = *reinterpret_cast<const float4 *>(gridf + g * GD + 4 * v);
+            q[4 * v] = t.x; q[4 * v + 1] = t.y; q[4 * v + 2] = t.z; q[4 * v + 3] = t.w;
+        }
         float d2 = 0;
 #pragma unroll
         for (int i = 0; i < GD; ++i) {
-            const float q = (float)pg[i];
-            const float diff = scale * q - xv[i];
+            const float diff = scale * q[i] - xv[i];
             d2 += wv[i] * diff * diff;
         }
         if (d2 < best_d2) { best_d2 = d2; best = g; }
     }
-    const uint8_t *pg = grid + best * GD;
 #pragma unroll
-    for (int i = 0; i < GD; ++i) L[i] = (pg[i] - 1) / 2;
+    for (int v = 0; v < GD / 4; ++v) {
+        const float4 t = *reinterpret_cast<const float4 *>(gridf + best * GD + 4 * v);
+        // coordinates are 2*level + 1
+        L[4 * v] = ((int)t.x - 1) >> 1; L[4 * v + 1] = ((int)t.y - 1) >> 1; L[4 * v + 2] = ((int)t.z - 1) >> 1; L[4 * v + 3] = ((int)t.w - 1) >> 1;
+    }
     return best;
 }
 
@@ -166,9 +184,9 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
                                                              IqSearchTable tab) {
     using T = Traits<TYPE>;
     constexpr int BS = T::BS, GD = T::GD, NG = BS / GD, NS = BS / 8, W = 256 / BS;  // W lanes per super-block
-    extern __shared__ __align__(16) uint8_t grid[];
-    for (int i = threadIdx.x; i < tab.grid_size * GD / 4; i += kThreads)
-        reinterpret_cast<uint32_t *>(grid)[i] = __ldg(reinterpret_cast<const uint32_t *>(tab.grid) + i);
+    // the codebook's coordinates as floats: no conversion in the neighbour scans, one or two 16-byte reads per entry
+    extern __shared__ __align__(16) float gridf[];
+    for (int i = threadIdx.x; i < tab.grid_size * GD; i += kThreads) gridf[i] = (float)__ldg(tab.grid + i);
     __syncthreads();
 
     const int lane = threadIdx.x & 31, j = lane & (W - 1), gbase = lane & ~(W - 1);
@@ -232,20 +250,22 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
 #pragma unroll
     for (int i = 1; i < BS; ++i) max = max > xval[i] ? max : xval[i];
 
-    int L[BS];
+    uint32_t L[BS / 4];
 #pragma unroll
-    for (int i = 0; i < BS; ++i) L[i] = 0;
+    for (int i = 0; i < BS / 4; ++i) L[i] = 0;
     float scale = 0.f;
     bool skipped = T::EPS > 0.f ? (max < T::EPS) : !(max != 0.f);
     float eff_max = max;
     if (!skipped && T::QP_INIT) {
-        scale = qp_quants_reg<BS>(T::KMAXQ + 1, xval, L, weight);
+        int Linit[BS];
+        scale = qp_quants_reg<BS>(T::KMAXQ + 1, xval, Linit, weight);
         eff_max = scale * T::KMAXQ;
         if (eff_max <= 0) {
             skipped = true;
             scale = 0.f;
+        } else {
 #pragma unroll
-            for (int i = 0; i < BS; ++i) L[i] = 0;
+            for (int i = 0; i < BS; ++i) lset(L, i, Linit[i]);
         }
     }
     int gidx[NG];
@@ -256,37 +276,44 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
         float best = 0;
         if (!T::QP_INIT) scale = max / (2 * T::KMAXQ - 1);
         uint32_t on_grid = TYPE == GGML_TYPE_IQ3_S ? 0u : 0xFFFFFFFFu;  // bit k: group k of the accepted candidate was a codebook point
+        // candidate by candidate, a neighbour scan wherever the rounding leaves the codebook
         for (int is = -T::IS_MAX; is <= T::IS_MAX; ++is) {
             const float id = ((float)(2 * T::KMAXQ - 1) + (float)is * T::STEP) / eff_max;
             const float this_scale = 1 / id;
-            int Laux[BS];
+            uint32_t Laux[BS / 4];
             uint32_t on_aux = 0;
+            // the block's sums run over the elements in order, i.e. group by group: each group adds its terms as
+            // soon as its levels are known
+            float sumqx = 0, sumq2 = 0;
 #pragma unroll
             for (int k = 0; k < NG; ++k) {
                 uint32_t u = 0;
+                int lk[GD];
 #pragma unroll
                 for (int i = 0; i < GD; ++i) {
                     const int l = nearest_int(0.5f * (id * xval[GD * k + i] - 1));
-                    Laux[GD * k + i] = imax(0, imin(T::KMAXQ - 1, l));
-                    u |= (uint32_t)Laux[GD * k + i] << (T::BITS * i);
+                    lk[i] = imax(0, imin(T::KMAXQ - 1, l));
+                    u |= (uint32_t)lk[i] << (T::BITS * i);
                 }
                 const int m = __ldg(tab.map + u);
-                if (m < 0) best_neighbour<GD>(tab.neighbours + (-m - 1), grid, xval + GD * k, waux + GD * k, this_scale, Laux + GD * k);
+                if (m < 0) best_neighbour<GD>(tab.neighbours + (-m - 1), gridf, xval + GD * k, waux + GD * k, this_scale, lk);
                 else on_aux |= 1u << k;
-            }
-            float sumqx = 0, sumq2 = 0;
 #pragma unroll
-            for (int i = 0; i < BS; ++i) {
-                const float w = weight[i];
-                const float q = (float)(2 * Laux[i] + 1);
-                sumqx += w * xval[i] * q;
-                sumq2 += w * q * q;
+                for (int i = 0; i < GD; ++i) {
+                    const float w = weight[GD * k + i];
+                    const float q = (float)(2 * lk[i] + 1);
+                    sumqx += w * xval[GD * k + i] * q;
+                    sumq2 += w * q * q;
+                }
+#pragma unroll
+                for (int v = 0; v < GD / 4; ++v)
+                    Laux[(GD * k) / 4 + v] = (uint32_t)lk[4 * v] | ((uint32_t)lk[4 * v + 1] << 8) | ((uint32_t)lk[4 * v + 2] << 16) | ((uint32_t)lk[4 * v + 3] << 24);
             }
             if (sumq2 > 0 && sumqx * sumqx > best * sumq2) {
                 scale = sumqx / sumq2;
                 best = scale * sumqx;
 #pragma unroll
-                for (int i = 0; i < BS; ++i) L[i] = Laux[i];
+                for (int i = 0; i < BS / 4; ++i) L[i] = Laux[i];
                 on_grid = on_aux;
             }
         }
@@ -311,22 +338,21 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
                 const int m = __ldg(tab.map + u);
                 if (TYPE == GGML_TYPE_IQ2_XS || TYPE == GGML_TYPE_IQ2_S) {
                     // levels become the rounding, or the best neighbour when the rounding is off the codebook
-                    if (m < 0) best_neighbour<GD>(tab.neighbours + (-m - 1), grid, xval + GD * k, waux + GD * k, scale, Lr);
+                    if (m < 0) best_neighbour<GD>(tab.neighbours + (-m - 1), gridf, xval + GD * k, waux + GD * k, scale, Lr);
 #pragma unroll
-                    for (int i = 0; i < GD; ++i) L[GD * k + i] = Lr[i];
+                    for (int i = 0; i < GD; ++i) lset(L, GD * k + i, Lr[i]);
                 } else {
                     int g = m;
-                    if (m < 0) g = best_neighbour<GD>(tab.neighbours + (-m - 1), grid, xval + GD * k, waux + GD * k, scale, Lr);
-                    const uint8_t *pg = grid + g * GD;
+                    if (m < 0) g = best_neighbour<GD>(tab.neighbours + (-m - 1), gridf, xval + GD * k, waux + GD * k, scale, Lr);
 #pragma unroll
-                    for (int i = 0; i < GD; ++i) L[GD * k + i] = (pg[i] - 1) / 2;
+                    for (int i = 0; i < GD; ++i) lset(L, GD * k + i, ((int)gridf[g * GD + i] - 1) >> 1);
                 }
             }
             float sumqx = 0, sumq2 = 0;
 #pragma unroll
             for (int i = 0; i < BS; ++i) {
                 const float w = weight[i];
-                const float q = (float)(2 * L[i] + 1);
+                const float q = (float)(2 * lget(L, i) + 1);
                 sumqx += w * xval[i] * q;
                 sumq2 += w * q * q;
             }
@@ -342,7 +368,7 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
         for (int k = 0; k < NG; ++k) {
             uint32_t u = 0;
 #pragma unroll
-            for (int i = 0; i < GD; ++i) u |= (uint32_t)L[GD * k + i] << (T::BITS * i);
+            for (int i = 0; i < GD; ++i) u |= (uint32_t)lget(L, GD * k + i) << (T::BITS * i);
             const int m = __ldg(tab.map + u);
             gidx[k] = m < 0 ? 0 : m;  // upstream aborts here; every path above ends on a codebook point
         }
@@ -436,7 +462,7 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
     if (!tab.grid) return cudaErrorInvalidValue;
     const int64_t nblocks = nelems / T::BS;
     if (nblocks <= 0) return cudaSuccess;
-    const size_t smem = (size_t)tab.grid_size * T::GD;
+    const size_t smem = (size_t)tab.grid_size * T::GD * sizeof(float);  // at most 32 KB
     const int64_t grid = (nblocks + kThreads - 1) / kThreads;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
     quant_iq23_kernel<TYPE><<<(unsigned)grid, kThreads, smem, stream>>>(src, qw, static_cast<uint8_t *>(dst), nblocks, n_per_row, tab);
