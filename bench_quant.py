@@ -22,7 +22,8 @@ import time
 NSETS = 3
 FP32_LANES = 148 * 128  # fp32 lanes of a B200
 
-# flop per element of the upstream algorithm (no FMA), for the pipe-bound encoders
+# flop per element of the upstream algorithm (no FMA), for the pipe-bound encoders: candidates x (operations per
+# element and candidate) of the scale searches
 FLOP_PER_ELEM = {"Q4_K": 480, "Q5_K": 370, "Q2_K": 375, "Q6_K": 280, "Q3_K": 125, "MXFP4": 85, "NVFP4": 85}
 
 BLOCK = {"Q4_0": (32, 18), "Q4_1": (32, 20), "Q5_0": (32, 22), "Q5_1": (32, 24), "Q8_0": (32, 34), "Q1_0": (128, 18),
@@ -75,6 +76,8 @@ def run(args, torch, dist, lib, ops, device, rank, world):
     wl = args.workload
     if wl == "convert":
         return run_convert(args, torch, dist, lib, device, rank, world, hbm)
+    if wl == "convert_file":
+        return run_convert_file(args, torch, lib, rank, world)
     if wl == "dequant_all":
         return run_dequant_all(args, torch, lib, ops, device, rank, world, hbm, peak_kind)
     shapes = {"q4k_roundtrip": (4096, 4096, "normal", ["Q4_K"], False),
@@ -192,6 +195,67 @@ def run_dequant_all(args, torch, lib, ops, device, rank, world, hbm, peak_kind):
 def statistics_mean(values):
     values = list(values)
     return sum(values) / len(values)
+
+
+def run_convert_file(args, torch, lib, rank, world):
+    """The converter as a user runs it: a Llama-shaped bf16 safetensors file (8 of the 32 layers by default, values
+    synthetic) -> `libgguf_b200.quantize_gguf` with --gpus N -> GGUF file, both on a RAM-backed file system when
+    there is one.  Reports fp32-equivalent GB/s of the whole command, file reads and writes included."""
+    import shutil
+    import struct
+    import tempfile
+    import numpy as np
+    from libgguf_b200 import quantize_gguf as qg
+    if rank != 0:
+        return
+    n_layers = int(os.environ.get("LIBGGUF_BENCH_LAYERS", "8"))
+    base = "/dev/shm" if os.path.isdir("/dev/shm") else None
+    tmp = tempfile.mkdtemp(prefix="libgguf_bench_", dir=base)
+    try:
+        shapes = [("model.embed_tokens.weight", (128256, 4096))]
+        for i in range(n_layers):
+            p = f"model.layers.{i}."
+            shapes += [(p + "self_attn.q_proj.weight", (4096, 4096)), (p + "self_attn.k_proj.weight", (1024, 4096)),
+                       (p + "self_attn.v_proj.weight", (1024, 4096)), (p + "self_attn.o_proj.weight", (4096, 4096)),
+                       (p + "mlp.gate_proj.weight", (14336, 4096)), (p + "mlp.up_proj.weight", (14336, 4096)),
+                       (p + "mlp.down_proj.weight", (4096, 14336)), (p + "input_layernorm.weight", (4096,))]
+        shapes += [("model.norm.weight", (4096,)), ("lm_head.weight", (128256, 4096))]
+        rng = np.random.default_rng(0)
+        block = (rng.standard_normal(1 << 24, dtype=np.float32) * 0.02).view(np.uint32) >> 16
+        block = block.astype(np.uint16)   # 16 Mi bf16 values, tiled over every tensor
+        header, offset = {}, 0
+        for name, shape in shapes:
+            n = int(np.prod(shape)) * 2
+            header[name] = {"dtype": "BF16", "shape": list(shape), "data_offsets": [offset, offset + n]}
+            offset += n
+        text = json.dumps(header, separators=(",", ":")).encode()
+        text += b" " * (-len(text) % 8)
+        src, dst = os.path.join(tmp, "model.safetensors"), os.path.join(tmp, "model.gguf")
+        with open(src, "wb") as f:
+            f.write(struct.pack("<Q", len(text)) + text)
+            for name, shape in shapes:
+                n = int(np.prod(shape))
+                for start in range(0, n, block.size):
+                    f.write(block[: min(block.size, n - start)].tobytes())
+        elements = offset // 2
+        ndev = min(args.gpus, torch.cuda.device_count())
+        times = []
+        for _ in range(1 + max(1, min(args.steps, 3))):
+            t0 = time.perf_counter()
+            rc = qg.main(["--src", src, "--dst", dst, "--qtype", "Q4_K_M", "--overwrite", "--gpus", str(ndev)])
+            times.append(time.perf_counter() - t0)
+            if rc != 0:
+                raise RuntimeError("converter failed")
+        best = min(times[1:])
+        print(json.dumps({"metric": "conversion GB/s of fp32-equivalent source, file to file", "value": elements * 4 / best / 1e9, "unit": "GB/s",
+                          "n_gpus": ndev, "steps": len(times) - 1, "warmup": 1, "ms_per_step": best * 1e3, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": f"convert_file: Llama-shaped bf16 safetensors, {n_layers} layers, Q4_K_M -> GGUF, through the command line front end",
+                                     "elements": elements, "source_file_bytes": os.path.getsize(src), "output_file_bytes": os.path.getsize(dst),
+                                     "directory": "RAM-backed" if base else "default temporary directory"},
+                          "all_times_s": [round(t, 3) for t in times]}))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
 
 
 def bind_to_gpu_cpus(device_index):

@@ -3,7 +3,8 @@
 // upstream's converter (csrc/quantize_gguf.cpp:1990-2223 with cuda_converter_context, :1732-1931)
 // walks the tensor plan on one GPU with two pinned host slots and one stream: read rows into a
 // pinned slot, h2d, quantize, d2h, write.  Here the same loop is a pool of per-GPU workers:
-//   * every tensor of a batch is cut into shards of whole rows (at most `chunk_bytes` of fp32),
+//   * every tensor of a batch is cut into shards of whole rows (at most `chunk_bytes` of source bytes; a 16-bit
+//     source is uploaded as it is and widened on the GPU; F32 / F16 / BF16 targets are converted there too),
 //   * shards go into one queue, largest first; each GPU's worker thread pulls the next shard when
 //     one of its slots frees up, so load balances itself and no GPU waits for another,
 //   * a worker owns `slots` independent streams, each with its own device input/output buffers
@@ -11,6 +12,8 @@
 //     shards go to different slots so copies in both directions overlap the kernels,
 //   * host memory that is already pinned (cudaHostAlloc / cudaHostRegister) is copied from and
 //     to directly; pageable memory goes through the slot's pinned staging,
+//   * a type that needs importance weights and got none gets them from a first pass over the tensor (column sums
+//     of squares in row order) on the first GPU,
 //   * there is no device-to-device traffic and no collective: a shard's bytes only ever cross
 //     its own GPU's PCIe link.  Results land at their row offset in the caller's output.
 // Host waits are cudaEventQuery polls with a deadline; a worker that sees an error (or an
