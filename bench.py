@@ -49,24 +49,77 @@ def peaks() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    """SM clock, power and throttle reasons sampled while the timed region runs: NVML queries from a thread of this
+    process (about a sample per millisecond, so even a region of a few milliseconds is covered), or, when the NVML
+    binding is missing, an `nvidia-smi -lms` child process."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, device_index: int):
         self.device_index = device_index
-        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.file = None
         self.proc = None
+        self.thread = None
+        self.samples = []          # (sm MHz, power W, reasons bitmask)
+        self.running = False
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(device_index))
+            self.max_sm = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    @staticmethod
+    def _physical_index(device_index: int) -> int:
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if device_index < len(ids) and ids[device_index].isdigit():
+                return int(ids[device_index])
+        return device_index
+
+    def _loop(self):
+        nv = self.nvml
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while self.running:
+            try:
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)),
+                                     nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0, int(reasons_fn(self.handle))))
+            except Exception:
+                break
+            time.sleep(0.0005)
 
     def start(self):
+        if self.nvml is not None:
+            import threading
+            self.running = True
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+            return
         try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-lms", "100", "-i", str(self.device_index)], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self.running = False
+            self.thread.join(timeout=2)
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": self.max_sm, "reasons": ["no samples"]}
+            mask = 0
+            for _, _, r in self.samples:
+                mask |= r
+            return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": self.max_sm, "samples": len(self.samples),
+                    "power_w_max": max(s[1] for s in self.samples), "reasons": sorted(n for bit, n in self.REASON_BITS.items() if mask & bit),
+                    "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -88,7 +141,7 @@ class ClockSampler:
                 if v.strip().lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "samples": len(rows),
-                "power_w_max": max(float(r[3]) for r in rows), "reasons": sorted(reasons)}
+                "power_w_max": max(float(r[3]) for r in rows), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -173,7 +226,7 @@ def run_reference_arm(args, rank: int, world: int) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="dequant_sweep")
