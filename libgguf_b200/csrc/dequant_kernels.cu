@@ -1170,43 +1170,39 @@ GGUF_D void store16(OutT *dst, const float *v) {
     }
 }
 
-// 16-byte asynchronous copy global -> shared, bypassing L1 and the register file.
-GGUF_D void cp_async16(void *smem, const void *gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
-}
-GGUF_D void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-GGUF_D void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-// Persistent CTAs walk the tiles (8192 elements) with a stride of the grid size.  The encoded bytes of tile i+1
-// are copied global -> shared asynchronously while tile i is decoded: the copy is issued right after the barrier
-// that says every thread has finished reading the buffer it goes into.
 template <int TYPE, class OutT>
 __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                int64_t nblocks) {
     using D = Fast<TYPE>;
     constexpr int TILE_BLOCKS = kTileElems / D::ELEMS;
     constexpr int TILE_BYTES = TILE_BLOCKS * D::BYTES;
-    static_assert(TILE_BYTES % 16 == 0, "tiles start on 16-byte boundaries");
-    constexpr int TILE_VECS = TILE_BYTES / 16;
+    constexpr int TILE_VECS = (TILE_BYTES + 15) / 16;
     constexpr int TILE_GROUPS = kTileElems / D::GROUP;
     constexpr int GROUPS_PER_BLOCK = D::ELEMS / D::GROUP;
-    __shared__ __align__(16) uint8_t tiles[2][TILE_VECS * 16 + 32];
+    __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 32];
     __shared__ float2 consts[TILE_GROUPS];
 
     const int tid = threadIdx.x;
-    const int64_t ntiles = (nblocks + TILE_BLOCKS - 1) / TILE_BLOCKS;
-    auto prefetch = [&](int64_t t, uint8_t *buf) {
-        const int64_t b0 = t * TILE_BLOCKS;
-        const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
-        const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
-        const int nvec = (nb * D::BYTES + 15) >> 4;
+    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
+    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
+    const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
+    const int nvec = (nb * D::BYTES + 15) >> 4;
+    uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+    grid_dependents_may_launch();
+    grid_dependency_wait();
 #pragma unroll
-        for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
-            const int i = k * kThreads + tid;
-            if (i < nvec) cp_async16(buf + 16 * i, g16 + i);
-        }
-        cp_async_commit();
-    };
+    for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
+        const int i = k * kThreads + tid;
+        if (i < nvec) s16[i] = __ldcs(g16 + i);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
+        const int g = k * kThreads + tid;
+        const int blk = g / GROUPS_PER_BLOCK;
+        if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
+    }
+    __syncthreads();
     // call c = u*kThreads + tid: position inside the block (e0) does not depend on u
     constexpr int CALL = CallElems<D>::value;
     constexpr int CALLS_PER_BLOCK = D::ELEMS / CALL;
@@ -1214,37 +1210,17 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
     static_assert(kThreads % CALLS_PER_BLOCK == 0, "a thread keeps its position inside the block across iterations");
     const int e0 = (tid % CALLS_PER_BLOCK) * CALL;
     const int blk0 = tid / CALLS_PER_BLOCK;
+    OutT *out = dst + b0 * D::ELEMS + (int64_t)blk0 * D::ELEMS + e0;
+    const uint8_t *bp = tile + blk0 * D::BYTES;
     const float2 *cp = consts + (blk0 * D::ELEMS + e0) / D::GROUP;
-
-    grid_dependents_may_launch();
-    grid_dependency_wait();
-    int64_t t = blockIdx.x;
-    if (t < ntiles) prefetch(t, tiles[0]);
-    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
-        const uint8_t *tile = tiles[it & 1];
-        cp_async_wait_all();
-        __syncthreads();  // tile t has landed; everybody is done with the other buffer and with consts
-        if (t + gridDim.x < ntiles) prefetch(t + gridDim.x, tiles[(it + 1) & 1]);
-        const int64_t b0 = t * TILE_BLOCKS;
-        const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
 #pragma unroll
-        for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
-            const int g = k * kThreads + tid;
-            const int blk = g / GROUPS_PER_BLOCK;
-            if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
-        }
-        __syncthreads();
-        OutT *out = dst + b0 * D::ELEMS + (int64_t)blk0 * D::ELEMS + e0;
-        const uint8_t *bp = tile + blk0 * D::BYTES;
+    for (int u = 0; u < CALLS_PER_THREAD; ++u) {
+        constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
+        if (blk0 + u * BLOCK_STEP < nb) {
+            float v[CALL];
+            D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
 #pragma unroll
-        for (int u = 0; u < CALLS_PER_THREAD; ++u) {
-            constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
-            if (blk0 + u * BLOCK_STEP < nb) {
-                float v[CALL];
-                D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
-#pragma unroll
-                for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
-            }
+            for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
         }
     }
 }
@@ -1260,16 +1236,8 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
     const int aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
     if constexpr (Fast<TYPE>::kEnabled) {
         if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-            // persistent: as many CTAs as can be resident, fewer for small inputs
-            static const int resident = [] {
-                int dev = 0, sms = 148, per_sm = 4;
-                cudaGetDevice(&dev);
-                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, dequant_fast_kernel<TYPE, OutT>, kThreads, 0);
-                return sms * (per_sm > 0 ? per_sm : 1);
-            }();
-            const cudaError_t launched = launch_overlapped(dequant_fast_kernel<TYPE, OutT>, (unsigned)(grid < resident ? grid : resident),
-                                                           kThreads, stream, static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks);
+            const cudaError_t launched = launch_overlapped(dequant_fast_kernel<TYPE, OutT>, (unsigned)grid, kThreads, stream,
+                                                           static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks);
             count_launch();
             return launched != cudaSuccess ? launched : cudaGetLastError();
         }
