@@ -517,7 +517,79 @@ def plan_file(options: Options):
     return dst, file_type, model, kv, plans, result
 
 
+class _PinnedArena:
+    """A page-locked host buffer from the library (the GPUs copy from / to it directly), seen as a numpy byte array."""
+
+    def __init__(self, lib, ctx, size: int):
+        import ctypes
+        self._lib, self._ctx, self._handle = lib, ctx, ctypes.c_void_p()
+        if lib.libgguf_cuda_host_buffer_create(ctx, size, ctypes.byref(self._handle)) != 0:
+            fail("cannot allocate pinned host memory: " + lib.libgguf_cuda_last_error(ctx).decode())
+        pointer = ctypes.cast(lib.libgguf_cuda_host_buffer_data(self._handle), ctypes.POINTER(ctypes.c_ubyte))
+        self.array = np.ctypeslib.as_array(pointer, shape=(size,))
+
+    def close(self):
+        if self._handle:
+            self.array = None
+            self._lib.libgguf_cuda_host_buffer_destroy(self._ctx, self._handle)
+            self._handle = None
+
+
+def _align(n: int, to: int = 256) -> int:
+    return (n + to - 1) // to * to
+
+
+@dataclass
+class _Piece:
+    plan: TensorPlan
+    row0: int
+    rows: int
+    last: bool      # last piece of its tensor: the alignment padding follows it
+
+    @property
+    def convert(self) -> bool:
+        return self.plan.qtype != self.plan.source_dtype
+
+
+def _pieces(plans, cap: int):
+    """Row ranges of the tensors to convert, none larger than `cap` bytes on either side; other tensors stay whole."""
+    for p in plans:
+        if p.qtype == p.source_dtype:
+            yield _Piece(p, 0, p.n_rows, True)
+            continue
+        row_in = p.n_per_row * SOURCE_DTYPES[p.source_dtype][2]
+        row_out = p.nbytes // p.n_rows
+        per = max(1, min(cap // row_in, cap // row_out))
+        for row0 in range(0, p.n_rows, per):
+            rows = min(per, p.n_rows - row0)
+            yield _Piece(p, row0, rows, row0 + rows == p.n_rows)
+
+
+def _batches(pieces, cap: int):
+    """Consecutive pieces grouped so that their source bytes and their encoded bytes each fit `cap`."""
+    batch, used_in, used_out = [], 0, 0
+    for piece in pieces:
+        p = piece.plan
+        need_in = _align(piece.rows * p.n_per_row * SOURCE_DTYPES[p.source_dtype][2]) if piece.convert else 0
+        need_out = _align(piece.rows * (p.nbytes // p.n_rows)) if piece.convert else 0
+        if batch and (used_in + need_in > cap or used_out + need_out > cap):
+            yield batch
+            batch, used_in, used_out = [], 0, 0
+        batch.append(piece)
+        used_in += need_in
+        used_out += need_out
+    if batch:
+        yield batch
+
+
 def convert(options: Options) -> dict:
+    """Runs the plan: row ranges of the source tensors are read from the file straight into pinned memory by a pool of
+    reader threads (one batch ahead of the GPUs), encoded by the multi-GPU pipeline into pinned memory, and written out
+    in plan order."""
+    import ctypes
+    from concurrent.futures import ThreadPoolExecutor
+
+    from ._native import lib
     from .convert import ConversionPipeline   # needs the CUDA library; planning above does not
 
     dst, _, _, kv, plans, result = plan_file(options)
@@ -526,38 +598,78 @@ def convert(options: Options) -> dict:
     source = np.memmap(options.src, dtype=np.uint8, mode="r")
     n_gpus = options.gpus
     if n_gpus <= 0:
-        import ctypes
-        from ._native import lib
         count = ctypes.c_int(0)
         if lib.libgguf_cuda_device_count(ctypes.byref(count)) != 0 or count.value < 1:
             fail("no CUDA device is available")
         n_gpus = count.value
-    with open(dst, "wb") as out, ConversionPipeline(list(range(n_gpus)), slots=3, chunk_bytes=options.chunk_bytes) as pipe:
-        out.write(head)
-        out.write(b"\0" * (pad_to(len(head)) - len(head)))
-        pending, pending_bytes = [], 0   # (plan, encoded array or None for a plain copy)
+    ctx = ctypes.c_void_p()
+    if lib.libgguf_cuda_context_create(0, ctypes.byref(ctx)) != 0:
+        fail("no CUDA device is available")
+    # two pinned arenas per direction; large enough to keep every GPU's slots busy, small enough to allocate quickly
+    cap = max(1 << 16, min(options.batch_bytes // 4, max(256 << 20, n_gpus * (128 << 20))))
+    chunk = max(1 << 12, min(options.chunk_bytes, cap // (3 * n_gpus)))
+    arenas, fd = [], os.open(options.src, os.O_RDONLY)
+    readers = ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1))
+    READ_PIECE = 16 << 20
 
-        def flush():
-            nonlocal pending, pending_bytes
-            batch = [(int(Q[p.qtype]), src_view(source, p), None, enc) for p, enc in pending if enc is not None]
-            if batch:
-                pipe.quantize(batch)
-            for p, enc in pending:
-                if enc is None:
-                    out.write(source[p.data_begin:p.data_end])
-                else:
-                    out.write(enc)
-                out.write(b"\0" * (pad_to(p.nbytes) - p.nbytes))
-            pending, pending_bytes = [], 0
+    def read_into(view: np.ndarray, file_offset: int):
+        done, total = 0, view.size
+        buffer = memoryview(view)
+        while done < total:
+            got = os.preadv(fd, [buffer[done:total]], file_offset + done)
+            if got <= 0:
+                fail("unexpected end of input file")
+            done += got
 
-        for p in plans:
-            plain_copy = p.qtype == p.source_dtype
-            enc = None if plain_copy else np.empty(p.nbytes, dtype=np.uint8)
-            pending.append((p, enc))
-            pending_bytes += p.nbytes + (p.data_end - p.data_begin)
-            if pending_bytes >= options.batch_bytes:
-                flush()
-        flush()
+    def stage(batch, arena_pair):
+        """Starts the reads of one batch; returns (entries for the pipeline, output view per piece, futures)."""
+        arena_in, arena_out = arena_pair
+        entries, outputs, futures, at_in, at_out = [], [], [], 0, 0
+        for piece in batch:
+            if not piece.convert:
+                outputs.append(None)
+                continue
+            p = piece.plan
+            np_dtype, _, esize = SOURCE_DTYPES[p.source_dtype]
+            nbytes_in, nbytes_out = piece.rows * p.n_per_row * esize, piece.rows * (p.nbytes // p.n_rows)
+            file_at = p.data_begin + piece.row0 * p.n_per_row * esize
+            raw = arena_in.array[at_in:at_in + nbytes_in]
+            for start in range(0, nbytes_in, READ_PIECE):
+                futures.append(readers.submit(read_into, raw[start:min(start + READ_PIECE, nbytes_in)], file_at + start))
+            enc = arena_out.array[at_out:at_out + nbytes_out]
+            entries.append((int(Q[p.qtype]), raw.view(np_dtype).reshape(piece.rows, p.n_per_row), None, enc))
+            outputs.append(enc)
+            at_in += _align(nbytes_in)
+            at_out += _align(nbytes_out)
+        return entries, outputs, futures
+
+    try:
+        batches = list(_batches(_pieces(plans, cap), cap))
+        arenas = [(_PinnedArena(lib, ctx, cap + 4096), _PinnedArena(lib, ctx, cap + 4096)) for _ in range(min(2, len(batches)))]
+        with open(dst, "wb") as out, ConversionPipeline(list(range(n_gpus)), slots=3, chunk_bytes=chunk) as pipe:
+            out.write(head)
+            out.write(b"\0" * (pad_to(len(head)) - len(head)))
+            staged = stage(batches[0], arenas[0]) if batches else None
+            for i, batch in enumerate(batches):
+                entries, outputs, futures = staged
+                for f in futures:
+                    f.result()
+                if i + 1 < len(batches):   # the next batch's reads run while this one is encoded and written
+                    staged = stage(batches[i + 1], arenas[(i + 1) & 1])
+                if entries:
+                    pipe.quantize(entries)
+                for piece, enc in zip(batch, outputs):
+                    p = piece.plan
+                    out.write(enc if enc is not None else source[p.data_begin:p.data_end])
+                    if piece.last:
+                        out.write(b"\0" * (pad_to(p.nbytes) - p.nbytes))
+    finally:
+        readers.shutdown(wait=True)
+        os.close(fd)
+        for pair in arenas:
+            for arena in pair:
+                arena.close()
+        lib.libgguf_cuda_context_destroy(ctx)
     return result
 
 
