@@ -1057,7 +1057,6 @@ struct OutPack<float> {
             for (int i = 0; i < 8; ++i) dst[i] = v[i];
         }
     }
-    static GGUF_D void store1(float *dst, float v) { *dst = v; }
 };
 
 template <>

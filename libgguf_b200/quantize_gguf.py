@@ -421,6 +421,7 @@ class Options:
     gpus: int = 0                                            # 0 = all visible
     chunk_bytes: int = 128 << 20
     batch_bytes: int = 4 << 30
+    timings: bool = False
 
 
 def qtype_nbytes(shape, name: str) -> int:
@@ -673,16 +674,6 @@ def convert(options: Options) -> dict:
     return result
 
 
-def src_view(source: np.ndarray, p: TensorPlan) -> np.ndarray:
-    """The tensor's source bytes as the rows x n_per_row array the pipeline takes (a view of the mapped file).
-    safetensors aligns tensor data to 8 bytes only by convention; a misaligned tensor is copied."""
-    np_dtype = SOURCE_DTYPES[p.source_dtype][0]
-    raw = source[p.data_begin:p.data_end]
-    if p.data_begin % np.dtype(np_dtype).itemsize:
-        raw = np.array(raw)
-    return raw.view(np_dtype).reshape(p.n_rows, p.n_per_row)
-
-
 def summary_lines(result: dict) -> list[str]:
     lines = [f"Wrote {result['output_path']}", f"Architecture: {result['arch']}", f"File type: {result['file_type']}",
              "Tensor types: " + ", ".join(f"{k}={v}" for k, v in sorted(result["tensor_types"].items()))]
@@ -701,10 +692,31 @@ def parse_args(argv) -> Options:
     ap.add_argument("--tensor-type", action="append", default=[], metavar="PATTERN=TYPE")
     ap.add_argument("--include", action="append", default=[])
     ap.add_argument("--exclude", action="append", default=[])
+    # options of upstream's command that choose how its own CPU / single-GPU loop runs: accepted so that existing command
+    # lines keep working; the ones with an equivalent here are mapped, the rest have nothing to configure
+    ap.add_argument("--imatrix", default="", help="accepted for command line parity; the Q/K quantizers do not use it")
+    ap.add_argument("--scratch-bytes", "--cpu-ram-bytes", dest="scratch_bytes", type=int, default=0, help="ignored (no CPU loop)")
+    ap.add_argument("--threads", type=int, default=0, help="ignored (no CPU loop)")
+    ap.add_argument("--backend", default="auto", choices=["auto", "cuda", "cpu"], help="'cpu' is refused: there is no CPU path")
+    ap.add_argument("--cuda-fallback", default="", help="ignored (every type is supported on the GPU)")
+    ap.add_argument("--verify-cuda-tensors", default="", help="ignored (parity is a test-suite matter here)")
+    ap.add_argument("--verify-cuda-large-tensors", default="", help="ignored")
+    ap.add_argument("--verify-cuda-random-tensors", default="", help="ignored")
+    ap.add_argument("--seed", default="", help="ignored")
+    ap.add_argument("--cuda-vram-bytes", type=int, default=0, help="largest shard in bytes (same as --chunk-mb)")
+    ap.add_argument("--cuda-batch-mb", type=int, default=0, help="largest shard in MiB (same as --chunk-mb)")
+    ap.add_argument("--cuda-pipeline", default="1", help="ignored (always pipelined)")
+    ap.add_argument("--timings", action="store_true", help="print the wall-clock time of the conversion to stderr")
     ap.add_argument("--gpus", type=int, default=0, help="number of GPUs to stream through (default: all)")
     ap.add_argument("--chunk-mb", type=int, default=128, help="largest shard, MiB of source bytes")
     ap.add_argument("--batch-mb", type=int, default=4096, help="host memory held between file writes, MiB")
     a = ap.parse_args(argv)
+    if a.backend == "cpu":
+        fail("CPU backend requested, but this converter encodes on CUDA devices only")
+    if a.cuda_vram_bytes > 0:
+        a.chunk_mb = max(1, a.cuda_vram_bytes >> 20)
+    if a.cuda_batch_mb > 0:
+        a.chunk_mb = a.cuda_batch_mb
     overrides = []
     for item in a.tensor_type:
         pattern, eq, name = item.partition("=")
@@ -712,12 +724,18 @@ def parse_args(argv) -> Options:
             fail("expected PATTERN=QTYPE for --tensor-type")
         overrides.append((pattern, parse_tensor_qtype_name(name)))
     return Options(src=a.src, qtype=a.qtype, dst=a.dst, policy=a.policy, tensor_overrides=overrides, include=a.include,
-                   exclude=a.exclude, overwrite=a.overwrite, gpus=a.gpus, chunk_bytes=a.chunk_mb << 20, batch_bytes=a.batch_mb << 20)
+                   exclude=a.exclude, overwrite=a.overwrite, gpus=a.gpus, chunk_bytes=a.chunk_mb << 20, batch_bytes=a.batch_mb << 20,
+                   timings=a.timings)
 
 
 def main(argv=None) -> int:
+    import time
     try:
-        result = convert(parse_args(sys.argv[1:] if argv is None else argv))
+        options = parse_args(sys.argv[1:] if argv is None else argv)
+        began = time.perf_counter()
+        result = convert(options)
+        if options.timings:
+            print(f"Timings: total={time.perf_counter() - began:.3f}s", file=sys.stderr)
     except ConversionError as exc:
         print(f"error: {exc}", file=sys.stderr)
         return 1

@@ -56,6 +56,11 @@ def test_rejections(tmp_path, checkpoints):
                           (["--qtype", "NVFP4"], "non-Q/K quantization families"), (["--qtype", "Q4_K_L"], "unsupported output file type")]:
         with pytest.raises(qg.ConversionError, match=message):
             qg.plan_file(qg.parse_args(["--src", src, "--dst", str(tmp_path / "x.gguf")] + argv))
+    with pytest.raises(qg.ConversionError, match="CPU backend requested"):
+        qg.parse_args(["--src", src, "--backend", "cpu"])
+    accepted = qg.parse_args(["--src", src, "--imatrix", "x.dat", "--threads", "4", "--scratch-bytes", "1024", "--cuda-batch-mb", "64",
+                              "--cuda-pipeline", "0", "--verify-cuda-tensors", "all", "--seed", "3", "--timings"])
+    assert accepted.chunk_bytes == 64 << 20 and accepted.timings
     with pytest.raises(qg.ConversionError, match="unsupported GGML tensor type"):
         qg.parse_args(["--src", src, "--tensor-type", "*=Q4_K_L"])
     unknown = str(tmp_path / "unknown.safetensors")
