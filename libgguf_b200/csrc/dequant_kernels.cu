@@ -622,6 +622,13 @@ struct Fast<GGML_TYPE_Q3_K> {
         const int hi = (s[8 + (g & 3)] >> (2 * (g >> 2))) & 3;
         return make_float2(half_hw(lds_u16(b + 108)) * (float)((lo | (hi << 4)) - 32), 0.f);
     }
+    // groups g and g + 8 (g < 8) take the two nibbles of one scale byte and two fields of one high-bits byte
+    static GGUF_D void prep_pair(const uint8_t *b, int g, float2 *out) {
+        const uint32_t s = b[96 + g], h = (uint32_t)b[104 + (g & 3)] >> (2 * (g >> 2));
+        const float d = half_hw(lds_u16(b + 108));
+        out[g] = make_float2(d * (float)((int)((s & 0xF) | ((h & 3) << 4)) - 32), 0.f);
+        out[g + 8] = make_float2(d * (float)((int)((s >> 4) | (((h >> 4) & 3) << 4)) - 32), 0.f);
+    }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
         const int n = e0 >> 7, j = (e0 >> 5) & 3, r = e0 & 16;
         const uint4 q = lds16_any(b + 32 + 32 * n + r);
@@ -1169,6 +1176,13 @@ GGUF_D void store16(OutT *dst, const float *v) {
     }
 }
 
+// Decoders that derive the constants of two groups from the same bytes provide prep_pair(block, g, out)
+// for groups g and g + GROUPS_PER_BLOCK / 2.
+template <class D, class = void>
+struct HasPrepPair : std::false_type {};
+template <class D>
+struct HasPrepPair<D, std::void_t<decltype(&D::prep_pair)>> : std::true_type {};
+
 template <int TYPE, class OutT>
 __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                int64_t nblocks) {
@@ -1195,11 +1209,21 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
         if (i < nvec) s16[i] = __ldcs(g16 + i);
     }
     __syncthreads();
+    if constexpr (HasPrepPair<D>::value) {
+        constexpr int PAIRS = GROUPS_PER_BLOCK / 2;
 #pragma unroll
-    for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
-        const int g = k * kThreads + tid;
-        const int blk = g / GROUPS_PER_BLOCK;
-        if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
+        for (int k = 0; k < (TILE_GROUPS / 2 + kThreads - 1) / kThreads; ++k) {
+            const int p = k * kThreads + tid;
+            const int blk = p / PAIRS;
+            if (blk < nb) D::prep_pair(tile + blk * D::BYTES, p % PAIRS, consts + blk * GROUPS_PER_BLOCK);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
+            const int g = k * kThreads + tid;
+            const int blk = g / GROUPS_PER_BLOCK;
+            if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
+        }
     }
     __syncthreads();
     // call c = u*kThreads + tid: position inside the block (e0) does not depend on u

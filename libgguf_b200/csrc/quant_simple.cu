@@ -631,77 +631,161 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
 }
 
 // lroundf(x * id) + 1.  With a finite id the product lies in [-1, 1] (or is NaN, which upstream's
-// conversion turns into digit 1) and rounding half away from zero is two comparisons; the library
-// call is kept for blocks whose scale is so small that 1 / d overflows.
-template <bool FINITE>
-GGUF_D int trit(float x, float id) {
+// conversion turns into digit 1) and rounding half away from zero is two comparisons.  When the
+// scale is so small that 1 / d overflows (or d is NaN) every product is an infinity or NaN, which
+// x86's conversion turns into the integer indefinite value 0x8000...0: digit 1 after the increment.
+GGUF_D uint32_t trit(float x, float id) {
     const float v = x * id;
-    if (FINITE) return 1 + (v >= 0.5f ? 1 : 0) - (v <= -0.5f ? 1 : 0);
-    return (int)lroundf(v) + 1;
+    return 1u + (v >= 0.5f ? 1u : 0u) - (v <= -0.5f ? 1u : 0u);
 }
+// five base-3 digits (most significant first) -> TQ1_0's byte: ceil(q * 256 / 243)
+GGUF_D uint32_t tq1_byte(uint32_t q) { return (q * 256u + 242u) / 243u; }
 
-template <bool TQ1, bool FINITE>
-GGUF_D void ternary_pack(const float *xb, uint8_t *out, int lane, float d, float id) {
-    if constexpr (TQ1) {
-        {   // 32 bytes, 5 trits each, elements n*32 + lane
-            int q = 0;
-#pragma unroll
-            for (int n = 0; n < 5; ++n) q = (q * 3 + trit<FINITE>(xb[n * 32 + lane], id)) & 0xFF;
-            out[lane] = (uint8_t)((q * 256 + 242) / 243);
-        }
-        if (lane < 16) {  // 16 bytes, elements 160 + n*16 + lane
-            int q = 0;
-#pragma unroll
-            for (int n = 0; n < 5; ++n) q = (q * 3 + trit<FINITE>(xb[160 + n * 16 + lane], id)) & 0xFF;
-            out[32 + lane] = (uint8_t)((q * 256 + 242) / 243);
-        }
-        if (lane < 4) {  // 4 bytes, 4 trits each, elements 240 + m*4 + lane, then one more *3
-            int q = 0;
-#pragma unroll
-            for (int m = 0; m < 4; ++m) q = (q * 3 + trit<FINITE>(xb[240 + m * 4 + lane], id)) & 0xFF;
-            q = (q * 3) & 0xFF;
-            out[48 + lane] = (uint8_t)((q * 256 + 242) / 243);
-        }
-        if (lane == 0) st16(out + 52, f32_to_half_bits(d));
-    } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            int q = 0;
-#pragma unroll
-            for (int n = 0; n < 4; ++n) q += (trit<FINITE>(xb[j * 128 + n * 32 + lane], id) & 3) << (2 * n);
-            out[j * 32 + lane] = (uint8_t)q;
-        }
-        if (lane == 0) st16(out + 64, f32_to_half_bits(d));
-    }
-}
+constexpr int kTernThreads = 128;               // eight lanes per block
+constexpr int kTernBlocks = kTernThreads / 8;   // blocks per tile
 
 // TQ1_0 / TQ2_0: 256-element blocks, d = max |x| (upstream tq1_0.cpp:16-98, tq2_0.cpp:16-53).
-// One warp per block; the block is staged in shared memory because each output byte mixes
-// elements 32 (or 16, or 4) apart.
+// Persistent CTAs walk tiles of sixteen blocks with a stride of the grid size and stage tile i+1 by 16-byte
+// asynchronous copies while tile i is encoded.  Eight lanes share a block: every output byte mixes elements 32
+// (or 16, or 4) apart, and lane L takes the elements of bytes 4L..4L+3 of each 32-byte group (TQ1_0: also bytes
+// 32+2L, 33+2L and, for L < 4, byte 48+L) straight from the staged block, 30 to 34 elements in registers.  The
+// encoded tile leaves as 16-byte vectors.
 template <bool TQ1>
-__global__ void __launch_bounds__(kThreads) quant_ternary_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
-                                                                int64_t nblocks) {
+__global__ void __launch_bounds__(kTernThreads) quant_ternary_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
+                                                                    int64_t nblocks) {
     constexpr int BYTES = TQ1 ? 54 : 66;
-    __shared__ float xs[kThreads / 32][256];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t blk = (int64_t)blockIdx.x * (kThreads / 32) + warp;
-    if (blk >= nblocks) return;
-    const float *x = src + blk * 256;
-    uint8_t *out = dst + blk * BYTES;
-    float amax = 0.0f;
+    __shared__ __align__(16) float xs[2][kTernBlocks * 256];
+    __shared__ __align__(16) uint8_t stage[kTernBlocks * BYTES + 16];
+    const int group = threadIdx.x >> 3, L = threadIdx.x & 7;
+    const int64_t ntiles = (nblocks + kTernBlocks - 1) / kTernBlocks;
+    uint8_t *tile = stage + (reinterpret_cast<uintptr_t>(dst) & 15);  // a tile starts a multiple of 16 bytes into dst
+
+    auto prefetch = [&](int64_t t, float *xin) {
+        const int64_t left = nblocks - t * kTernBlocks;
+        const int nvec = (int)(left < kTernBlocks ? left : kTernBlocks) * 64;
+        const float4 *g4 = reinterpret_cast<const float4 *>(src + t * kTernBlocks * 256);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const float v = x[k * 32 + lane];
-        xs[warp][k * 32 + lane] = v;
-        amax = fmaxf(amax, fabsf(v));
+        for (int k = 0; k < kTernBlocks * 64 / kTernThreads; ++k) {
+            const int i = k * kTernThreads + threadIdx.x;
+            if (i < nvec) cp_async16(xin + 4 * i, g4 + i);
+        }
+        cp_async_commit();
+    };
+
+    int64_t t = blockIdx.x;
+    grid_dependents_may_launch();
+    grid_dependency_wait();
+    if (t < ntiles) prefetch(t, xs[0]);
+    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
+        const int64_t tnext = t + gridDim.x;
+        if (tnext < ntiles) {
+            prefetch(tnext, xs[(it + 1) & 1]);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();  // tile t has landed; every thread is done with the previous tile's stage
+        const int64_t first = t * kTernBlocks;
+        const float *xb = xs[it & 1] + group * 256;
+        // Groups past the end of a short last tile run on stale data (all lanes take part in the shuffles) and store nothing.
+        const bool live = first + group < nblocks;
+        constexpr int N = TQ1 ? 36 : 32;
+        float x[N];
+        if constexpr (TQ1) {
+#pragma unroll
+            for (int n = 0; n < 5; ++n) {
+                const float4 v = *reinterpret_cast<const float4 *>(xb + n * 32 + 4 * L);
+                x[4 * n] = v.x; x[4 * n + 1] = v.y; x[4 * n + 2] = v.z; x[4 * n + 3] = v.w;
+                const float2 w = *reinterpret_cast<const float2 *>(xb + 160 + n * 16 + 2 * L);
+                x[20 + 2 * n] = w.x; x[21 + 2 * n] = w.y;
+            }
+#pragma unroll
+            for (int n = 0; n < 4; ++n) x[30 + n] = L < 4 ? xb[240 + n * 4 + L] : 0.f;
+            x[34] = x[35] = 0.f;
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {  // k = 4 * group-of-128 + n
+                const float4 v = *reinterpret_cast<const float4 *>(xb + k * 32 + 4 * L);
+                x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+            }
+        }
+        float amax = amax_nan<N>(x);
+#pragma unroll
+        for (int m = 4; m > 0; m >>= 1) {
+            const float other = __shfl_xor_sync(kFull, amax, m);
+            amax = amax3_nan(amax, other, other);
+        }
+        if (amax != amax) {
+            // upstream's MAX(a, b) = a > b ? a : b forgets the running maximum at a NaN: redo its loop in element order
+            float a = 0.f;
+            for (int i = 0; i < 256; ++i) {
+                const float m = fabsf(xb[i]);
+                a = a > m ? a : m;
+            }
+            amax = a;
+        }
+        const float d = amax;
+        const float id = d ? 1.0f / d : 0.0f;
+        const bool finite = id < kInfinity;   // otherwise every digit is 1
+        uint8_t *out = tile + group * BYTES;
+        if (live) {
+            if constexpr (TQ1) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t q = 0;
+#pragma unroll
+                    for (int n = 0; n < 5; ++n) q = q * 3u + trit(x[4 * n + c], id);
+                    out[4 * L + c] = (uint8_t)tq1_byte(finite ? q : 121u);
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t q = 0;
+#pragma unroll
+                    for (int n = 0; n < 5; ++n) q = q * 3u + trit(x[20 + 2 * n + c], id);
+                    out[32 + 2 * L + c] = (uint8_t)tq1_byte(finite ? q : 121u);
+                }
+                if (L < 4) {
+                    uint32_t q = 0;
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) q = q * 3u + trit(x[30 + n], id);
+                    out[48 + L] = (uint8_t)tq1_byte(finite ? q * 3u : 120u);
+                }
+                if (L == 0) st16(out + 52, f32_to_half_bits(d));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t q = 0;
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) q |= trit(x[4 * (4 * j + n) + c], id) << (2 * n);
+                        out[32 * j + 4 * L + c] = (uint8_t)(finite ? q : 0x55u);
+                    }
+                }
+                if (L == 0) st16(out + 64, f32_to_half_bits(d));
+            }
+        }
+        __syncthreads();
+        const int64_t left = nblocks - first;
+        flush_tile(tile, dst + first * BYTES, (int)(left < kTernBlocks ? left : kTernBlocks) * BYTES, threadIdx.x, kTernThreads);
     }
-#pragma unroll
-    for (int m = 16; m > 0; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(kFull, amax, m));
-    __syncwarp();
-    const float d = amax;
-    const float id = d ? 1.0f / d : 0.0f;
-    if (id < kInfinity) ternary_pack<TQ1, true>(xs[warp], out, lane, d, id);
-    else ternary_pack<TQ1, false>(xs[warp], out, lane, d, id);
+}
+
+template <bool TQ1>
+cudaError_t launch_ternary(const float *src, uint8_t *dst, int64_t nblocks, cudaStream_t stream) {
+    const int64_t ntiles = (nblocks + kTernBlocks - 1) / kTernBlocks;
+    if (ntiles <= 0) return cudaSuccess;
+    static const int resident = [] {
+        int dev = 0, sms = 148, per_sm = 6;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_ternary_kernel<TQ1>, kTernThreads, 0);
+        return sms * (per_sm > 0 ? per_sm : 1);
+    }();
+    const int64_t grid = ntiles < resident ? ntiles : resident;
+    const cudaError_t launched = launch_overlapped(quant_ternary_kernel<TQ1>, (unsigned)grid, kTernThreads, stream, src, dst, nblocks);
+    count_launch();
+    return launched != cudaSuccess ? launched : cudaGetLastError();
 }
 
 // Plain storage types: fp32 copy, fp16 and bf16 conversion with upstream's rounding and NaN
@@ -773,16 +857,8 @@ cudaError_t launch_quantize_simple(int type, const float *src, void *dst, int64_
         case GGML_TYPE_MXFP4: return launch32<Simple::MXFP4>(src, dst, nelems, mx_steps, stream);
         case GGML_TYPE_NVFP4: return launch32<Simple::NVFP4>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_Q1_0: return launch32<Simple::Q1_0>(src, dst, nelems, nullptr, stream);
-        case GGML_TYPE_TQ1_0:
-        case GGML_TYPE_TQ2_0: {
-            const int64_t nblocks = nelems / 256;
-            if (nblocks <= 0) return cudaSuccess;
-            const unsigned grid = (unsigned)((nblocks + 7) / 8);
-            if (type == GGML_TYPE_TQ1_0) quant_ternary_kernel<true><<<grid, kThreads, 0, stream>>>(src, out, nblocks);
-            else quant_ternary_kernel<false><<<grid, kThreads, 0, stream>>>(src, out, nblocks);
-            count_launch();
-            return cudaGetLastError();
-        }
+        case GGML_TYPE_TQ1_0: return launch_ternary<true>(src, out, nelems / 256, stream);
+        case GGML_TYPE_TQ2_0: return launch_ternary<false>(src, out, nelems / 256, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -221,8 +221,8 @@ def _edge_rows(width=256):
     return np.ascontiguousarray(np.stack(rows)), finite
 
 
-@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "MXFP4", "NVFP4"])
-def test_edge_blocks_of_the_32_element_types(gguf, checker, name):
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "MXFP4", "NVFP4", "TQ1_0", "TQ2_0"])
+def test_edge_blocks_of_the_simple_types(gguf, checker, name):
     qtype = inputs.QTYPES[name]
     x, finite = _edge_rows()
     got, want = gguf.quantize_rows(x, qtype), checker.quantize_rows(x, qtype)
