@@ -845,6 +845,84 @@ constexpr uint32_t kIq3sLevels0 = 1u | (3u << 8) | (5u << 16) | (7u << 24);     
 constexpr uint32_t kIq3sLevels1 = 9u | (11u << 8) | (13u << 16) | (15u << 24);
 constexpr uint32_t kIq1Levels = 0u | (1u << 8) | (2u << 16);                         // grid value + 1
 
+// ---- signed codebook types: selector tables --------------------------------------------------
+// For the IQ2 and IQ3 families the packed codebook entry is kept already widened to permute selectors
+// (one nibble per coordinate), and the element's sign goes into bit 2 of its nibble (IQ2: the permute
+// then reads the level from a table of +levels and -levels) or into a second permute that picks
+// between the +level and the -level (IQ3).  The levels are stored with an offset of 128, removed
+// together with the 2^23 of the byte-to-float step.  The tables are copied to shared memory by every
+// CTA: a gather over a 1-4 KB table costs a few bank conflicts there, one L1 wavefront per touched
+// line in global memory.
+namespace selectors {
+#define GGUF_CODEBOOK(name, count, ...) constexpr uint16_t packed_##name[count] = {__VA_ARGS__};
+#include "gguf_codebooks.inc"
+#undef GGUF_CODEBOOK
+template <class T, int N>
+struct Table { T v[N]; };
+constexpr uint32_t widen2(uint32_t c) {
+    c = (c | (c << 8)) & 0x00FF00FFu;
+    c = (c | (c << 4)) & 0x0F0F0F0Fu;
+    return (c | (c << 2)) & 0x33333333u;
+}
+constexpr uint32_t widen3(uint32_t c) {
+    c = (c & 0x03Fu) | ((c << 2) & 0x3F00u);
+    return (c & 0x0707u) | ((c << 1) & 0x7070u);
+}
+template <int N>
+constexpr Table<uint32_t, N> make2(const uint16_t (&packed)[N]) {
+    Table<uint32_t, N> t{};
+    for (int i = 0; i < N; ++i) t.v[i] = widen2(packed[i]);
+    return t;
+}
+template <int N>
+constexpr Table<uint16_t, N> make3(const uint16_t (&packed)[N]) {
+    Table<uint16_t, N> t{};
+    for (int i = 0; i < N; ++i) t.v[i] = (uint16_t)widen3(packed[i]);
+    return t;
+}
+}  // namespace selectors
+static __device__ __align__(16) const selectors::Table<uint32_t, 256> k_sel_IQ2XXS = selectors::make2(selectors::packed_IQ2XXS);
+static __device__ __align__(16) const selectors::Table<uint32_t, 512> k_sel_IQ2XS = selectors::make2(selectors::packed_IQ2XS);
+static __device__ __align__(16) const selectors::Table<uint32_t, 1024> k_sel_IQ2S = selectors::make2(selectors::packed_IQ2S);
+static __device__ __align__(16) const selectors::Table<uint16_t, 256> k_sel_IQ3XXS = selectors::make3(selectors::packed_IQ3XXS);
+static __device__ __align__(16) const selectors::Table<uint16_t, 512> k_sel_IQ3S = selectors::make3(selectors::packed_IQ3S);
+
+constexpr uint32_t biased_levels(int a, int b, int c, int d) {
+    return (uint32_t)(128 + a) | ((uint32_t)(128 + b) << 8) | ((uint32_t)(128 + c) << 16) | ((uint32_t)(128 + d) << 24);
+}
+constexpr uint32_t kIq2Plus = biased_levels(8, 25, 43, 0), kIq2Minus = biased_levels(-8, -25, -43, 0);
+constexpr uint32_t kIq3xxsPlus0 = biased_levels(4, 12, 20, 28), kIq3xxsPlus1 = biased_levels(36, 44, 52, 62);
+constexpr uint32_t kIq3xxsMinus0 = biased_levels(-4, -12, -20, -28), kIq3xxsMinus1 = biased_levels(-36, -44, -52, -62);
+constexpr uint32_t kIq3sPlus0 = biased_levels(1, 3, 5, 7), kIq3sPlus1 = biased_levels(9, 11, 13, 15);
+constexpr uint32_t kIq3sMinus0 = biased_levels(-1, -3, -5, -7), kIq3sMinus1 = biased_levels(-9, -11, -13, -15);
+
+// bit j of s (8 bits) -> bit 2 of nibble j.  Each multiplication is a shift-and-or: the copies do not overlap.
+GGUF_D uint32_t sign_nibbles(uint32_t s) {
+    uint32_t x = (s * 0x1001u) & 0x000F000Fu;
+    x = (x * 0x41u) & 0x03030303u;
+    return (x * 0x24u) & 0x44444444u;
+}
+// v[0..3] = scale * (byte_k(levels) - 128)
+GGUF_D void emit4_biased(uint32_t levels, float scale, float *v) {
+    const float2 nb = make_float2(-(kTwo23 + 128.f), -(kTwo23 + 128.f)), sc = make_float2(scale, scale);
+    const float2 a = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_byte(levels, 0), magic_byte(levels, 1)), nb));
+    const float2 b = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_byte(levels, 2), magic_byte(levels, 3)), nb));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+// Eight values of a 2-bit grid point: sel = the entry's selectors, signs = one bit per element.
+GGUF_D void emit_signed2(uint32_t sel, uint32_t signs, float scale, float *v) {
+    sel |= sign_nibbles(signs);
+    emit4_biased(__byte_perm(kIq2Plus, kIq2Minus, sel), scale, v);
+    emit4_biased(__byte_perm(kIq2Plus, kIq2Minus, sel >> 16), scale, v + 4);
+}
+// Eight values of two 3-bit grid points (four each).
+GGUF_D void emit_signed3(uint32_t sel_a, uint32_t sel_b, uint32_t signs, uint32_t p0, uint32_t p1, uint32_t m0, uint32_t m1,
+                         float scale, float *v) {
+    const uint32_t pick = sign_nibbles(signs);
+    emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_a), __byte_perm(m0, m1, sel_a), pick | 0x3210u), scale, v);
+    emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_b), __byte_perm(m0, m1, sel_b), (pick >> 16) | 0x3210u), scale, v + 4);
+}
+
 template <>
 struct Fast<GGML_TYPE_IQ2_XXS> {
     static constexpr bool kEnabled = true;
@@ -853,15 +931,17 @@ struct Fast<GGML_TYPE_IQ2_XXS> {
         const uint32_t aux1 = lds_u32_a2(b + 2 + 8 * ib32 + 4);
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)(aux1 >> 28)) * 0.25f, 0.f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_sel_IQ2XXS);
+    static GGUF_D const void *table() { return k_sel_IQ2XXS.v; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
         const uint8_t *q = b + 2 + 8 * (e0 >> 5);
         const uint32_t aux1 = lds_u32_a2(q + 4);
         const int l = (e0 >> 3) & 3;  // 0 or 2
         const uint32_t pair = lds_u16(q + l);
 #pragma unroll
         for (int k = 0; k < 2; ++k)
-            emit_grid2(__ldg(&k_codebook_IQ2XXS[(pair >> (8 * k)) & 0xFFu]), kIq2Levels,
-                       iq_signs_from_index((aux1 >> (7 * (l + k))) & 127), c.x, 0.f, v + 8 * k);
+            emit_signed2(sel[(pair >> (8 * k)) & 0xFFu], iq_signs_from_index((aux1 >> (7 * (l + k))) & 127), c.x, v + 8 * k);
     }
 };
 
@@ -873,11 +953,14 @@ struct Fast<GGML_TYPE_IQ2_XS> {
         const int sc = b[66 + (g16 >> 1)];
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)((g16 & 1) ? (sc >> 4) : (sc & 0xF))) * 0.25f, 0.f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_sel_IQ2XS);
+    static GGUF_D const void *table() { return k_sel_IQ2XS.v; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const uint32_t q = lds_u16(b + 2 + 2 * ((e0 >> 3) + k));
-            emit_grid2(__ldg(&k_codebook_IQ2XS[q & 511u]), kIq2Levels, iq_signs_from_index(q >> 9), c.x, 0.f, v + 8 * k);
+            emit_signed2(sel[q & 511u], iq_signs_from_index(q >> 9), c.x, v + 8 * k);
         }
     }
 };
@@ -890,7 +973,10 @@ struct Fast<GGML_TYPE_IQ2_S> {
         const int sc = b[74 + (g16 >> 1)];
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)((g16 & 1) ? (sc >> 4) : (sc & 0xF))) * 0.25f, 0.f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_sel_IQ2S);
+    static GGUF_D const void *table() { return k_sel_IQ2S.v; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
         const int g = e0 >> 3, ib32 = g >> 2;
         const uint32_t qh = b[66 + ib32];
         const uint32_t low = lds_u16(b + 2 + g), signs = lds_u16(b + 2 + 32 + g);  // g is even
@@ -898,7 +984,7 @@ struct Fast<GGML_TYPE_IQ2_S> {
         for (int k = 0; k < 2; ++k) {
             const int l = (g & 3) + k;
             const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 0x300u);
-            emit_grid2(__ldg(&k_codebook_IQ2S[idx]), kIq2Levels, (signs >> (8 * k)) & 0xFFu, c.x, 0.f, v + 8 * k);
+            emit_signed2(sel[idx], (signs >> (8 * k)) & 0xFFu, c.x, v + 8 * k);
         }
     }
 };
@@ -911,15 +997,18 @@ struct Fast<GGML_TYPE_IQ3_XXS> {
         const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)(aux >> 28)) * 0.5f, 0.f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_sel_IQ3XXS);
+    static GGUF_D const void *table() { return k_sel_IQ3XXS.v; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint16_t *sel = static_cast<const uint16_t *>(tab);
         const int g = e0 >> 3, ib32 = g >> 2;  // g even: grid points 2g .. 2g+3
         const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
         const uint32_t idx = lds_u32_a2(b + 2 + 2 * g);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const uint32_t signs = iq_signs_from_index((aux >> (7 * ((g & 3) + k))) & 127);
-            emit_grid3(__ldg(&k_codebook_IQ3XXS[(idx >> (16 * k)) & 0xFFu]), kIq3xxsLevels0, kIq3xxsLevels1, signs, c.x, v + 8 * k);
-            emit_grid3(__ldg(&k_codebook_IQ3XXS[(idx >> (16 * k + 8)) & 0xFFu]), kIq3xxsLevels0, kIq3xxsLevels1, signs >> 4, c.x, v + 8 * k + 4);
+            emit_signed3(sel[(idx >> (16 * k)) & 0xFFu], sel[(idx >> (16 * k + 8)) & 0xFFu], signs, kIq3xxsPlus0, kIq3xxsPlus1,
+                         kIq3xxsMinus0, kIq3xxsMinus1, c.x, v + 8 * k);
         }
     }
 };
@@ -932,7 +1021,10 @@ struct Fast<GGML_TYPE_IQ3_S> {
         const int sc = b[106 + (ib32 >> 1)];
         return make_float2(half_hw(lds_u16(b)) * (float)(1 + 2 * ((ib32 & 1) ? (sc >> 4) : (sc & 0xF))), 0.f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_sel_IQ3S);
+    static GGUF_D const void *table() { return k_sel_IQ3S.v; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint16_t *sel = static_cast<const uint16_t *>(tab);
         const int g = e0 >> 3, ib32 = g >> 2;
         const uint32_t qh = b[66 + ib32];
         const uint32_t idx = lds_u32_a2(b + 2 + 2 * g), sg = lds_u16(b + 74 + g);
@@ -941,9 +1033,7 @@ struct Fast<GGML_TYPE_IQ3_S> {
             const int l = (g & 3) + k;
             const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
             const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
-            const uint32_t signs = (sg >> (8 * k)) & 0xFFu;
-            emit_grid3(__ldg(&k_codebook_IQ3S[i1]), kIq3sLevels0, kIq3sLevels1, signs, c.x, v + 8 * k);
-            emit_grid3(__ldg(&k_codebook_IQ3S[i2]), kIq3sLevels0, kIq3sLevels1, signs >> 4, c.x, v + 8 * k + 4);
+            emit_signed3(sel[i1], sel[i2], (sg >> (8 * k)) & 0xFFu, kIq3sPlus0, kIq3sPlus1, kIq3sMinus0, kIq3sMinus1, c.x, v + 8 * k);
         }
     }
 };
@@ -1183,6 +1273,13 @@ struct HasPrepPair : std::false_type {};
 template <class D>
 struct HasPrepPair<D, std::void_t<decltype(&D::prep_pair)>> : std::true_type {};
 
+// Decoders that look codebook entries up provide kTableBytes / table(): the kernel copies the table to
+// shared memory and hands it to run() as a fifth argument.
+template <class D, class = void>
+struct TableBytes { static constexpr int value = 0; };
+template <class D>
+struct TableBytes<D, std::void_t<decltype(D::kTableBytes)>> { static constexpr int value = D::kTableBytes; };
+
 template <int TYPE, class OutT>
 __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                int64_t nblocks) {
@@ -1201,7 +1298,18 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
     const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
     const int nvec = (nb * D::BYTES + 15) >> 4;
     uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+    constexpr int TABLE_BYTES = TableBytes<D>::value;
+    static_assert(TABLE_BYTES % 16 == 0, "the table moves as 16-byte vectors");
+    __shared__ __align__(16) uint8_t table[TABLE_BYTES ? TABLE_BYTES : 16];
     grid_dependents_may_launch();
+    if constexpr (TABLE_BYTES > 0) {  // constant data: does not wait for the previous kernel
+        const uint4 *g = static_cast<const uint4 *>(D::table());
+#pragma unroll
+        for (int k = 0; k < (TABLE_BYTES / 16 + kThreads - 1) / kThreads; ++k) {
+            const int i = k * kThreads + tid;
+            if (i < TABLE_BYTES / 16) reinterpret_cast<uint4 *>(table)[i] = __ldg(g + i);
+        }
+    }
     grid_dependency_wait();
 #pragma unroll
     for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
@@ -1241,7 +1349,8 @@ __global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *_
         constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
         if (blk0 + u * BLOCK_STEP < nb) {
             float v[CALL];
-            D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
+            if constexpr (TABLE_BYTES > 0) D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v, table);
+            else D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
 #pragma unroll
             for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
         }
