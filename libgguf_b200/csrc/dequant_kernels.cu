@@ -880,12 +880,47 @@ constexpr Table<uint16_t, N> make3(const uint16_t (&packed)[N]) {
     for (int i = 0; i < N; ++i) t.v[i] = (uint16_t)widen3(packed[i]);
     return t;
 }
+// bit j of s (8 bits) -> bit 2 of nibble j
+constexpr uint32_t sign_nibbles(uint32_t s) {
+    uint32_t x = (s | (s << 12)) & 0x000F000Fu;
+    x = (x | (x << 6)) & 0x03030303u;
+    return ((x << 2) | (x << 5)) & 0x44444444u;
+}
+// The sign patterns, ready for use: N = 128 for the formats that store a 7-bit index (the eighth sign makes the
+// parity even, upstream libgguf_tables.cpp ksigns_iq2xs), 256 for those that store the byte.  PICK = false: the
+// bits to OR into a 2-bit entry's selectors; PICK = true: per half, the selector that picks byte k from the
+// +levels (k) or the -levels (4 + k).
+template <int N, bool PICK>
+constexpr Table<uint32_t, N> make_signs() {
+    Table<uint32_t, N> t{};
+    for (uint32_t i = 0; i < (uint32_t)N; ++i) {
+        uint32_t s = i;
+        if (N == 128) {
+            uint32_t parity = 0;
+            for (int k = 0; k < 7; ++k) parity ^= (i >> k) & 1u;
+            s |= parity << 7;
+        }
+        const uint32_t x = sign_nibbles(s);
+        t.v[i] = PICK ? (((x & 0xFFFFu) | 0x3210u) | (((x >> 16) | 0x3210u) << 16)) : x;
+    }
+    return t;
+}
+template <class E, int NE, int NS>
+struct Tables {
+    Table<E, NE> entry;
+    Table<uint32_t, NS> signs;
+};
 }  // namespace selectors
-static __device__ __align__(16) const selectors::Table<uint32_t, 256> k_sel_IQ2XXS = selectors::make2(selectors::packed_IQ2XXS);
-static __device__ __align__(16) const selectors::Table<uint32_t, 512> k_sel_IQ2XS = selectors::make2(selectors::packed_IQ2XS);
-static __device__ __align__(16) const selectors::Table<uint32_t, 1024> k_sel_IQ2S = selectors::make2(selectors::packed_IQ2S);
-static __device__ __align__(16) const selectors::Table<uint16_t, 256> k_sel_IQ3XXS = selectors::make3(selectors::packed_IQ3XXS);
-static __device__ __align__(16) const selectors::Table<uint16_t, 512> k_sel_IQ3S = selectors::make3(selectors::packed_IQ3S);
+static __device__ __align__(16) const selectors::Tables<uint32_t, 256, 128> k_tab_IQ2XXS = {
+    selectors::make2(selectors::packed_IQ2XXS), selectors::make_signs<128, false>()};
+static __device__ __align__(16) const selectors::Tables<uint32_t, 512, 128> k_tab_IQ2XS = {
+    selectors::make2(selectors::packed_IQ2XS), selectors::make_signs<128, false>()};
+static __device__ __align__(16) const selectors::Tables<uint32_t, 1024, 256> k_tab_IQ2S = {
+    selectors::make2(selectors::packed_IQ2S), selectors::make_signs<256, false>()};
+static __device__ __align__(16) const selectors::Tables<uint16_t, 256, 128> k_tab_IQ3XXS = {
+    selectors::make3(selectors::packed_IQ3XXS), selectors::make_signs<128, true>()};
+static __device__ __align__(16) const selectors::Tables<uint16_t, 512, 256> k_tab_IQ3S = {
+    selectors::make3(selectors::packed_IQ3S), selectors::make_signs<256, true>()};
 
 constexpr uint32_t biased_levels(int a, int b, int c, int d) {
     return (uint32_t)(128 + a) | ((uint32_t)(128 + b) << 8) | ((uint32_t)(128 + c) << 16) | ((uint32_t)(128 + d) << 24);
@@ -896,12 +931,6 @@ constexpr uint32_t kIq3xxsMinus0 = biased_levels(-4, -12, -20, -28), kIq3xxsMinu
 constexpr uint32_t kIq3sPlus0 = biased_levels(1, 3, 5, 7), kIq3sPlus1 = biased_levels(9, 11, 13, 15);
 constexpr uint32_t kIq3sMinus0 = biased_levels(-1, -3, -5, -7), kIq3sMinus1 = biased_levels(-9, -11, -13, -15);
 
-// bit j of s (8 bits) -> bit 2 of nibble j.  Each multiplication is a shift-and-or: the copies do not overlap.
-GGUF_D uint32_t sign_nibbles(uint32_t s) {
-    uint32_t x = (s * 0x1001u) & 0x000F000Fu;
-    x = (x * 0x41u) & 0x03030303u;
-    return (x * 0x24u) & 0x44444444u;
-}
 // v[0..3] = scale * (byte_k(levels) - 128)
 GGUF_D void emit4_biased(uint32_t levels, float scale, float *v) {
     const float2 nb = make_float2(-(kTwo23 + 128.f), -(kTwo23 + 128.f)), sc = make_float2(scale, scale);
@@ -909,18 +938,17 @@ GGUF_D void emit4_biased(uint32_t levels, float scale, float *v) {
     const float2 b = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_byte(levels, 2), magic_byte(levels, 3)), nb));
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
-// Eight values of a 2-bit grid point: sel = the entry's selectors, signs = one bit per element.
+// Eight values of a 2-bit grid point: sel = the entry's selectors, signs = the sign table's entry.
 GGUF_D void emit_signed2(uint32_t sel, uint32_t signs, float scale, float *v) {
-    sel |= sign_nibbles(signs);
+    sel |= signs;
     emit4_biased(__byte_perm(kIq2Plus, kIq2Minus, sel), scale, v);
     emit4_biased(__byte_perm(kIq2Plus, kIq2Minus, sel >> 16), scale, v + 4);
 }
-// Eight values of two 3-bit grid points (four each).
-GGUF_D void emit_signed3(uint32_t sel_a, uint32_t sel_b, uint32_t signs, uint32_t p0, uint32_t p1, uint32_t m0, uint32_t m1,
+// Eight values of two 3-bit grid points (four each); pick = the sign table's entry.
+GGUF_D void emit_signed3(uint32_t sel_a, uint32_t sel_b, uint32_t pick, uint32_t p0, uint32_t p1, uint32_t m0, uint32_t m1,
                          float scale, float *v) {
-    const uint32_t pick = sign_nibbles(signs);
-    emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_a), __byte_perm(m0, m1, sel_a), pick | 0x3210u), scale, v);
-    emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_b), __byte_perm(m0, m1, sel_b), (pick >> 16) | 0x3210u), scale, v + 4);
+    emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_a), __byte_perm(m0, m1, sel_a), pick), scale, v);
+    emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_b), __byte_perm(m0, m1, sel_b), pick >> 16), scale, v + 4);
 }
 
 template <>
@@ -931,17 +959,17 @@ struct Fast<GGML_TYPE_IQ2_XXS> {
         const uint32_t aux1 = lds_u32_a2(b + 2 + 8 * ib32 + 4);
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)(aux1 >> 28)) * 0.25f, 0.f);
     }
-    static constexpr int kTableBytes = sizeof(k_sel_IQ2XXS);
-    static GGUF_D const void *table() { return k_sel_IQ2XXS.v; }
+    static constexpr int kTableBytes = sizeof(k_tab_IQ2XXS);
+    static GGUF_D const void *table() { return &k_tab_IQ2XXS; }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
-        const uint32_t *sel = static_cast<const uint32_t *>(tab);
+        const auto *t = static_cast<const decltype(k_tab_IQ2XXS) *>(tab);
         const uint8_t *q = b + 2 + 8 * (e0 >> 5);
         const uint32_t aux1 = lds_u32_a2(q + 4);
         const int l = (e0 >> 3) & 3;  // 0 or 2
         const uint32_t pair = lds_u16(q + l);
 #pragma unroll
         for (int k = 0; k < 2; ++k)
-            emit_signed2(sel[(pair >> (8 * k)) & 0xFFu], iq_signs_from_index((aux1 >> (7 * (l + k))) & 127), c.x, v + 8 * k);
+            emit_signed2(t->entry.v[(pair >> (8 * k)) & 0xFFu], t->signs.v[(aux1 >> (7 * (l + k))) & 127], c.x, v + 8 * k);
     }
 };
 
@@ -953,14 +981,14 @@ struct Fast<GGML_TYPE_IQ2_XS> {
         const int sc = b[66 + (g16 >> 1)];
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)((g16 & 1) ? (sc >> 4) : (sc & 0xF))) * 0.25f, 0.f);
     }
-    static constexpr int kTableBytes = sizeof(k_sel_IQ2XS);
-    static GGUF_D const void *table() { return k_sel_IQ2XS.v; }
+    static constexpr int kTableBytes = sizeof(k_tab_IQ2XS);
+    static GGUF_D const void *table() { return &k_tab_IQ2XS; }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
-        const uint32_t *sel = static_cast<const uint32_t *>(tab);
+        const auto *t = static_cast<const decltype(k_tab_IQ2XS) *>(tab);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const uint32_t q = lds_u16(b + 2 + 2 * ((e0 >> 3) + k));
-            emit_signed2(sel[q & 511u], iq_signs_from_index(q >> 9), c.x, v + 8 * k);
+            emit_signed2(t->entry.v[q & 511u], t->signs.v[q >> 9], c.x, v + 8 * k);
         }
     }
 };
@@ -973,10 +1001,10 @@ struct Fast<GGML_TYPE_IQ2_S> {
         const int sc = b[74 + (g16 >> 1)];
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)((g16 & 1) ? (sc >> 4) : (sc & 0xF))) * 0.25f, 0.f);
     }
-    static constexpr int kTableBytes = sizeof(k_sel_IQ2S);
-    static GGUF_D const void *table() { return k_sel_IQ2S.v; }
+    static constexpr int kTableBytes = sizeof(k_tab_IQ2S);
+    static GGUF_D const void *table() { return &k_tab_IQ2S; }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
-        const uint32_t *sel = static_cast<const uint32_t *>(tab);
+        const auto *t = static_cast<const decltype(k_tab_IQ2S) *>(tab);
         const int g = e0 >> 3, ib32 = g >> 2;
         const uint32_t qh = b[66 + ib32];
         const uint32_t low = lds_u16(b + 2 + g), signs = lds_u16(b + 2 + 32 + g);  // g is even
@@ -984,7 +1012,7 @@ struct Fast<GGML_TYPE_IQ2_S> {
         for (int k = 0; k < 2; ++k) {
             const int l = (g & 3) + k;
             const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 0x300u);
-            emit_signed2(sel[idx], (signs >> (8 * k)) & 0xFFu, c.x, v + 8 * k);
+            emit_signed2(t->entry.v[idx], t->signs.v[(signs >> (8 * k)) & 0xFFu], c.x, v + 8 * k);
         }
     }
 };
@@ -997,17 +1025,17 @@ struct Fast<GGML_TYPE_IQ3_XXS> {
         const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
         return make_float2(half_hw(lds_u16(b)) * (0.5f + (float)(aux >> 28)) * 0.5f, 0.f);
     }
-    static constexpr int kTableBytes = sizeof(k_sel_IQ3XXS);
-    static GGUF_D const void *table() { return k_sel_IQ3XXS.v; }
+    static constexpr int kTableBytes = sizeof(k_tab_IQ3XXS);
+    static GGUF_D const void *table() { return &k_tab_IQ3XXS; }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
-        const uint16_t *sel = static_cast<const uint16_t *>(tab);
+        const auto *t = static_cast<const decltype(k_tab_IQ3XXS) *>(tab);
         const int g = e0 >> 3, ib32 = g >> 2;  // g even: grid points 2g .. 2g+3
         const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
         const uint32_t idx = lds_u32_a2(b + 2 + 2 * g);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-            const uint32_t signs = iq_signs_from_index((aux >> (7 * ((g & 3) + k))) & 127);
-            emit_signed3(sel[(idx >> (16 * k)) & 0xFFu], sel[(idx >> (16 * k + 8)) & 0xFFu], signs, kIq3xxsPlus0, kIq3xxsPlus1,
+            const uint32_t signs = t->signs.v[(aux >> (7 * ((g & 3) + k))) & 127];
+            emit_signed3(t->entry.v[(idx >> (16 * k)) & 0xFFu], t->entry.v[(idx >> (16 * k + 8)) & 0xFFu], signs, kIq3xxsPlus0, kIq3xxsPlus1,
                          kIq3xxsMinus0, kIq3xxsMinus1, c.x, v + 8 * k);
         }
     }
@@ -1021,10 +1049,10 @@ struct Fast<GGML_TYPE_IQ3_S> {
         const int sc = b[106 + (ib32 >> 1)];
         return make_float2(half_hw(lds_u16(b)) * (float)(1 + 2 * ((ib32 & 1) ? (sc >> 4) : (sc & 0xF))), 0.f);
     }
-    static constexpr int kTableBytes = sizeof(k_sel_IQ3S);
-    static GGUF_D const void *table() { return k_sel_IQ3S.v; }
+    static constexpr int kTableBytes = sizeof(k_tab_IQ3S);
+    static GGUF_D const void *table() { return &k_tab_IQ3S; }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
-        const uint16_t *sel = static_cast<const uint16_t *>(tab);
+        const auto *t = static_cast<const decltype(k_tab_IQ3S) *>(tab);
         const int g = e0 >> 3, ib32 = g >> 2;
         const uint32_t qh = b[66 + ib32];
         const uint32_t idx = lds_u32_a2(b + 2 + 2 * g), sg = lds_u16(b + 74 + g);
@@ -1033,7 +1061,7 @@ struct Fast<GGML_TYPE_IQ3_S> {
             const int l = (g & 3) + k;
             const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
             const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
-            emit_signed3(sel[i1], sel[i2], (sg >> (8 * k)) & 0xFFu, kIq3sPlus0, kIq3sPlus1, kIq3sMinus0, kIq3sMinus1, c.x, v + 8 * k);
+            emit_signed3(t->entry.v[i1], t->entry.v[i2], t->signs.v[(sg >> (8 * k)) & 0xFFu], kIq3sPlus0, kIq3sPlus1, kIq3sMinus0, kIq3sMinus1, c.x, v + 8 * k);
         }
     }
 };
