@@ -128,8 +128,8 @@ LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4(float scale, uint64_t *mismatches
 /* Same, for the forms the quantizers actually run.  mode 0: as above.  mode 1: the MXFP4 form, built on the hardware
  * E2M1 conversion (`scale` must be 2^(e-128) with integer 0 <= e <= 252).  mode 2: the NVFP4 form, two hardware
  * conversions bracketing the quotient; inputs whose two conversions differ (a tie lies within 2^-21 of the quotient)
- * are redone by the exact search in the quantizer and are counted in `fallbacks` (may be null) here instead of being
- * compared.  Modes 1 and 2 look only at the inputs the quantizers route there (finite, |x| <= 2^20 * scale). */
+ * are settled by one comparison with the midpoint of the two candidate levels, as in the quantizer, and are counted in
+ * `fallbacks` (may be null).  Modes 1 and 2 look only at the inputs the quantizers route there (finite, |x| <= 2^20 * scale). */
 LIBGGUF_CUDA_API int libgguf_cuda_selftest_fp4_mode(float scale, int mode, uint64_t *mismatches, uint64_t *fallbacks);
 
 /* Number of CUDA devices visible to the process (no upstream counterpart; the converter front end uses it to

@@ -110,9 +110,10 @@ GGUF_D uint32_t nonzero_nibbles(uint32_t v) {
     v |= v >> 2;
     return v & 0x11111111u;
 }
-// Codes of elements x[0..3] (low nibbles) and y[0..3] (high nibbles) of four bytes; `undecided` gets
-// bit 4n set for every nibble n whose two conversions differ.
-GGUF_D uint32_t fp4_word_bracketed(const float *x, const float *y, const Fp4Bracket &k, uint32_t &undecided) {
+// Codes of elements x[0..3] (low nibbles) and y[0..3] (high nibbles) of four bytes by the lower end of the
+// bracket; `other` gets the nibbles (XOR) by which the upper end's codes differ: non-zero exactly where a tie
+// lies between the two ends.
+GGUF_D uint32_t fp4_word_bracketed(const float *x, const float *y, const Fp4Bracket &k, uint32_t &other) {
     float lo_a[4], hi_a[4], lo_b[4], hi_b[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -121,50 +122,31 @@ GGUF_D uint32_t fp4_word_bracketed(const float *x, const float *y, const Fp4Brac
         lo_b[i] = x[i] * k.hi;
         hi_b[i] = y[i] * k.hi;
     }
-    const uint32_t a = cvt_e2m1x8(lo_a, hi_a), b = cvt_e2m1x8(lo_b, hi_b);
-    undecided = nonzero_nibbles(a ^ b);
-    return drop_negative_zero(a);
+    const uint32_t a = drop_negative_zero(cvt_e2m1x8(lo_a, hi_a)), b = drop_negative_zero(cvt_e2m1x8(lo_b, hi_b));
+    other = a ^ b;
+    return a;
 }
-// Any scale: the same answer as best_index_fp4_thresholds by a three-step binary search over the
-// seven midpoints t[k] = {0.5,1.5,2.5,3.5,5,7,10}[k] * e (exact products).  Returns the 4-bit code.
-struct Fp4Midpoints { float t[7]; };
-GGUF_D Fp4Midpoints fp4_midpoints(float e) {
-    return {{0.5f * e, 1.5f * e, 2.5f * e, 3.5f * e, 5.f * e, 7.f * e, 10.f * e}};
-}
-GGUF_D uint32_t fp4_code_bsearch(float x, const Fp4Midpoints &k) {
-    const float m = fabsf(x);
-    const bool p2 = m > k.t[3];
-    const float mid = p2 ? k.t[5] : k.t[1], up = p2 ? k.t[6] : k.t[2], down = p2 ? k.t[4] : k.t[0];
-    uint32_t idx = p2 ? 4u : 0u;
-    const bool p1 = m > mid;
-    if (p1) idx += 2u;
-    if (m > (p1 ? up : down)) idx += 1u;
-    // sign bit, except on level 0: (idx + 7) & 8 is 8 exactly when idx >= 1
-    return idx | ((__float_as_uint(x) >> 28) & (idx + 7u) & 8u);
-}
-// Redoes the undecided elements of a 16-element sub-block whose 8 code bytes are in shared memory.
-// x: the sub-block's elements (shared memory); mask: bit 4n of `lo` / `hi` set for nibble n of the first /
-// second four bytes (byte n/2, high half when n is odd; the high halves hold elements 8..15).
-// Only valid scales reach this function (fp4_thresholds_valid).
-__device__ __noinline__ void fp4_fix_subblock(const float *x, uint8_t *bytes, uint32_t lo, uint32_t hi, float e) {
-    const Fp4Midpoints k = fp4_midpoints(e);
-#pragma unroll 1
-    for (int w = 0; w < 2; ++w) {
-        uint32_t undecided = w ? hi : lo;
-        while (undecided) {
-            const int n = (__ffs((int)undecided) - 1) >> 2;
-            undecided &= undecided - 1;
-            const uint32_t code = fp4_code_bsearch(x[4 * w + (n >> 1) + 8 * (n & 1)], k);
-            uint8_t &byte = bytes[4 * w + (n >> 1)];
-            byte = (n & 1) ? (uint8_t)((byte & 0x0F) | (code << 4)) : (uint8_t)((byte & 0xF0) | code);
-        }
+// Settles the nibbles of `word` that the bracket left open.  The two candidate codes are neighbours; the scan
+// takes the larger magnitude only when |x| lies strictly above their midpoint {0.5,1.5,2.5,3.5,5,7,10}[m] * e
+// (m = the smaller code's magnitude bits; the product is exact).  x: the sub-block in shared memory; nibble n
+// of word w is element 4w + n/2 (low halves) or 8 + 4w + n/2 (high halves).
+GGUF_D uint32_t fp4_settle(uint32_t word, uint32_t other, const float *x, int w, float e) {
+    uint32_t open = nonzero_nibbles(other);
+    const float half_e = 0.5f * e;
+    while (open) {
+        const int bit = __ffs((int)open) - 1;  // 4n
+        open &= open - 1;
+        const uint32_t m = (word >> bit) & 7u;
+        const uint32_t twice_mid = (0x140E0A07050301ull >> (8 * m)) & 0xFFu;
+        const float v = x[4 * w + (bit >> 3) + ((bit & 4) ? 8 : 0)];
+        if (fabsf(v) > (float)twice_mid * half_e) word ^= other & (0xFu << bit);
     }
+    return word;
 }
-
 // mode 0: threshold search against the scan.  mode 1: power-of-two-scale hardware path (e is
-// 2^(ebyte-128), ebyte <= 252).  mode 2: bracketed hardware path; inputs it leaves to the
-// exact search are counted in `fallbacks`, not compared.  Modes 1 and 2 only look at the
-// inputs the quantizers send down those paths (|x| <= 2^20 * e).
+// 2^(ebyte-128), ebyte <= 252).  mode 2: bracketed hardware path; inputs whose bracket straddles a
+// tie are settled by the midpoint comparison and counted in `fallbacks`.  Modes 1 and 2 only look
+// at the inputs the quantizers send down those paths (|x| <= 2^20 * e).
 __global__ void selftest_fp4_kernel(float e, int mode, int ebyte, unsigned long long *mismatches, unsigned long long *fallbacks) {
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     unsigned long long bad = 0, fell = 0;
@@ -183,10 +165,13 @@ __global__ void selftest_fp4_kernel(float e, int mode, int ebyte, unsigned long 
             if ((int)(drop_negative_zero(cvt_e2m1x8(lo, hi)) & 0xFu) != want) ++bad;
         } else {
             float xs[8] = {x, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            uint32_t undecided;
-            const uint32_t word = fp4_word_bracketed(xs, xs + 4, fp4_bracket(e), undecided);
-            if (undecided & 1u) ++fell;
-            else if ((int)(word & 0xFu) != want) ++bad;
+            uint32_t other;
+            uint32_t word = fp4_word_bracketed(xs, xs + 4, fp4_bracket(e), other);
+            if (other & 0xFu) {
+                ++fell;
+                word = fp4_settle(word, other & 0xFu, xs, 0, e);
+            }
+            if ((int)(word & 0xFu) != want) ++bad;
         }
     }
     if (bad) atomicAdd(mismatches, bad);
@@ -606,9 +591,13 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
                     const float d = ue4m3_half_to_f32(ue);
                     if (fp4_thresholds_valid(amax, d)) {
                         const Fp4Bracket k = fp4_bracket(d);
-                        uint32_t undecided[2], words[2];
+                        uint32_t other[2], words[2];
 #pragma unroll
-                        for (int w = 0; w < 2; ++w) words[w] = fp4_word_bracketed(xs + 4 * w, xs + 4 * w + 8, k, undecided[w]);
+                        for (int w = 0; w < 2; ++w) words[w] = fp4_word_bracketed(xs + 4 * w, xs + 4 * w + 8, k, other[w]);
+                        if (other[0] | other[1]) {
+#pragma unroll
+                            for (int w = 0; w < 2; ++w) words[w] = fp4_settle(words[w], other[w], xrow + 16 * sb, w, d);
+                        }
                         *scale_byte = ue;
                         if (word_aligned) {
                             reinterpret_cast<uint32_t *>(qs)[0] = words[0];
@@ -617,7 +606,6 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
                             st32(qs, words[0]);
                             st32(qs + 4, words[1]);
                         }
-                        if (undecided[0] | undecided[1]) fp4_fix_subblock(xrow + 16 * sb, qs, undecided[0], undecided[1], d);
                         done = true;
                     }
                 }
