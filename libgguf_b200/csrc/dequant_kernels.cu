@@ -921,6 +921,24 @@ static __device__ __align__(16) const selectors::Tables<uint16_t, 256, 128> k_ta
     selectors::make3(selectors::packed_IQ3XXS), selectors::make_signs<128, true>()};
 static __device__ __align__(16) const selectors::Tables<uint16_t, 512, 256> k_tab_IQ3S = {
     selectors::make3(selectors::packed_IQ3S), selectors::make_signs<256, true>()};
+static __device__ __align__(16) const selectors::Table<uint32_t, 2048> k_tab_IQ1S = selectors::make2(selectors::packed_IQ1S);
+
+// IQ1: v = scale * ((code + 1 - 1) + bias') with bias = -1 -+ 0.125 already holding the -1.  The codes 0..2 enter
+// the mantissa of 2^20 in units of 1/8 (table bytes 0, 8, 16), so one subtraction of 2^20 - bias removes the
+// magic constant and applies the bias; both are multiples of 1/8 below 2^21, hence exact, as are upstream's two steps.
+constexpr uint32_t kIq1Eighths = 0u | (8u << 8) | (16u << 16);
+GGUF_D float magic_eighths(uint32_t w, int k) { return __uint_as_float(__byte_perm(w, 0x49800000u, 0x7640u | (uint32_t)k)); }
+GGUF_D void emit_iq1(uint32_t sel, float scale, float bias, float *v) {
+    const float off = bias - 1048576.f;
+    const float2 nb = make_float2(off, off), sc = make_float2(scale, scale);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t levels = __byte_perm(kIq1Eighths, 0, sel >> (16 * h));
+        const float2 a = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_eighths(levels, 0), magic_eighths(levels, 1)), nb));
+        const float2 b = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_eighths(levels, 2), magic_eighths(levels, 3)), nb));
+        v[4 * h] = a.x; v[4 * h + 1] = a.y; v[4 * h + 2] = b.x; v[4 * h + 3] = b.y;
+    }
+}
 
 constexpr uint32_t biased_levels(int a, int b, int c, int d) {
     return (uint32_t)(128 + a) | ((uint32_t)(128 + b) << 8) | ((uint32_t)(128 + c) << 16) | ((uint32_t)(128 + d) << 24);
@@ -1075,14 +1093,17 @@ struct Fast<GGML_TYPE_IQ1_S> {
         const uint32_t qh = lds_u16(b + 34 + 2 * ib);
         return make_float2(half_hw(lds_u16(b)) * (float)(2 * ((qh >> 12) & 7) + 1), (qh & 0x8000u) ? -1.125f : -0.875f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_tab_IQ1S);
+    static GGUF_D const void *table() { return &k_tab_IQ1S; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
         const int g = e0 >> 3, ib = g >> 2;
         const uint32_t qh = lds_u16(b + 34 + 2 * ib), low = lds_u16(b + 2 + g);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const int l = (g & 3) + k;
             const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8);
-            emit_grid2(__ldg(&k_codebook_IQ1S[idx]), kIq1Levels, 0u, c.x, c.y, v + 8 * k);
+            emit_iq1(sel[idx], c.x, c.y, v + 8 * k);
         }
     }
 };
@@ -1098,14 +1119,17 @@ struct Fast<GGML_TYPE_IQ1_M> {
         const uint32_t sc = lds_u16(b + 48 + 2 * (ib >> 1));
         return make_float2(half_hw(dbits) * (float)(2 * ((sc >> (6 * (ib & 1) + 3 * (g16 & 1))) & 7) + 1), 0.f);
     }
-    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
+    static constexpr int kTableBytes = sizeof(k_tab_IQ1S);
+    static GGUF_D const void *table() { return &k_tab_IQ1S; }
+    static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
         const int g = e0 >> 3;  // even: grid points g, g + 1 share the byte qh[g / 2]
         const uint32_t qh = b[32 + (g >> 1)], low = lds_u16(b + g);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
             const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | ((qh << (k ? 4 : 8)) & 0x700u);
             const float bias = (qh & (k ? 0x80u : 0x08u)) ? -1.125f : -0.875f;
-            emit_grid2(__ldg(&k_codebook_IQ1S[idx]), kIq1Levels, 0u, c.x, bias, v + 8 * k);
+            emit_iq1(sel[idx], c.x, bias, v + 8 * k);
         }
     }
 };
