@@ -800,56 +800,14 @@ struct Fast<GGML_TYPE_Q5_1> {
 };
 
 // ---- codebook types ----------------------------------------------------------------------------
-// A packed codebook entry holds eight 2-bit codes (IQ2, IQ1) or four 3-bit codes (IQ3).  The codes are
-// widened to 4-bit permute selectors and looked up in a level table held in registers.
-// eight 2-bit fields -> eight nibbles
-GGUF_D uint32_t widen_2bit(uint32_t c) {
-    c = (c | (c << 8)) & 0x00FF00FFu;
-    c = (c | (c << 4)) & 0x0F0F0F0Fu;
-    return (c | (c << 2)) & 0x33333333u;
-}
-// four 3-bit fields -> four nibbles
-GGUF_D uint32_t widen_3bit(uint32_t c) {
-    c = (c & 0x03Fu) | ((c << 2) & 0x3F00u);
-    return (c & 0x0707u) | ((c << 1) & 0x7070u);
-}
 // unaligned little-endian 32-bit value from a 2-byte aligned shared-memory address
 GGUF_D uint32_t lds_u32_a2(const uint8_t *p) { return lds_u16(p) | (lds_u16(p + 2) << 16); }
-// v[0..3] = scale * (byte_k(levels) + bias), sign of v[k] flipped when bit k of `signs` is set
-GGUF_D void emit4(uint32_t levels, uint32_t signs, float scale, float bias, float *v) {
-    const float2 nb = make_float2(-kTwo23, -kTwo23), sc = make_float2(scale, scale), bs = make_float2(bias, bias);
-    float2 a = __fadd2_rn(make_float2(magic_byte(levels, 0), magic_byte(levels, 1)), nb);
-    float2 b = __fadd2_rn(make_float2(magic_byte(levels, 2), magic_byte(levels, 3)), nb);
-    if (bias != 0.f) { a = __fadd2_rn(a, bs); b = __fadd2_rn(b, bs); }
-    a = __fmul2_rn(sc, a);
-    b = __fmul2_rn(sc, b);
-    v[0] = __uint_as_float(__float_as_uint(a.x) ^ ((signs << 31) & 0x80000000u));
-    v[1] = __uint_as_float(__float_as_uint(a.y) ^ ((signs << 30) & 0x80000000u));
-    v[2] = __uint_as_float(__float_as_uint(b.x) ^ ((signs << 29) & 0x80000000u));
-    v[3] = __uint_as_float(__float_as_uint(b.y) ^ ((signs << 28) & 0x80000000u));
-}
-// Eight values of a 2-bit grid point.  `table`: the levels of codes 0..3 in its bytes.
-GGUF_D void emit_grid2(uint32_t code, uint32_t table, uint32_t signs, float scale, float bias, float *v) {
-    const uint32_t sel = widen_2bit(code);
-    emit4(__byte_perm(table, 0, sel & 0xFFFFu), signs, scale, bias, v);
-    emit4(__byte_perm(table, 0, sel >> 16), signs >> 4, scale, bias, v + 4);
-}
-// Four values of a 3-bit grid point.  (t0, t1): the levels of codes 0..7.
-GGUF_D void emit_grid3(uint32_t code, uint32_t t0, uint32_t t1, uint32_t signs, float scale, float *v) {
-    emit4(__byte_perm(t0, t1, widen_3bit(code)), signs, scale, 0.f, v);
-}
-constexpr uint32_t kIq2Levels = 8u | (25u << 8) | (43u << 16);                       // upstream iq2xxs_grid bytes
-constexpr uint32_t kIq3xxsLevels0 = 4u | (12u << 8) | (20u << 16) | (28u << 24);     // upstream iq3xxs_grid bytes
-constexpr uint32_t kIq3xxsLevels1 = 36u | (44u << 8) | (52u << 16) | (62u << 24);
-constexpr uint32_t kIq3sLevels0 = 1u | (3u << 8) | (5u << 16) | (7u << 24);          // upstream iq3s_grid bytes
-constexpr uint32_t kIq3sLevels1 = 9u | (11u << 8) | (13u << 16) | (15u << 24);
-constexpr uint32_t kIq1Levels = 0u | (1u << 8) | (2u << 16);                         // grid value + 1
 
-// ---- signed codebook types: selector tables --------------------------------------------------
-// For the IQ2 and IQ3 families the packed codebook entry is kept already widened to permute selectors
-// (one nibble per coordinate), and the element's sign goes into bit 2 of its nibble (IQ2: the permute
-// then reads the level from a table of +levels and -levels) or into a second permute that picks
-// between the +level and the -level (IQ3).  The levels are stored with an offset of 128, removed
+// A packed codebook entry holds eight 2-bit codes (IQ2, IQ1) or four 3-bit codes (IQ3).  The decoders keep
+// every entry already widened to permute selectors (one nibble per coordinate); the levels themselves sit in
+// registers and a PRMT looks four of them up at once.  For the IQ2 and IQ3 families the element's sign goes
+// into bit 2 of its nibble (IQ2: the permute then reads the level from a table of +levels and -levels) or
+// into a second permute that picks between the +level and the -level (IQ3).  The levels are stored with an offset of 128, removed
 // together with the 2^23 of the byte-to-float step.  The tables are copied to shared memory by every
 // CTA: a gather over a 1-4 KB table costs a few bank conflicts there, one L1 wavefront per touched
 // line in global memory.
