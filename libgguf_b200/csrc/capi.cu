@@ -17,6 +17,7 @@
 #include "../../include/libgguf_cuda_native.h"
 #include "device_state.h"
 #include "gguf_common.cuh"
+#include "host_stage.h"
 #include "kernels.h"
 
 namespace gguf {
@@ -168,6 +169,7 @@ struct HostCallStaging {
     float *d_imatrix = nullptr;
     size_t im_cap = 0;
     cudaStream_t stream = nullptr;
+    StageRing ring;  // large calls: pinned slots, host copies overlapped with the device
 };
 HostCallStaging g_staging[kMaxDevices];
 
@@ -193,6 +195,25 @@ bool pick_device(int *dev) {
 
 // Rows per staged piece: bounded so that a huge host matrix never needs a huge device buffer.
 constexpr size_t kStageBytes = size_t(256) << 20;
+// Calls that move at least kPipelineBytes go through the pinned ring in pieces of kPieceBytes.
+constexpr size_t kPipelineBytes = size_t(8) << 20;
+constexpr size_t kPieceBytes = size_t(32) << 20;
+
+// LIBGGUF_CUDA_HOST_PIPELINE=0 keeps every call on the single-buffer path.
+bool pipeline_enabled() {
+    static const bool enabled = [] {
+        const char *env = getenv("LIBGGUF_CUDA_HOST_PIPELINE");
+        return !(env && env[0] == '0');
+    }();
+    return enabled;
+}
+
+int64_t piece_rows(size_t in_row, size_t out_row, int64_t nrows) {
+    const size_t widest = in_row > out_row ? in_row : out_row;
+    int64_t rows = (int64_t)(kPieceBytes / widest);
+    if (rows < 1) rows = 1;
+    return rows < nrows ? rows : nrows;
+}
 
 }  // namespace
 
@@ -220,17 +241,29 @@ extern "C" size_t libgguf_quantize_chunk(enum ggml_type type, const float *src, 
         if (!state) return 0;
     }
     const size_t in_row = (size_t)n_per_row * 4;
-    int64_t rows_per_piece = (int64_t)(kStageBytes / in_row);
-    if (rows_per_piece < 1) rows_per_piece = 1;
-    if (rows_per_piece > nrows) rows_per_piece = nrows;
-    if (!grow(&st.d_in, &st.in_cap, (size_t)rows_per_piece * in_row)) return 0;
-    if (!grow(&st.d_out, &st.out_cap, (size_t)rows_per_piece * row_size)) return 0;
     const float *d_im = nullptr;
     if (imatrix && !storage) {
         if (!grow((void **)&st.d_imatrix, &st.im_cap, in_row)) return 0;
         if (cudaMemcpyAsync(st.d_imatrix, imatrix, in_row, cudaMemcpyHostToDevice, st.stream) != cudaSuccess) { cudaGetLastError(); return 0; }
         d_im = st.d_imatrix;
     }
+    if ((size_t)nrows * in_row >= kPipelineBytes && pipeline_enabled()) {
+        if (d_im && cudaStreamSynchronize(st.stream) != cudaSuccess) { cudaGetLastError(); return 0; }
+        const int64_t rpp = piece_rows(in_row, row_size, nrows);
+        if (!st.ring.reserve((size_t)rpp * in_row, (size_t)rpp * row_size)) { cudaGetLastError(); return 0; }
+        const cudaError_t err = run_staged(st.ring, (const char *)in, in_row, out, row_size, nrows, rpp,
+            [&](const void *d_in, void *d_out, int64_t, int64_t nr, cudaStream_t stream) {
+                if (storage) return launch_store(type, (const float *)d_in, d_out, nr * n_per_row, stream);
+                return launch_quantize((int)type, (const float *)d_in, d_im, d_out, nr, n_per_row, state, stream);
+            });
+        if (err != cudaSuccess) { cudaGetLastError(); return 0; }
+        return (size_t)nrows * row_size;
+    }
+    int64_t rows_per_piece = (int64_t)(kStageBytes / in_row);
+    if (rows_per_piece < 1) rows_per_piece = 1;
+    if (rows_per_piece > nrows) rows_per_piece = nrows;
+    if (!grow(&st.d_in, &st.in_cap, (size_t)rows_per_piece * in_row)) return 0;
+    if (!grow(&st.d_out, &st.out_cap, (size_t)rows_per_piece * row_size)) return 0;
     for (int64_t r0 = 0; r0 < nrows; r0 += rows_per_piece) {
         const int64_t nr = nrows - r0 < rows_per_piece ? nrows - r0 : rows_per_piece;
         cudaError_t err = cudaMemcpyAsync(st.d_in, in + r0 * n_per_row, (size_t)nr * in_row, cudaMemcpyHostToDevice, st.stream);
@@ -260,6 +293,16 @@ extern "C" size_t libgguf_dequantize_chunk(enum ggml_type type, const void *src,
     std::lock_guard<std::mutex> guard(st.lock);
     if (!st.stream && cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); return 0; }
     const size_t out_row = (size_t)n_per_row * 4;
+    if ((size_t)nrows * out_row >= kPipelineBytes && pipeline_enabled()) {
+        const int64_t rpp = piece_rows(row_size, out_row, nrows);
+        if (!st.ring.reserve((size_t)rpp * row_size, (size_t)rpp * out_row)) { cudaGetLastError(); return 0; }
+        const cudaError_t err = run_staged(st.ring, in, row_size, (char *)out, out_row, nrows, rpp,
+            [&](const void *d_in, void *d_out, int64_t, int64_t nr, cudaStream_t stream) {
+                return launch_dequantize((int)type, d_in, d_out, nr * n_per_row, 0, stream);
+            });
+        if (err != cudaSuccess) { cudaGetLastError(); return 0; }
+        return (size_t)nrows * (size_t)n_per_row * sizeof(float);
+    }
     int64_t rows_per_piece = (int64_t)(kStageBytes / out_row);
     if (rows_per_piece < 1) rows_per_piece = 1;
     if (rows_per_piece > nrows) rows_per_piece = nrows;
@@ -282,9 +325,10 @@ extern "C" void libgguf_quantize_free(void) {
     for (int dev = 0; dev < kMaxDevices; ++dev) {
         HostCallStaging &st = g_staging[dev];
         std::lock_guard<std::mutex> guard(st.lock);
-        if (st.d_in || st.d_out || st.d_imatrix || st.stream) {
+        if (st.d_in || st.d_out || st.d_imatrix || st.stream || st.ring.stream[0]) {
             if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); continue; }
             if (st.stream) cudaStreamSynchronize(st.stream);
+            st.ring.release();
             cudaFree(st.d_in); cudaFree(st.d_out); cudaFree(st.d_imatrix);
             if (st.stream) cudaStreamDestroy(st.stream);
             st.d_in = st.d_out = nullptr;

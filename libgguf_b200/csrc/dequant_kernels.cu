@@ -1121,11 +1121,15 @@ struct Fast<GGML_TYPE_TQ2_0> {
 // TQ1_0: digit n of a byte is ((byte * 3^n) & 0xFF) * 3 >> 8.  Elements 0..159 take digit e/32 of byte
 // e%32, elements 160..239 digit (e-160)/16 of byte 32 + (e-160)%16, elements 240..255 digit (e-240)/4
 // of byte 48 + (e-240)%4.  Four bytes at a time: the even and the odd bytes are multiplied in 16-bit
-// lanes (255 * 81 < 2^15, so nothing crosses a lane).
-GGUF_D uint32_t tq1_digits(uint32_t w, uint32_t pow3) {
-    const uint32_t even = ((((w & 0x00FF00FFu) * pow3) & 0x00FF00FFu) * 3u >> 8) & 0x00030003u;
-    const uint32_t odd = (((((w >> 8) & 0x00FF00FFu) * pow3) & 0x00FF00FFu) * 3u >> 8) & 0x00030003u;
-    return even | (odd << 8);
+// lanes (255 * 81 < 2^15, so nothing crosses a lane); after the multiplication by 3 (at most 765) the
+// digit is the lane's high byte, which the byte-to-float permute picks up directly.
+GGUF_D void tq1_emit4(uint32_t w, uint32_t pow3, float2 c, float *v) {
+    const uint32_t even = (((w & 0x00FF00FFu) * pow3) & 0x00FF00FFu) * 3u;
+    const uint32_t odd = ((((w >> 8) & 0x00FF00FFu) * pow3) & 0x00FF00FFu) * 3u;
+    const float2 nb = make_float2(-(kTwo23 + 1.f), -(kTwo23 + 1.f)), sc = make_float2(c.x, c.x);
+    const float2 a = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_byte(even, 1), magic_byte(odd, 1)), nb));
+    const float2 b = __fmul2_rn(sc, __fadd2_rn(make_float2(magic_byte(even, 3), magic_byte(odd, 3)), nb));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 template <>
 struct Fast<GGML_TYPE_TQ1_0> {
@@ -1140,12 +1144,8 @@ struct Fast<GGML_TYPE_TQ1_0> {
         const uint4 q = lds16_any(b + at);  // 54-byte blocks: the 16 bytes stay inside the tile's padding
         const uint32_t w[4] = {q.x, last ? q.x : q.y, last ? q.x : q.z, last ? q.x : q.w};
         const uint32_t pw[4] = {last ? 1u : p, last ? 3u : p, last ? 9u : p, last ? 27u : p};
-        uint4 digits;
-        digits.x = tq1_digits(w[0], pw[0]);
-        digits.y = tq1_digits(w[1], pw[1]);
-        digits.z = tq1_digits(w[2], pw[2]);
-        digits.w = tq1_digits(w[3], pw[3]);
-        affine16<false>(digits, -(kTwo23 + 1.f), c, v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tq1_emit4(w[i], pw[i], c, v + 4 * i);
     }
 };
 

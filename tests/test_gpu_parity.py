@@ -228,3 +228,23 @@ def test_edge_blocks_of_the_simple_types(gguf, checker, name):
     got, want = gguf.quantize_rows(x, qtype), checker.quantize_rows(x, qtype)
     for r in range(x.shape[0]):
         assert np.array_equal(got[r], want[r]), (name, r, "finite" if r < finite else "with NaN")
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q6_K"])
+def test_large_host_calls_go_through_the_pinned_ring_in_ragged_pieces(gguf, checker, name):
+    """A host-pointer call of 82 MB is split into three pieces (8192, 8192 and 3616 rows of 1024) that overlap on two
+    streams; every row must still equal the checker's, with and without an importance row, and decode back bit-exactly."""
+    qtype = inputs.QTYPES[name]
+    rows, cols = 20000, 1024
+    x = (np.random.default_rng(23).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.05))
+    want = checker.quantize_rows(x, qtype)
+    got = gguf.quantize_rows(x, qtype)
+    assert np.array_equal(got, want)
+    imatrix = np.random.default_rng(24).random(cols, dtype=np.float32) + np.float32(0.1)
+    if name != "Q8_0":
+        assert np.array_equal(gguf.quantize_rows(x, qtype, imatrix=imatrix), checker.quantize_rows(x, qtype, imatrix=imatrix))
+    dec = gguf.dequantize_rows(got, qtype, cols)
+    assert np.array_equal(dec.view(np.uint32), checker.dequantize_rows(want, qtype, cols).view(np.uint32))
+    # a chunk that starts inside the matrix
+    part = gguf.quantize_rows(x[5000:19000], qtype)
+    assert np.array_equal(part, want[5000:19000])
