@@ -197,7 +197,7 @@ bool pick_device(int *dev) {
 constexpr size_t kStageBytes = size_t(256) << 20;
 // Calls that move at least kPipelineBytes go through the pinned ring in pieces of kPieceBytes.
 constexpr size_t kPipelineBytes = size_t(8) << 20;
-constexpr size_t kPieceBytes = size_t(32) << 20;
+constexpr size_t kPieceBytes = size_t(16) << 20;
 
 // LIBGGUF_CUDA_HOST_PIPELINE=0 keeps every call on the single-buffer path.
 bool pipeline_enabled() {

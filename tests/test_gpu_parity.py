@@ -232,7 +232,7 @@ def test_edge_blocks_of_the_simple_types(gguf, checker, name):
 
 @pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q6_K"])
 def test_large_host_calls_go_through_the_pinned_ring_in_ragged_pieces(gguf, checker, name):
-    """A host-pointer call of 82 MB is split into three pieces (8192, 8192 and 3616 rows of 1024) that overlap on two
+    """A host-pointer call of 82 MB is split into five pieces (four of 4096 rows of 1024 and one of 3616) that overlap on two
     streams; every row must still equal the checker's, with and without an importance row, and decode back bit-exactly."""
     qtype = inputs.QTYPES[name]
     rows, cols = 20000, 1024
