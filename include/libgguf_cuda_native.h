@@ -116,6 +116,12 @@ LIBGGUF_CUDA_API const char *libgguf_cuda_thread_last_error(void);
 /* Number of kernels this library has launched in this process (all devices, all threads). */
 LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
 
+/* No upstream counterpart.  The quantizers that stage their input with bulk asynchronous copies bound every wait
+ * for a copy; a wait that runs out makes the CTA count it and return (its part of the output is then not written).
+ * Stores the count of such events on the current device since the library was loaded; 0 on a healthy device.
+ * Blocking (waits for the device). */
+LIBGGUF_CUDA_API int libgguf_cuda_staging_timeouts(uint64_t *count);
+
 /* Builds (once per device) the IQ search tables a quantizer of this type needs, on the current
  * device, and waits for the upload.  Optional: the row functions do it on first use. */
 LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);

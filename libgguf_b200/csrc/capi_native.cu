@@ -35,6 +35,7 @@ using namespace gguf;
 namespace gguf {
 cudaError_t selftest_fp4(float e, int mode, int ebyte, unsigned long long *device_counters, cudaStream_t stream);
 int64_t static_scratch_max_rows();
+cudaError_t read_staging_timeouts(unsigned long long *count);
 cudaError_t launch_quantize_legacy_weighted_static(int type, const float *src, const float *qw, void *dst, int64_t nrows,
                                                    int64_t n_per_row, cudaStream_t stream);
 }  // namespace gguf
@@ -174,6 +175,15 @@ const char *libgguf_cuda_last_error(const libgguf_cuda_context *ctx) {
 const char *libgguf_cuda_thread_last_error(void) { return t_thread_error.c_str(); }
 
 uint64_t libgguf_cuda_kernel_launch_count(void) { return launch_count(); }
+
+int libgguf_cuda_staging_timeouts(uint64_t *count) {
+    if (!count) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "staging_timeouts requires an output pointer");
+    unsigned long long value = 0;
+    const cudaError_t error = gguf::read_staging_timeouts(&value);
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
+    *count = value;
+    return ok(nullptr);
+}
 
 int libgguf_cuda_event_create(libgguf_cuda_context *ctx, libgguf_cuda_event **out) {
     if (!ctx || !out) return fail(ctx, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "event create requires a context and output pointer");

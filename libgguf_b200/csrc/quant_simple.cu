@@ -11,6 +11,7 @@
 #include <float.h>
 #include <math.h>
 
+#include "bulk_copy.cuh"
 #include "gguf_common.cuh"
 #include "gguf_tables.cuh"
 #include "kernels.h"
@@ -632,47 +633,54 @@ GGUF_D uint32_t tq1_byte(uint32_t q) { return (q * 256u + 242u) / 243u; }
 constexpr int kTernThreads = 128;               // eight lanes per block
 constexpr int kTernBlocks = kTernThreads / 8;   // blocks per tile
 
+// Copies that did not land within the wait limit, all launches of this process on the device.
+__device__ unsigned long long g_staging_timeouts;
+
 // TQ1_0 / TQ2_0: 256-element blocks, d = max |x| (upstream tq1_0.cpp:16-98, tq2_0.cpp:16-53).
-// Persistent CTAs walk tiles of sixteen blocks with a stride of the grid size and stage tile i+1 by 16-byte
-// asynchronous copies while tile i is encoded.  Eight lanes share a block: every output byte mixes elements 32
-// (or 16, or 4) apart, and lane L takes the elements of bytes 4L..4L+3 of each 32-byte group (TQ1_0: also bytes
-// 32+2L, 33+2L and, for L < 4, byte 48+L) straight from the staged block, 30 to 34 elements in registers.  The
-// encoded tile leaves as 16-byte vectors.
+// Persistent CTAs walk tiles of sixteen blocks (16 KB, contiguous) with a stride of the grid size; one thread
+// stages tile i+1 with a single bulk asynchronous copy while tile i is encoded.  Eight lanes share a block: every
+// output byte mixes elements 32 (or 16, or 4) apart, and lane L takes the elements of bytes 4L..4L+3 of each
+// 32-byte group (TQ1_0: also bytes 32+2L, 33+2L and, for L < 4, byte 48+L) straight from the staged block, 30 to 34
+// elements in registers.  The encoded tile leaves as 16-byte vectors.
 template <bool TQ1>
 __global__ void __launch_bounds__(kTernThreads) quant_ternary_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,
                                                                     int64_t nblocks) {
     constexpr int BYTES = TQ1 ? 54 : 66;
-    __shared__ __align__(16) float xs[2][kTernBlocks * 256];
+    __shared__ __align__(128) float xs[2][kTernBlocks * 256];
     __shared__ __align__(16) uint8_t stage[kTernBlocks * BYTES + 16];
+    __shared__ __align__(8) uint64_t landed[2];
     const int group = threadIdx.x >> 3, L = threadIdx.x & 7;
     const int64_t ntiles = (nblocks + kTernBlocks - 1) / kTernBlocks;
     uint8_t *tile = stage + (reinterpret_cast<uintptr_t>(dst) & 15);  // a tile starts a multiple of 16 bytes into dst
 
-    auto prefetch = [&](int64_t t, float *xin) {
+    if (threadIdx.x == 0) {
+        mbarrier_init(&landed[0], 1);
+        mbarrier_init(&landed[1], 1);
+        fence_async_shared();
+    }
+    __syncthreads();
+    // thread 0 only; every thread has passed a barrier since it last read the slot
+    auto prefetch = [&](int64_t t, int slot) {
         const int64_t left = nblocks - t * kTernBlocks;
-        const int nvec = (int)(left < kTernBlocks ? left : kTernBlocks) * 64;
-        const float4 *g4 = reinterpret_cast<const float4 *>(src + t * kTernBlocks * 256);
-#pragma unroll
-        for (int k = 0; k < kTernBlocks * 64 / kTernThreads; ++k) {
-            const int i = k * kTernThreads + threadIdx.x;
-            if (i < nvec) cp_async16(xin + 4 * i, g4 + i);
-        }
-        cp_async_commit();
+        const uint32_t bytes = (uint32_t)(left < kTernBlocks ? left : kTernBlocks) * 1024u;
+        fence_async_shared();
+        bulk_load(xs[slot], src + t * kTernBlocks * 256, bytes, &landed[slot]);
     };
 
     int64_t t = blockIdx.x;
     grid_dependents_may_launch();
     grid_dependency_wait();
-    if (t < ntiles) prefetch(t, xs[0]);
+    if (t < ntiles && threadIdx.x == 0) prefetch(t, 0);
     for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
         const int64_t tnext = t + gridDim.x;
-        if (tnext < ntiles) {
-            prefetch(tnext, xs[(it + 1) & 1]);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+        if (tnext < ntiles && threadIdx.x == 0) prefetch(tnext, (it + 1) & 1);
+        // slot it & 1 is on its (it / 2)-th use: wait for that phase
+        const bool arrived = mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u);
+        // also orders the previous tile's flush before this tile's writes to the stage
+        if (!__syncthreads_and(arrived)) {
+            if (threadIdx.x == 0) atomicAdd(&g_staging_timeouts, 1ull);
+            return;
         }
-        __syncthreads();  // tile t has landed; every thread is done with the previous tile's stage
         const int64_t first = t * kTernBlocks;
         const float *xb = xs[it & 1] + group * 256;
         // Groups past the end of a short last tile run on stale data (all lanes take part in the shuffles) and store nothing.
@@ -810,6 +818,10 @@ cudaError_t launch32(const float *src, void *dst, int64_t nelems, const float *m
 }
 
 }  // namespace
+
+cudaError_t read_staging_timeouts(unsigned long long *count) {
+    return cudaMemcpyFromSymbol(count, g_staging_timeouts, sizeof(*count));
+}
 
 cudaError_t launch_store(int type, const float *src, void *dst, int64_t nelems, cudaStream_t stream) {
     if (nelems <= 0) return cudaSuccess;

@@ -248,3 +248,16 @@ def test_large_host_calls_go_through_the_pinned_ring_in_ragged_pieces(gguf, chec
     # a chunk that starts inside the matrix
     part = gguf.quantize_rows(x[5000:19000], qtype)
     assert np.array_equal(part, want[5000:19000])
+
+
+def test_bulk_copy_staging_never_ran_out_of_its_wait_limit(gguf):
+    """The ternary quantizers stage their input with bulk asynchronous copies whose waits are bounded; a wait that
+    gives up is counted on the device.  After a pass over a ragged number of blocks the count must still be zero."""
+    import ctypes
+    from libgguf_b200._native import lib
+    x = np.random.default_rng(5).standard_normal((1237, 768), dtype=np.float32)
+    for name in ("TQ1_0", "TQ2_0"):
+        gguf.quantize_rows(x, inputs.QTYPES[name])
+    count = ctypes.c_uint64(123)
+    assert lib.libgguf_cuda_staging_timeouts(ctypes.byref(count)) == 0
+    assert count.value == 0
