@@ -122,6 +122,11 @@ LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
  * Blocking (waits for the device). */
 LIBGGUF_CUDA_API int libgguf_cuda_staging_timeouts(uint64_t *count);
 
+/* No upstream counterpart.  memcpy split over the library's pool of host copy threads (LIBGGUF_CUDA_COPY_THREADS,
+ * default 8 on hosts with 16 or more CPUs); the host-pointer chunk functions of libgguf.h use it to fill and drain
+ * their pinned staging slots.  Needs no device.  The ranges must not overlap. */
+LIBGGUF_CUDA_API void libgguf_cuda_host_copy(void *dst, const void *src, size_t bytes);
+
 /* Builds (once per device) the IQ search tables a quantizer of this type needs, on the current
  * device, and waits for the upload.  Optional: the row functions do it on first use. */
 LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);

@@ -9,6 +9,7 @@
 #include "../../include/libgguf_cuda_native.h"
 #include "device_state.h"
 #include "gguf_common.cuh"
+#include "host_stage.h"
 #include "kernels.h"
 
 struct libgguf_cuda_context {
@@ -175,6 +176,10 @@ const char *libgguf_cuda_last_error(const libgguf_cuda_context *ctx) {
 const char *libgguf_cuda_thread_last_error(void) { return t_thread_error.c_str(); }
 
 uint64_t libgguf_cuda_kernel_launch_count(void) { return launch_count(); }
+
+void libgguf_cuda_host_copy(void *dst, const void *src, size_t bytes) {
+    if (dst && src && bytes) gguf::parallel_copy(dst, src, bytes);
+}
 
 int libgguf_cuda_staging_timeouts(uint64_t *count) {
     if (!count) return fail(nullptr, LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT, "staging_timeouts requires an output pointer");

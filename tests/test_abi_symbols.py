@@ -45,3 +45,20 @@ def test_type_queries_need_no_device():
     assert lib.libgguf_cuda_dequantize_row_size(30, 10) == 20
     assert lib.libgguf_cuda_dequantize_row_size(14, 256) == 210
     assert lib.libgguf_cuda_last_error(None) == b"libgguf CUDA context is null"
+
+
+def test_host_copy_pool_copies_every_byte():
+    """The copy pool behind the host-pointer calls (no device involved): large, odd-sized and back-to-back
+    copies arrive intact and touch nothing past their end."""
+    import numpy as np
+    from libgguf_b200 import _native
+    lib = ctypes.CDLL(str(_native.LIB_PATH))
+    lib.libgguf_cuda_host_copy.restype = None
+    lib.libgguf_cuda_host_copy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+    rng = np.random.default_rng(3)
+    src = rng.integers(0, 256, size=48 << 20, dtype=np.uint8)
+    for offset, size in [(0, 48 << 20), (1, (33 << 20) + 12345), (7, (2 << 20) + 1), (3, 4096), (0, 0)] + [(i, (3 << 20) + 7777 * i) for i in range(1, 40)]:
+        dst = np.full(size + 64, 0xA5, dtype=np.uint8)
+        lib.libgguf_cuda_host_copy(dst.ctypes.data, src.ctypes.data + offset, size)
+        assert np.array_equal(dst[:size], src[offset:offset + size])
+        assert (dst[size:] == 0xA5).all()
