@@ -590,12 +590,19 @@ def convert(options: Options) -> dict:
     import ctypes
     from concurrent.futures import ThreadPoolExecutor
 
+    import time
+
     from ._native import lib
     from .convert import ConversionPipeline   # needs the CUDA library; planning above does not
 
+    clock = time.perf_counter
+    began = clock()
+    # wall-clock seconds of the calling thread per stage; the reads and the host<->device copies overlap the encode
+    spent = {"metadata": 0.0, "read": 0.0, "cuda_quant": 0.0, "write": 0.0}
     dst, _, _, kv, plans, result = plan_file(options)
     infos = [TensorInfo(p.key, tuple(p.write_shape), int(Q[p.qtype]), p.nbytes) for p in plans]
     head = header_bytes(kv, infos)
+    spent["metadata"] = clock() - began
     source = np.memmap(options.src, dtype=np.uint8, mode="r")
     n_gpus = options.gpus
     if n_gpus <= 0:
@@ -644,6 +651,7 @@ def convert(options: Options) -> dict:
             at_out += _align(nbytes_out)
         return entries, outputs, futures
 
+    counts = {"cuda_chunks": 0, "cuda_max_input": 0, "cuda_max_output": 0}
     try:
         batches = list(_batches(_pieces(plans, cap), cap))
         arenas = [(_PinnedArena(lib, ctx, cap + 4096), _PinnedArena(lib, ctx, cap + 4096)) for _ in range(min(2, len(batches)))]
@@ -653,17 +661,27 @@ def convert(options: Options) -> dict:
             staged = stage(batches[0], arenas[0]) if batches else None
             for i, batch in enumerate(batches):
                 entries, outputs, futures = staged
+                t0 = clock()
                 for f in futures:
                     f.result()
+                t1 = clock()
                 if i + 1 < len(batches):   # the next batch's reads run while this one is encoded and written
                     staged = stage(batches[i + 1], arenas[(i + 1) & 1])
                 if entries:
                     pipe.quantize(entries)
+                t2 = clock()
                 for piece, enc in zip(batch, outputs):
                     p = piece.plan
                     out.write(enc if enc is not None else source[p.data_begin:p.data_end])
                     if piece.last:
                         out.write(b"\0" * (pad_to(p.nbytes) - p.nbytes))
+                spent["read"] += t1 - t0
+                spent["cuda_quant"] += t2 - t1
+                spent["write"] += clock() - t2
+                for entry in entries:
+                    counts["cuda_chunks"] += 1
+                    counts["cuda_max_input"] = max(counts["cuda_max_input"], entry[1].nbytes)
+                    counts["cuda_max_output"] = max(counts["cuda_max_output"], entry[3].nbytes)
     finally:
         readers.shutdown(wait=True)
         os.close(fd)
@@ -671,7 +689,22 @@ def convert(options: Options) -> dict:
             for arena in pair:
                 arena.close()
         lib.libgguf_cuda_context_destroy(ctx)
+    result["timings"] = dict(spent, total=clock() - began, tensors=len(plans), cuda_tensors=sum(1 for p in plans if p.qtype != p.source_dtype),
+                             threads=min(8, os.cpu_count() or 1), scratch=cap, cuda_vram=chunk, **counts)
     return result
+
+
+def timings_line(result: dict) -> str:
+    """The stderr line of upstream's --timings (csrc/quantize_gguf.cpp:2527-2547), same tokens in the same order.  The
+    reads, the host<->device copies and the encode overlap here: `read` is the time the writer waited for source
+    bytes, `cuda_quant` the time it waited for the GPUs (copies included, hence h2d = d2h = 0), nothing is converted
+    on the CPU and nothing is verified against a second backend."""
+    t = result["timings"]
+    return ("Timings: total=%.3fs metadata=%.3fs read=%.3fs cpu_convert=%.3fs h2d=%.3fs cuda_quant=%.3fs d2h=%.3fs write=%.3fs "
+            "tensors=%d cuda_tensors=%d cuda_verified=%d cuda_chunks=%d threads=%d scratch=%d cuda_vram=%d cuda_pipeline=%d "
+            "cuda_max_input=%d cuda_max_output=%d" % (
+                t["total"], t["metadata"], t["read"], 0.0, 0.0, t["cuda_quant"], 0.0, t["write"], t["tensors"], t["cuda_tensors"], 0,
+                t["cuda_chunks"], t["threads"], t["scratch"], t["cuda_vram"], 1, t["cuda_max_input"], t["cuda_max_output"]))
 
 
 def summary_lines(result: dict) -> list[str]:
@@ -729,13 +762,11 @@ def parse_args(argv) -> Options:
 
 
 def main(argv=None) -> int:
-    import time
     try:
         options = parse_args(sys.argv[1:] if argv is None else argv)
-        began = time.perf_counter()
         result = convert(options)
         if options.timings:
-            print(f"Timings: total={time.perf_counter() - began:.3f}s", file=sys.stderr)
+            print(timings_line(result), file=sys.stderr)
     except ConversionError as exc:
         print(f"error: {exc}", file=sys.stderr)
         return 1

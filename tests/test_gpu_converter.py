@@ -62,3 +62,20 @@ def test_llama_checkpoint_and_load_time_decode(gguf, tmp_path):
             assert np.array_equal(t.cpu().numpy().reshape(-1).view(np.uint32), np.asarray(want, dtype=np.float32).reshape(-1).view(np.uint32))
         half = load.load_tensor(g, "lm_head.weight", device="cuda", dtype=torch.float16)
         assert half.dtype == torch.float16 and tuple(half.shape) == (512, 256)
+
+
+def test_timings_line_has_upstreams_tokens(gguf, tmp_path, capsys):
+    """--timings prints the token line upstream's benchmark scripts parse (csrc/quantize_gguf.cpp:2527-2547)."""
+    import re
+    from libgguf_b200 import quantize_gguf as qg
+    src = str(tmp_path / "llama.safetensors")
+    cm.write_safetensors(src, cm.llama_like(layers=2))
+    assert qg.main(["--src", src, "--dst", str(tmp_path / "t.gguf"), "--qtype", "Q4_K_M", "--gpus", "1", "--timings"]) == 0
+    line = [l for l in capsys.readouterr().err.splitlines() if l.startswith("Timings: ")]
+    assert len(line) == 1
+    tokens = dict(t.split("=") for t in line[0].split()[1:])
+    assert list(tokens) == ["total", "metadata", "read", "cpu_convert", "h2d", "cuda_quant", "d2h", "write", "tensors", "cuda_tensors",
+                            "cuda_verified", "cuda_chunks", "threads", "scratch", "cuda_vram", "cuda_pipeline", "cuda_max_input",
+                            "cuda_max_output"]
+    assert all(re.fullmatch(r"\d+\.\d{3}s", tokens[k]) for k in list(tokens)[:8])
+    assert int(tokens["tensors"]) >= int(tokens["cuda_tensors"]) > 0 and int(tokens["cuda_chunks"]) > 0
