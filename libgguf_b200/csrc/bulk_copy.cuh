@@ -25,6 +25,11 @@ GGUF_D void bulk_load(void *smem_dst, const void *gmem_src, uint32_t bytes, uint
                  ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
 
+// An arrival that brings no bytes (a thread with nothing to copy, on a barrier that counts every thread).
+GGUF_D void mbarrier_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
 // Waits for the phase with parity `parity` to complete; false when the limit ran out.  A try_wait suspends the
 // thread for a hardware-defined time slice, so the limit is many milliseconds, far beyond any copy.
 constexpr int kBulkWaitLimit = 1 << 18;

@@ -784,6 +784,94 @@ cudaError_t launch_ternary(const float *src, uint8_t *dst, int64_t nblocks, cuda
     return launched != cudaSuccess ? launched : cudaGetLastError();
 }
 
+// Q1_0, upstream q1_0.cpp:16-55: d = (sum of |x| over the block's 128 elements, added in element order) / 128, one
+// bit per element (x >= 0).  The sum is a chain of 128 dependent additions, so a lane owns a whole block: one-warp
+// CTAs walk tiles of 32 blocks; every lane stages its own block (512 bytes) with one bulk asynchronous copy into a
+// row padded to 132 floats (16-byte aligned, conflict-free 16-byte reads), one tile ahead of the one being encoded.
+// Four lanes per block, the sum handed from lane to lane, executed the chain four times over and ran at 81 %.
+constexpr int kQ1Stride = 132;
+__global__ void __launch_bounds__(32) quant_q1_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst, int64_t nblocks) {
+    constexpr int BYTES = 18;
+    __shared__ __align__(128) float xs[2][32 * kQ1Stride];
+    __shared__ __align__(16) uint8_t stage[32 * BYTES + 16];
+    __shared__ __align__(8) uint64_t landed[2];
+    const int lane = threadIdx.x;
+    const int64_t ntiles = (nblocks + 31) / 32;
+    uint8_t *tile = stage + (reinterpret_cast<uintptr_t>(dst) & 15);  // a tile starts a multiple of 16 bytes into dst
+    if (lane == 0) {
+        mbarrier_init(&landed[0], 32);
+        mbarrier_init(&landed[1], 32);
+        fence_async_shared();
+    }
+    __syncwarp();
+    // A lane overwrites the row it read itself during the slot's previous use, hence only the proxy fence.
+    auto prefetch = [&](int64_t t, int slot) {
+        const int64_t b = t * 32 + lane;
+        if (b < nblocks) {
+            fence_async_shared();
+            bulk_load(xs[slot] + lane * kQ1Stride, src + b * 128, 512u, &landed[slot]);
+        } else {
+            mbarrier_arrive(&landed[slot]);
+        }
+    };
+
+    int64_t t = blockIdx.x;
+    grid_dependents_may_launch();
+    grid_dependency_wait();
+    if (t < ntiles) prefetch(t, 0);
+    for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
+        const int64_t tnext = t + gridDim.x;
+        if (tnext < ntiles) prefetch(tnext, (it + 1) & 1);
+        const bool arrived = mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u);
+        if (!__all_sync(kFull, arrived)) {
+            if (lane == 0) atomicAdd(&g_staging_timeouts, 1ull);
+            return;
+        }
+        const float *row = xs[it & 1] + lane * kQ1Stride;
+        float total = 0.f;
+        uint32_t bits[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float4 v = *reinterpret_cast<const float4 *>(row + 32 * w + 4 * k);
+                total += fabsf(v.x); total += fabsf(v.y); total += fabsf(v.z); total += fabsf(v.w);
+                word |= (v.x >= 0.0f ? 1u : 0u) << (4 * k) | (v.y >= 0.0f ? 1u : 0u) << (4 * k + 1) |
+                        (v.z >= 0.0f ? 1u : 0u) << (4 * k + 2) | (v.w >= 0.0f ? 1u : 0u) << (4 * k + 3);
+            }
+            bits[w] = word;
+        }
+        const int64_t first = t * 32;
+        if (first + lane < nblocks) {  // lanes past the end of a short last tile worked on stale rows
+            uint8_t *out = tile + lane * BYTES;
+            st16(out, f32_to_half_bits(total / 128.0f));
+#pragma unroll
+            for (int w = 0; w < 4; ++w) st32(out + 2 + 4 * w, bits[w]);
+        }
+        __syncwarp();
+        const int64_t left = nblocks - first;
+        flush_tile(tile, dst + first * BYTES, (int)(left < 32 ? left : 32) * BYTES, lane, 32);
+        __syncwarp();  // the flush has read the stage before the next tile's blocks are written to it
+    }
+}
+
+cudaError_t launch_q1(const float *src, uint8_t *dst, int64_t nblocks, cudaStream_t stream) {
+    const int64_t ntiles = (nblocks + 31) / 32;
+    if (ntiles <= 0) return cudaSuccess;
+    static const int resident = [] {
+        int dev = 0, sms = 148, per_sm = 6;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_q1_kernel, 32, 0);
+        return sms * (per_sm > 0 ? per_sm : 1);
+    }();
+    const int64_t grid = ntiles < resident ? ntiles : resident;
+    const cudaError_t launched = launch_overlapped(quant_q1_kernel, (unsigned)grid, 32, stream, src, dst, nblocks);
+    count_launch();
+    return launched != cudaSuccess ? launched : cudaGetLastError();
+}
+
 // Plain storage types: fp32 copy, fp16 and bf16 conversion with upstream's rounding and NaN
 // handling (upstream libgguf_storage.cpp:105-125).  kind: 0 copy, 1 fp16, 2 bf16.
 template <int KIND>
@@ -856,7 +944,7 @@ cudaError_t launch_quantize_simple(int type, const float *src, void *dst, int64_
         case GGML_TYPE_Q5_1: return launch32<Simple::Q5_1>(src, dst, nelems, nullptr, stream);
         case GGML_TYPE_MXFP4: return launch32<Simple::MXFP4>(src, dst, nelems, mx_steps, stream);
         case GGML_TYPE_NVFP4: return launch32<Simple::NVFP4>(src, dst, nelems, nullptr, stream);
-        case GGML_TYPE_Q1_0: return launch32<Simple::Q1_0>(src, dst, nelems, nullptr, stream);
+        case GGML_TYPE_Q1_0: return launch_q1(src, out, nelems / 128, stream);
         case GGML_TYPE_TQ1_0: return launch_ternary<true>(src, out, nelems / 256, stream);
         case GGML_TYPE_TQ2_0: return launch_ternary<false>(src, out, nelems / 256, stream);
         default: return cudaErrorInvalidValue;
