@@ -179,7 +179,7 @@ __global__ void selftest_fp4_kernel(float e, int mode, int ebyte, unsigned long 
     if (fell) atomicAdd(fallbacks, fell);
 }
 
-enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4, NVFP4, Q1_0 };
+enum class Simple { Q8_0, Q4_0, Q4_1, Q5_0, Q5_1, MXFP4, NVFP4 };
 
 template <Simple K> struct SimpleGeom;
 template <> struct SimpleGeom<Simple::Q8_0> { static constexpr int BYTES = 34; };   // bytes per 32 elements
@@ -189,9 +189,7 @@ template <> struct SimpleGeom<Simple::Q5_0> { static constexpr int BYTES = 22; }
 template <> struct SimpleGeom<Simple::Q5_1> { static constexpr int BYTES = 24; };
 template <> struct SimpleGeom<Simple::MXFP4> { static constexpr int BYTES = 17; };
 template <> struct SimpleGeom<Simple::NVFP4> { static constexpr int BYTES = 18; };  // half of a 64-element block
-// Q1_0: a 128-element block (18 bytes) is four runs; BYTES is not used for it
-template <> struct SimpleGeom<Simple::Q1_0> { static constexpr int BYTES = 0; };
-template <Simple K> constexpr int kBytesPer4Runs = K == Simple::Q1_0 ? 18 : 4 * SimpleGeom<K>::BYTES;
+template <Simple K> constexpr int kBytesPer4Runs = 4 * SimpleGeom<K>::BYTES;
 
 GGUF_D void st16(uint8_t *p, uint16_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); }
 GGUF_D void st32(uint8_t *p, uint32_t v) { p[0] = (uint8_t)v; p[1] = (uint8_t)(v >> 8); p[2] = (uint8_t)(v >> 16); p[3] = (uint8_t)(v >> 24); }
@@ -423,7 +421,7 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
     const int64_t r0 = t * kBlockThreads;
     const int nr = (int)(nruns - r0 < kBlockThreads ? nruns - r0 : kBlockThreads);
     uint8_t *gdst = dst + r0 / 4 * BYTES4;   // r0 is a multiple of 128
-    if (K == Simple::Q1_0 || threadIdx.x < nr) {
+    if (threadIdx.x < nr) {
         const float *xrow = xin + threadIdx.x * kRowStride;
         float x[32];
 #pragma unroll
@@ -432,36 +430,7 @@ __global__ void __launch_bounds__(kBlockThreads) quant32_kernel(const float *__r
             x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
         }
         uint8_t *out = tile + threadIdx.x * BYTES;
-        if constexpr (K == Simple::Q1_0) {
-            // upstream q1_0.cpp:16-55: d = (sum of |x| over the 128 elements, added in element order) / 128, one
-            // bit per element (x >= 0).  The block's four runs sit in four neighbouring lanes; the sum is
-            // handed from lane to lane, every lane adding its 32 magnitudes to what it receives.
-            // Rows past the end of a short last tile hold stale data and are computed but not stored
-            // (all 32 lanes take part in the shuffles).
-            const int lane = threadIdx.x & 31, part = threadIdx.x & 3;
-            float total = 0.f;
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                float t = __shfl_sync(kFull, total, (lane & ~3) | ((p + 3) & 3));
-                if (p == 0) t = 0.f;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) t += fabsf(x[j]);
-                if (part == p) total = t;
-            }
-            uint32_t bits = 0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) bits |= (x[j] >= 0.0f ? 1u : 0u) << j;
-            if (threadIdx.x < nr) {
-                uint8_t *blk = tile + (threadIdx.x >> 2) * 18;
-                if (even) {
-                    reinterpret_cast<uint16_t *>(blk + 2 + 4 * part)[0] = (uint16_t)bits;
-                    reinterpret_cast<uint16_t *>(blk + 2 + 4 * part)[1] = (uint16_t)(bits >> 16);
-                } else {
-                    st32(blk + 2 + 4 * part, bits);
-                }
-                if (part == 3) st16(blk, f32_to_half_bits(total / 128.0f));
-            }
-        } else if constexpr (K == Simple::Q8_0) {
+        if constexpr (K == Simple::Q8_0) {
             const float amax = amax_nan<32>(x);
             const float d = amax / 127.0f;
             const float id = d ? 1.0f / d : 0.0f;
