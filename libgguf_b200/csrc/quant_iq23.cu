@@ -1,14 +1,22 @@
 // Lattice quantizers IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S.
 //
-// One thread owns one block of 32 (16 for IQ2_XS / IQ2_S) elements and keeps the magnitudes, the
-// importance weights and their square roots in registers; the 8 or 16 threads of a super-block
-// sit next to each other in a warp.  Per block the upstream algorithm is run literally: sign
-// extraction (with the even-parity fix where the format stores 7 sign bits), a loop over
-// candidate scales in which every group of 8 (or 4) magnitudes is rounded to the lattice and,
-// when the rounded point is not a codebook entry, replaced by the best of its precomputed
+// One lane owns one block of 32 (16 for IQ2_XS / IQ2_S) elements; the 8 or 16 lanes of a
+// super-block sit next to each other in a warp.  Per block the upstream algorithm is run
+// literally: sign extraction (with the even-parity fix where the format stores 7 sign bits), a
+// loop over candidate scales in which every group of 8 (or 4) magnitudes is rounded to the lattice
+// and, when the rounded point is not a codebook entry, replaced by the best of its precomputed
 // neighbours, the accept/reject chain on (sumqx, sumq2), the final re-projection, and the 4-bit
-// block scale against the super-block maximum.  The codebook is staged in shared
-// memory as floats (<= 32 KB) once per CTA; the lattice map and neighbour lists stay in global memory (L2 resident).
+// block scale against the super-block maximum.
+//
+// The neighbour scans are nine tenths of the arithmetic and their lengths differ from group to
+// group (1 to about 300 entries), so a lane that scanned its own lists left two thirds of the
+// warp idle.  Here the warp works in rounds: every lane rounds its groups for one candidate and
+// queues the scans that came up, the warp lays the queued lists end to end and every lane
+// evaluates an equal stretch of that sequence (whatever lists it crosses), and the owners read the
+// winners back and run the accept/reject chain.  The codebook is staged in shared memory as
+// bfloat16 pairs (exact for its small odd integers), every lane's magnitudes and root weights in
+// padded rows; the lattice map and the neighbour lists stay in global memory (L1/L2 resident) and
+// are fetched a few steps ahead of their use.
 // upstream: csrc/quant/iq2_xxs.cpp:4-224, iq2_xs.cpp:4-230, iq2_s.cpp:4-218, iq3_xxs.cpp:4-273,
 // iq3_s.cpp:5-233, csrc/common/libgguf_iq_tables.cpp:434-462 and :683-711.
 #include <float.h>
@@ -22,31 +30,30 @@ namespace gguf {
 namespace {
 
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kThreads = 64;
 
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
-    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS;
+    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 64, CTAS = 6;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = true;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_XS> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_S> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_XXS> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6;
     static constexpr bool PARITY = true, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_S> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 0.f;  // upstream tests `!max`
 };
@@ -142,52 +149,178 @@ GGUF_D float qp_quants_reg(int nmax, const float (&x)[N], int (&L)[N], const flo
     return suml2 > 0.0f ? sumlx / suml2 : 0.0f;
 }
 
-// Best of the precomputed neighbours of an off-codebook lattice point: first strict minimum of
-// sum_i w[i] * (scale*q[i] - x[i])^2 with the terms added in coordinate order.  Writes the
-// winner's levels to L[0..GD) and returns its codebook index.
+// Codebook entry g of the staged codebook: coordinates are small odd integers, kept as bfloat16 pairs (exact), so an
+// entry is one 16-byte (8 coordinates) or 8-byte (4 coordinates) read and a shift or mask per coordinate.  As floats
+// an entry of eight took two 16-byte reads that used half of the banks, and the gathers of 32 lanes at 32 random
+// entries kept the shared-memory pipe busier than the arithmetic.
 template <int GD>
-GGUF_D int best_neighbour(const uint16_t *__restrict__ nb, const float *gridf, const float *xv, const float *wv, float scale,
-                          int *L) {
-    const int n = __ldg(nb);
+GGUF_D void grid_entry(const uint32_t *gridh, int g, float (&q)[GD]) {
+    uint32_t w[GD / 2];
+    if constexpr (GD == 8) {
+        const uint4 t = *reinterpret_cast<const uint4 *>(gridh + g * 4);
+        w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+    } else {
+        const uint2 t = *reinterpret_cast<const uint2 *>(gridh + g * 2);
+        w[0] = t.x; w[1] = t.y;
+    }
+#pragma unroll
+    for (int i = 0; i < GD / 2; ++i) {
+        q[2 * i] = __uint_as_float(w[i] << 16);
+        q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+}
+
+// Weighted squared distance of codebook entry g from the group, terms added in coordinate order.
+template <int GD>
+GGUF_D float neighbour_d2(const uint32_t *gridh, int g, float scale, const float (&xv)[GD], const float (&wv)[GD]) {
+    float q[GD];
+    grid_entry<GD>(gridh, g, q);
+    float d2 = 0;
+#pragma unroll
+    for (int i = 0; i < GD; ++i) {
+        const float diff = scale * q[i] - xv[i];
+        d2 += wv[i] * diff * diff;
+    }
+    return d2;
+}
+
+template <int N>
+GGUF_D void load_staged(const float *p, float (&x)[N]) {  // shared memory, 16-byte aligned
+#pragma unroll
+    for (int k = 0; k < N / 4; ++k) {
+        const float4 v = reinterpret_cast<const float4 *>(p)[k];
+        x[4 * k] = v.x; x[4 * k + 1] = v.y; x[4 * k + 2] = v.z; x[4 * k + 3] = v.w;
+    }
+}
+
+// One neighbour scan a warp has to run: which list, which group of which lane's block, at which scale.
+struct ScanTask {
+    uint32_t list;   // offset of the list's count in the neighbour array
+    uint32_t xoff;   // float offset of the group in the warp's staged magnitudes / weights
+    float scale;
+    uint32_t n;      // list length
+};
+
+constexpr unsigned long long kNoWinner = ~0ull;
+
+// The warp's pending scans, evaluated with the work spread evenly: the T lists are laid end to end
+// (E entries, `first[t]` = position of list t's first entry) and every lane takes a contiguous
+// stretch of E/32 entries, whatever lists it crosses.  A list's winner is the first strict minimum
+// in list order, i.e. the minimum of (distance bits, position) as one 64-bit key; a lane that saw
+// a whole list stores its key, lanes that share a list combine theirs with a shared-memory
+// atomic minimum.  Distances are sums of non-negative terms, so their bit patterns order like
+// the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
+template <int GD, int TMAX>
+GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
+                          const float *xs, const float *ws, const uint32_t *gridh, const uint16_t *__restrict__ lists) {
+    constexpr int AHEAD = 4;  // list entries are fetched this many steps early, across list boundaries
+    const uint32_t share = (E + 31) >> 5;
+    uint32_t e = umin((uint32_t)lane * share, E);
+    const uint32_t end = umin(e + share, E);
+    if (e >= end) return;
+    int t = 0;
+#pragma unroll
+    for (int step = TMAX / 2; step; step >>= 1) {
+        const int c = t + step;
+        if (c < T && first[c] <= e) t = c;
+    }
+    ScanTask tk = tasks[t];
+    float xv[GD], wv[GD];
+    load_staged<GD>(xs + tk.xoff, xv);
+    load_staged<GD>(ws + tk.xoff, wv);
+    uint32_t j = e - first[t];
+    bool whole = j == 0;
     float best_d2 = FLT_MAX;
-    int best = -1;
-    int g_next = __ldg(nb + 1);  // the index of the next entry is fetched while the current one is evaluated
-    for (int j = 1; j <= n; ++j) {
-        const int g = g_next;
-        g_next = __ldg(nb + (j < n ? j + 1 : j));
-        float q[GD];
-#pragma unroll
-        for (int v = 0; v < GD / 4; ++v) {
-            const float4 t = *reinterpret_cast<const float4 *>(gridf + g * GD + 4 * v);
-            q[4 * v] = t.x; q[4 * v + 1] = t.y; q[4 * v + 2] = t.z; q[4 * v + 3] = t.w;
+    uint32_t best_at = 0xFFFFFFFFu;
+    // Entries are taken two at a time (two independent sums in flight); where a list or the lane's stretch ends on
+    // an odd entry the second one repeats the first and is ignored.  The fetch cursor forms the same pairs AHEAD
+    // steps in front of the evaluation cursor and hands them over as (first | second << 12 | pair << 31).
+    int ft = t;
+    uint32_t fj = j, fn = tk.n, fe = e;
+    const uint16_t *fnb = lists + tk.list + 1;
+    uint32_t ring[AHEAD];
+    auto fetch = [&]() -> uint32_t {
+        uint32_t rec = 0;
+        if (fe < end) {
+            const bool two = fj + 1 < fn && fe + 1 < end;
+            const uint32_t g0 = __ldg(fnb + fj);
+            const uint32_t g1 = __ldg(fnb + fj + (two ? 1 : 0));
+            rec = g0 | (g1 << 12) | (two ? 0x80000000u : 0u);
+            const uint32_t adv = two ? 2u : 1u;
+            fe += adv;
+            fj += adv;
+            if (fj == fn && fe < end) {
+                ++ft;
+                fj = 0;
+                fn = tasks[ft].n;
+                fnb = lists + tasks[ft].list + 1;
+            }
         }
-        float d2 = 0;
+        return rec;
+    };
 #pragma unroll
-        for (int i = 0; i < GD; ++i) {
-            const float diff = scale * q[i] - xv[i];
-            d2 += wv[i] * diff * diff;
+    for (int d = 0; d < AHEAD; ++d) ring[d] = fetch();
+    while (e < end) {
+        {
+            {
+                const uint32_t rec = ring[0];
+#pragma unroll
+                for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
+                ring[AHEAD - 1] = fetch();
+                const uint32_t g0 = rec & 0xFFFu, g1 = (rec >> 12) & 0xFFFu, two = rec >> 31;
+                const float d2a = neighbour_d2<GD>(gridh, (int)g0, tk.scale, xv, wv);
+                const float d2b = neighbour_d2<GD>(gridh, (int)g1, tk.scale, xv, wv);
+                if (d2a < best_d2) { best_d2 = d2a; best_at = (j << 16) | g0; }
+                if (two && d2b < best_d2) { best_d2 = d2b; best_at = ((j + 1) << 16) | g1; }
+                e += 1 + two;
+                j += 1 + two;
+                if (j == tk.n) {
+                    if (best_d2 < FLT_MAX) {
+                        const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
+                        if (whole) winner[t] = key;
+                        else atomicMin(winner + t, key);
+                    }
+                    ++t;
+                    j = 0;
+                    whole = true;
+                    best_d2 = FLT_MAX;
+                    best_at = 0xFFFFFFFFu;
+                    if (e < end) {
+                        tk = tasks[t];
+                        load_staged<GD>(xs + tk.xoff, xv);
+                        load_staged<GD>(ws + tk.xoff, wv);
+                    }
+                }
+            }
         }
-        if (d2 < best_d2) { best_d2 = d2; best = g; }
     }
-#pragma unroll
-    for (int v = 0; v < GD / 4; ++v) {
-        const float4 t = *reinterpret_cast<const float4 *>(gridf + best * GD + 4 * v);
-        // coordinates are 2*level + 1
-        L[4 * v] = ((int)t.x - 1) >> 1; L[4 * v + 1] = ((int)t.y - 1) >> 1; L[4 * v + 2] = ((int)t.z - 1) >> 1; L[4 * v + 3] = ((int)t.w - 1) >> 1;
-    }
-    return best;
+    if (j != 0 && best_d2 < FLT_MAX)
+        atomicMin(winner + t, ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at);
 }
 
 template <int TYPE>
-__global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__restrict__ src, const float *__restrict__ qw,
+__global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) quant_iq23_kernel(const float *__restrict__ src, const float *__restrict__ qw,
                                                              uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
                                                              IqSearchTable tab) {
     using T = Traits<TYPE>;
     constexpr int BS = T::BS, GD = T::GD, NG = BS / GD, NS = BS / 8, W = 256 / BS;  // W lanes per super-block
     // the codebook's coordinates as floats: no conversion in the neighbour scans, one or two 16-byte reads per entry
-    extern __shared__ __align__(16) float gridf[];
-    for (int i = threadIdx.x; i < tab.grid_size * GD; i += kThreads) gridf[i] = (float)__ldg(tab.grid + i);
+    constexpr int kThreads = T::THREADS;
+    extern __shared__ __align__(16) uint32_t gridh[];
+    for (int i = threadIdx.x; i < tab.grid_size * GD / 2; i += kThreads) {
+        const uint32_t lo = __float_as_uint((float)__ldg(tab.grid + 2 * i)), hi = __float_as_uint((float)__ldg(tab.grid + 2 * i + 1));
+        gridh[i] = (lo >> 16) | (hi & 0xFFFF0000u);
+    }
     __syncthreads();
+    // per warp: every lane's magnitudes and root weights in rows padded by four floats, the pending
+    // scans of one candidate, where each list starts in the concatenation, and each scan's winner
+    constexpr int XP = BS + 4, TMAX = 32 * NG;
+    constexpr int kWarpFloats = 2 * 32 * XP + TMAX * 4 + TMAX + TMAX * 2;
+    float *const wbase = reinterpret_cast<float *>(gridh) + tab.grid_size * (GD / 2) + (threadIdx.x >> 5) * kWarpFloats;
+    float *const xs = wbase, *const ws = wbase + 32 * XP;
+    ScanTask *const tasks = reinterpret_cast<ScanTask *>(wbase + 2 * 32 * XP);
+    unsigned long long *const winner = reinterpret_cast<unsigned long long *>(wbase + 2 * 32 * XP + TMAX * 4);
+    uint32_t *const first = reinterpret_cast<uint32_t *>(wbase + 2 * 32 * XP + TMAX * 4 + TMAX * 2);
 
     const int lane = threadIdx.x & 31, j = lane & (W - 1), gbase = lane & ~(W - 1);
     int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x;
@@ -249,6 +382,14 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
     float max = xval[0];
 #pragma unroll
     for (int i = 1; i < BS; ++i) max = max > xval[i] ? max : xval[i];
+    {
+#pragma unroll
+        for (int v = 0; v < BS / 4; ++v) {
+            *reinterpret_cast<float4 *>(xs + (threadIdx.x & 31) * XP + 4 * v) = make_float4(xval[4 * v], xval[4 * v + 1], xval[4 * v + 2], xval[4 * v + 3]);
+            *reinterpret_cast<float4 *>(ws + (threadIdx.x & 31) * XP + 4 * v) = make_float4(waux[4 * v], waux[4 * v + 1], waux[4 * v + 2], waux[4 * v + 3]);
+        }
+        __syncwarp();
+    }
 
     uint32_t L[BS / 4];
 #pragma unroll
@@ -272,105 +413,166 @@ __global__ void __launch_bounds__(kThreads) quant_iq23_kernel(const float *__res
 #pragma unroll
     for (int k = 0; k < NG; ++k) gidx[k] = 0;
 
-    if (!skipped) {
+    {
+        // Every lane rounds its groups for one candidate, the warp runs all the scans that came up with the
+        // work spread evenly over the lanes, then every lane adds up its candidate and accepts or rejects it.
+        const uint16_t *lists = tab.neighbours;
+        // the magnitudes are read back from the lane's staged row from here on, which frees their registers
+        const float *const xrow = xs + lane * XP;
+        // rounds the groups selected by `want` at inverse scale id, queues the scans, runs them; returns the
+        // codebook entry of each selected group in g[] and the mask of groups that needed a scan
+        auto project = [&](uint32_t want, float id, float at_scale, int (&g)[NG]) -> uint32_t {
+            uint32_t off = 0, total_n = 0;
+            uint32_t nk[NG];
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                g[k] = 0;
+                nk[k] = 0;
+                if ((want >> k) & 1) {
+                    uint32_t u = 0;
+                    float xk[GD];
+                    load_staged<GD>(xrow + GD * k, xk);
+#pragma unroll
+                    for (int i = 0; i < GD; ++i) {
+                        const int l = imax(0, imin(T::KMAXQ - 1, nearest_int(0.5f * (id * xk[i] - 1))));
+                        u |= (uint32_t)l << (T::BITS * i);
+                    }
+                    g[k] = __ldg(tab.map + u);
+                    if (g[k] < 0) off |= 1u << k;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                if ((off >> k) & 1) {
+                    nk[k] = __ldg(lists + (-g[k] - 1));
+                    total_n += nk[k];
+                }
+            }
+            // slots and positions: one inclusive scan over (entries << 10 | scans)
+            const uint32_t mine = (total_n << 10) | (uint32_t)__popc(off);
+            uint32_t incl = mine;
+#pragma unroll
+            for (int dlt = 1; dlt < 32; dlt <<= 1) {
+                const uint32_t o = __shfl_up_sync(kFull, incl, dlt);
+                if (lane >= dlt) incl += o;
+            }
+            const uint32_t all = __shfl_sync(kFull, incl, 31);
+            uint32_t slot = (incl - mine) & 1023u, pos = (incl - mine) >> 10;
+            const uint32_t slot0 = slot;
+            __syncwarp();  // the previous round's winners have been read
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                if ((off >> k) & 1) {
+                    ScanTask tk;
+                    tk.list = (uint32_t)(-g[k] - 1);
+                    tk.xoff = (uint32_t)(lane * XP + GD * k);
+                    tk.scale = at_scale;
+                    tk.n = nk[k];
+                    tasks[slot] = tk;
+                    first[slot] = pos;
+                    winner[slot] = kNoWinner;
+                    ++slot;
+                    pos += nk[k];
+                }
+            }
+            __syncwarp();
+            if (all >> 10) balanced_scan<GD, TMAX>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, lists);
+            __syncwarp();
+            slot = slot0;
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                if ((off >> k) & 1) {
+                    const uint32_t w = (uint32_t)winner[slot++] & 0xFFFFu;
+                    g[k] = w < (uint32_t)tab.grid_size ? (int)w : 0;
+                }
+            }
+            return off;
+        };
+        constexpr uint32_t kAllGroups = NG == 32 ? 0xFFFFFFFFu : ((1u << NG) - 1);
         float best = 0;
-        if (!T::QP_INIT) scale = max / (2 * T::KMAXQ - 1);
-        uint32_t on_grid = TYPE == GGML_TYPE_IQ3_S ? 0u : 0xFFFFFFFFu;  // bit k: group k of the accepted candidate was a codebook point
-        // candidate by candidate, a neighbour scan wherever the rounding leaves the codebook
+        if (!T::QP_INIT && !skipped) scale = max / (2 * T::KMAXQ - 1);
+        uint32_t on_grid = TYPE == GGML_TYPE_IQ3_S ? 0u : 0xFFFFFFFFu;
         for (int is = -T::IS_MAX; is <= T::IS_MAX; ++is) {
             const float id = ((float)(2 * T::KMAXQ - 1) + (float)is * T::STEP) / eff_max;
             const float this_scale = 1 / id;
-            uint32_t Laux[BS / 4];
-            uint32_t on_aux = 0;
-            // the block's sums run over the elements in order, i.e. group by group: each group adds its terms as
-            // soon as its levels are known
-            float sumqx = 0, sumq2 = 0;
+            int g[NG];
+            const uint32_t off = project(skipped ? 0u : kAllGroups, id, this_scale, g);
+            if (!skipped) {
+                float sumqx = 0, sumq2 = 0;
 #pragma unroll
-            for (int k = 0; k < NG; ++k) {
-                uint32_t u = 0;
-                int lk[GD];
+                for (int k = 0; k < NG; ++k) {
+                    float q[GD], xk[GD];
+                    grid_entry<GD>(gridh, g[k], q);
+                    load_staged<GD>(xrow + GD * k, xk);
 #pragma unroll
-                for (int i = 0; i < GD; ++i) {
-                    const int l = nearest_int(0.5f * (id * xval[GD * k + i] - 1));
-                    lk[i] = imax(0, imin(T::KMAXQ - 1, l));
-                    u |= (uint32_t)lk[i] << (T::BITS * i);
+                    for (int i = 0; i < GD; ++i) {
+                        const float w = weight[GD * k + i];
+                        sumqx += w * xk[i] * q[i];
+                        sumq2 += w * q[i] * q[i];
+                    }
                 }
-                const int m = __ldg(tab.map + u);
-                if (m < 0) best_neighbour<GD>(tab.neighbours + (-m - 1), gridf, xval + GD * k, waux + GD * k, this_scale, lk);
-                else on_aux |= 1u << k;
+                if (sumq2 > 0 && sumqx * sumqx > best * sumq2) {
+                    scale = sumqx / sumq2;
+                    best = scale * sumqx;
 #pragma unroll
-                for (int i = 0; i < GD; ++i) {
-                    const float w = weight[GD * k + i];
-                    const float q = (float)(2 * lk[i] + 1);
-                    sumqx += w * xval[GD * k + i] * q;
+                    for (int k = 0; k < NG; ++k) {
+                        float q[GD];
+                        grid_entry<GD>(gridh, g[k], q);
+#pragma unroll
+                        for (int v = 0; v < GD / 4; ++v)
+                            L[(GD * k) / 4 + v] = (uint32_t)(((int)q[4 * v] - 1) >> 1) | ((uint32_t)(((int)q[4 * v + 1] - 1) >> 1) << 8) |
+                                                  ((uint32_t)(((int)q[4 * v + 2] - 1) >> 1) << 16) | ((uint32_t)(((int)q[4 * v + 3] - 1) >> 1) << 24);
+                    }
+                    on_grid = ~off;
+                }
+            }
+        }
+        // re-projection at the accepted scale: all groups (IQ2_XXS, IQ3_S) or those the accepted candidate scanned
+        bool reproject = false;
+        if (!skipped) {
+            if (TYPE == GGML_TYPE_IQ2_XXS) reproject = scale > 0;
+            else reproject = (on_grid & kAllGroups) != kAllGroups && scale > 0;
+        }
+        {
+            constexpr bool all_groups = TYPE == GGML_TYPE_IQ2_XXS || TYPE == GGML_TYPE_IQ3_S;
+            const uint32_t want = reproject ? (all_groups ? kAllGroups : (~on_grid & kAllGroups)) : 0u;
+            int g[NG];
+            project(want, reproject ? 1 / scale : 0.f, scale, g);
+            if (reproject) {
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    if ((want >> k) & 1) {
+                        float q[GD];
+                        grid_entry<GD>(gridh, g[k], q);
+#pragma unroll
+                        for (int i = 0; i < GD; ++i) lset(L, GD * k + i, ((int)q[i] - 1) >> 1);
+                    }
+                }
+                float sumqx = 0, sumq2 = 0;
+#pragma unroll
+                for (int i = 0; i < BS; ++i) {
+                    const float w = weight[i];
+                    const float q = (float)(2 * lget(L, i) + 1);
+                    sumqx += w * xrow[i] * q;
                     sumq2 += w * q * q;
                 }
-#pragma unroll
-                for (int v = 0; v < GD / 4; ++v)
-                    Laux[(GD * k) / 4 + v] = (uint32_t)lk[4 * v] | ((uint32_t)lk[4 * v + 1] << 8) | ((uint32_t)lk[4 * v + 2] << 16) | ((uint32_t)lk[4 * v + 3] << 24);
-            }
-            if (sumq2 > 0 && sumqx * sumqx > best * sumq2) {
-                scale = sumqx / sumq2;
-                best = scale * sumqx;
-#pragma unroll
-                for (int i = 0; i < BS / 4; ++i) L[i] = Laux[i];
-                on_grid = on_aux;
+                if (sumq2 > 0) scale = sumqx / sumq2;
             }
         }
-        // re-projection at the accepted scale
-        bool reproject;
-        if (TYPE == GGML_TYPE_IQ2_XXS) reproject = scale > 0;
-        else reproject = (on_grid & ((NG == 32) ? 0xFFFFFFFFu : ((1u << NG) - 1))) != ((NG == 32) ? 0xFFFFFFFFu : ((1u << NG) - 1)) && scale > 0;
-        if (reproject) {
-            const float id = 1 / scale;
+        if (!skipped) {
+            if (scale < 0) {
+                scale = -scale;
+#pragma unroll
+                for (int k = 0; k < NS; ++k) signs[k] = T::PARITY ? (~signs[k]) & 127 : (~signs[k]) & 0xFF;
+            }
 #pragma unroll
             for (int k = 0; k < NG; ++k) {
-                const bool all_groups = TYPE == GGML_TYPE_IQ2_XXS || TYPE == GGML_TYPE_IQ3_S;
-                if (!all_groups && ((on_grid >> k) & 1)) continue;
                 uint32_t u = 0;
-                int Lr[GD];
 #pragma unroll
-                for (int i = 0; i < GD; ++i) {
-                    const int l = imax(0, imin(T::KMAXQ - 1, nearest_int(0.5f * (id * xval[GD * k + i] - 1))));
-                    u |= (uint32_t)l << (T::BITS * i);
-                    Lr[i] = l;
-                }
+                for (int i = 0; i < GD; ++i) u |= (uint32_t)lget(L, GD * k + i) << (T::BITS * i);
                 const int m = __ldg(tab.map + u);
-                if (TYPE == GGML_TYPE_IQ2_XS || TYPE == GGML_TYPE_IQ2_S) {
-                    // levels become the rounding, or the best neighbour when the rounding is off the codebook
-                    if (m < 0) best_neighbour<GD>(tab.neighbours + (-m - 1), gridf, xval + GD * k, waux + GD * k, scale, Lr);
-#pragma unroll
-                    for (int i = 0; i < GD; ++i) lset(L, GD * k + i, Lr[i]);
-                } else {
-                    int g = m;
-                    if (m < 0) g = best_neighbour<GD>(tab.neighbours + (-m - 1), gridf, xval + GD * k, waux + GD * k, scale, Lr);
-#pragma unroll
-                    for (int i = 0; i < GD; ++i) lset(L, GD * k + i, ((int)gridf[g * GD + i] - 1) >> 1);
-                }
+                gidx[k] = m < 0 ? 0 : m;
             }
-            float sumqx = 0, sumq2 = 0;
-#pragma unroll
-            for (int i = 0; i < BS; ++i) {
-                const float w = weight[i];
-                const float q = (float)(2 * lget(L, i) + 1);
-                sumqx += w * xval[i] * q;
-                sumq2 += w * q * q;
-            }
-            if (sumq2 > 0) scale = sumqx / sumq2;
-        }
-        if (scale < 0) {
-            scale = -scale;
-            // upstream flips the first four sign bytes (all of them for the 16-element formats)
-#pragma unroll
-            for (int k = 0; k < NS; ++k) signs[k] = T::PARITY ? (~signs[k]) & 127 : (~signs[k]) & 0xFF;
-        }
-#pragma unroll
-        for (int k = 0; k < NG; ++k) {
-            uint32_t u = 0;
-#pragma unroll
-            for (int i = 0; i < GD; ++i) u |= (uint32_t)lget(L, GD * k + i) << (T::BITS * i);
-            const int m = __ldg(tab.map + u);
-            gidx[k] = m < 0 ? 0 : m;  // upstream aborts here; every path above ends on a codebook point
         }
     }
 
@@ -462,9 +664,12 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
     if (!tab.grid) return cudaErrorInvalidValue;
     const int64_t nblocks = nelems / T::BS;
     if (nblocks <= 0) return cudaSuccess;
-    const size_t smem = (size_t)tab.grid_size * T::GD * sizeof(float);  // at most 32 KB
+    constexpr int kThreads = T::THREADS, NG = T::BS / T::GD, XP = T::BS + 4, TMAX = 32 * NG;
     const int64_t grid = (nblocks + kThreads - 1) / kThreads;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
+    const size_t smem = ((size_t)tab.grid_size * T::GD / 2 + (kThreads / 32) * (2 * 32 * XP + TMAX * 7)) * sizeof(float);
+    static const cudaError_t attr = cudaFuncSetAttribute(quant_iq23_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    if (attr != cudaSuccess) return attr;
     quant_iq23_kernel<TYPE><<<(unsigned)grid, kThreads, smem, stream>>>(src, qw, static_cast<uint8_t *>(dst), nblocks, n_per_row, tab);
     count_launch();
     return cudaGetLastError();
