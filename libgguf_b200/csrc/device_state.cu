@@ -101,7 +101,18 @@ const DeviceState *device_state_for(int type, int dev) {
         t.grid = upload(slot, h.grid);
         t.map = upload(slot, h.map);
         t.neighbours = upload(slot, h.neighbours);
-        if (!t.grid || !t.map || !t.neighbours) return nullptr;
+        {   // one load then tells a scan where its list is and how long (offsets < 2^21, counts < 2^9 for every codebook)
+            std::vector<int32_t> packed(h.map.size());
+            for (size_t i = 0; i < h.map.size(); ++i) {
+                const int32_t m = h.map[i];
+                if (m >= 0) { packed[i] = m; continue; }
+                const uint32_t off = (uint32_t)(-m - 1), n = h.neighbours[off];
+                if (off >= (1u << 21) || n >= (1u << 9)) return nullptr;
+                packed[i] = -(int32_t)(((off << 9) | n) + 1);
+            }
+            t.map_n = upload(slot, packed);
+        }
+        if (!t.grid || !t.map || !t.neighbours || !t.map_n) return nullptr;
         t.grid_size = h.grid_size;
         t.dims = h.dims;
         t.map_size = (int)h.map.size();

@@ -16,6 +16,7 @@ struct IqSearchTable {
     const uint8_t *grid = nullptr;         // grid_size x dims bytes, coordinate value 2*code+1
     const int32_t *map = nullptr;          // lattice index -> grid index (>= 0) or -(offset+1) into neighbours
     const uint16_t *neighbours = nullptr;  // [count, idx0, idx1, ...] runs
+    const int32_t *map_n = nullptr;        // as map, the list's count folded in: -(((offset << 9) | count) + 1)
     int grid_size = 0;
     int dims = 0;
     int map_size = 0;

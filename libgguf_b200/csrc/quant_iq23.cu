@@ -419,15 +419,12 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
         const uint16_t *lists = tab.neighbours;
         // the magnitudes are read back from the lane's staged row from here on, which frees their registers
         const float *const xrow = xs + lane * XP;
-        // rounds the groups selected by `want` at inverse scale id, queues the scans, runs them; returns the
-        // codebook entry of each selected group in g[] and the mask of groups that needed a scan
-        auto project = [&](uint32_t want, float id, float at_scale, int (&g)[NG]) -> uint32_t {
-            uint32_t off = 0, total_n = 0;
-            uint32_t nk[NG];
+        // rounds the groups selected by `want` at inverse scale id and looks the lattice points up: a codebook entry
+        // (>= 0) or, negative, where the point's neighbour list is and how long
+        auto lookup = [&](uint32_t want, float id, int (&g)[NG]) {
 #pragma unroll
             for (int k = 0; k < NG; ++k) {
                 g[k] = 0;
-                nk[k] = 0;
                 if ((want >> k) & 1) {
                     uint32_t u = 0;
                     float xk[GD];
@@ -437,14 +434,23 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                         const int l = imax(0, imin(T::KMAXQ - 1, nearest_int(0.5f * (id * xk[i] - 1))));
                         u |= (uint32_t)l << (T::BITS * i);
                     }
-                    g[k] = __ldg(tab.map + u);
-                    if (g[k] < 0) off |= 1u << k;
+                    g[k] = __ldg(tab.map_n + u);
                 }
             }
+        };
+        // queues the scans of the looked-up groups and runs them; g[] becomes the codebook entry of every group;
+        // returns the mask of groups that needed a scan
+        auto project = [&](float at_scale, int (&g)[NG]) -> uint32_t {
+            uint32_t off = 0, total_n = 0;
+            uint32_t nk[NG];
 #pragma unroll
             for (int k = 0; k < NG; ++k) {
-                if ((off >> k) & 1) {
-                    nk[k] = __ldg(lists + (-g[k] - 1));
+                nk[k] = 0;
+                if (g[k] < 0) {
+                    off |= 1u << k;
+                    const uint32_t v = (uint32_t)(-g[k] - 1);
+                    nk[k] = v & 511u;
+                    g[k] = (int)(v >> 9);  // the list's offset until the winner replaces it
                     total_n += nk[k];
                 }
             }
@@ -464,7 +470,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
             for (int k = 0; k < NG; ++k) {
                 if ((off >> k) & 1) {
                     ScanTask tk;
-                    tk.list = (uint32_t)(-g[k] - 1);
+                    tk.list = (uint32_t)g[k];
                     tk.xoff = (uint32_t)(lane * XP + GD * k);
                     tk.scale = at_scale;
                     tk.n = nk[k];
@@ -492,11 +498,17 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
         float best = 0;
         if (!T::QP_INIT && !skipped) scale = max / (2 * T::KMAXQ - 1);
         uint32_t on_grid = TYPE == GGML_TYPE_IQ3_S ? 0u : 0xFFFFFFFFu;
+        // the look-ups of candidate is + 1 are issued before the scans of candidate is run
+        int g_ahead[NG];
+        lookup(skipped ? 0u : kAllGroups, ((float)(2 * T::KMAXQ - 1) + (float)(-T::IS_MAX) * T::STEP) / eff_max, g_ahead);
         for (int is = -T::IS_MAX; is <= T::IS_MAX; ++is) {
             const float id = ((float)(2 * T::KMAXQ - 1) + (float)is * T::STEP) / eff_max;
             const float this_scale = 1 / id;
             int g[NG];
-            const uint32_t off = project(skipped ? 0u : kAllGroups, id, this_scale, g);
+#pragma unroll
+            for (int k = 0; k < NG; ++k) g[k] = g_ahead[k];
+            if (is < T::IS_MAX) lookup(skipped ? 0u : kAllGroups, ((float)(2 * T::KMAXQ - 1) + (float)(is + 1) * T::STEP) / eff_max, g_ahead);
+            const uint32_t off = project(this_scale, g);
             if (!skipped) {
                 float sumqx = 0, sumq2 = 0;
 #pragma unroll
@@ -537,7 +549,8 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
             constexpr bool all_groups = TYPE == GGML_TYPE_IQ2_XXS || TYPE == GGML_TYPE_IQ3_S;
             const uint32_t want = reproject ? (all_groups ? kAllGroups : (~on_grid & kAllGroups)) : 0u;
             int g[NG];
-            project(want, reproject ? 1 / scale : 0.f, scale, g);
+            lookup(want, reproject ? 1 / scale : 0.f, g);
+            project(scale, g);
             if (reproject) {
 #pragma unroll
                 for (int k = 0; k < NG; ++k) {
