@@ -33,14 +33,20 @@ GGUF_D void load_group(const float *p, float (&x)[N]) {
     }
 }
 
-// upstream libgguf_iq_tables.cpp:714-781 (the reachable part: a non-empty neighbour list)
-GGUF_D int best_neighbour_ternary(const uint16_t *__restrict__ nb, const uint8_t *__restrict__ grid, const float *xv,
-                                  const float *wv, float scale, const float (&xg)[3], int *L) {
+// upstream libgguf_iq_tables.cpp:714-781 (the reachable part: a non-empty neighbour list), run by the whole warp for
+// the group of one of its lanes: lane i evaluates entries i, i + 32, ... of the list; the winner is the first strict
+// minimum in list order, i.e. the smallest (distance, position), found with two warp-wide integer minima (distances
+// are sums of non-negative terms, so their bit patterns order like the values; FLT_MAX and NaN never win, as
+// upstream's `<` against FLT_MAX).  All lanes pass the same list, scale and values.  Left to the owning lane alone the
+// four scans of a block (1 to 205 entries each) ran with a third of the warp busy.
+GGUF_D int best_neighbour_ternary(const uint16_t *__restrict__ nb, const uint8_t *__restrict__ grid, const float (&xv)[8],
+                                  const float (&wv)[8], float scale, const float (&xg)[3], int lane) {
     const int n = __ldg(nb);
     float best_score = FLT_MAX;
-    int best = -1;
-    for (int j = 1; j <= n; ++j) {
-        const int g = __ldg(nb + j);
+    uint32_t best_j = 0xFFFFFFFFu;
+    int best = 0;
+    for (int j = lane; j < n; j += 32) {
+        const int g = __ldg(nb + 1 + j);
         const uint2 pgw = __ldg(reinterpret_cast<const uint2 *>(grid) + g);
         float d2 = 0;
 #pragma unroll
@@ -50,12 +56,13 @@ GGUF_D int best_neighbour_ternary(const uint16_t *__restrict__ nb, const uint8_t
             const float diff = scale * q - xv[i];
             d2 += wv[i] * diff * diff;
         }
-        if (d2 < best_score) { best_score = d2; best = g; }
+        if (d2 < best_score) { best_score = d2; best_j = (uint32_t)j; best = g; }
     }
-    const uint2 pgw = __ldg(reinterpret_cast<const uint2 *>(grid) + best);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) L[i] = (int)(((i < 4 ? pgw.x : pgw.y) >> (8 * (i & 3))) & 0xFF) >> 1;
-    return best;
+    const uint32_t bits = best_j == 0xFFFFFFFFu ? 0xFFFFFFFFu : __float_as_uint(best_score);
+    const uint32_t low = __reduce_min_sync(kFull, bits);
+    const uint32_t first = __reduce_min_sync(kFull, bits == low ? best_j : 0xFFFFFFFFu);
+    if (first == 0xFFFFFFFFu) return 0;  // nothing comparable (upstream would index with -1)
+    return __shfl_sync(kFull, best, (int)(first & 31u));
 }
 
 GGUF_D float level_value(const uint8_t *__restrict__ grid, int index, int i, const float (&xg)[3]) {
@@ -228,39 +235,56 @@ __global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__rest
                 scale = -scale;
                 best_k = IS_M ? 3 - best_k : -best_k;
             }
-            bool all_on_grid = true;
 #pragma unroll
             for (int k = 0; k < NG; ++k) {
-                const bool plus = IS_M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
-                const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
                 uint32_t u = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) u |= (uint32_t)L[8 * k + i] << (2 * i);
-                int g = __ldg(tab.map + u);
-                if (g < 0) {
-                    all_on_grid = false;
-                    g = best_neighbour_ternary(tab.neighbours + (-g - 1), tab.grid, xb + 8 * k, weight + 8 * k, scale, xx, L + 8 * k);
-                }
-                index[k] = g;
-            }
-            if (!all_on_grid) {
-                float sumqx = 0, sumq2 = 0;
-#pragma unroll
-                for (int k = 0; k < NG; ++k) {
-                    const bool plus = IS_M ? (k == 0 ? best_k < 2 : (best_k % 2 == 0)) : best_k == 1;
-                    const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float w = weight[8 * k + i];
-                        const float q = level_value(tab.grid, index[k], i, xx);
-                        sumqx += w * q * xb[8 * k + i];
-                        sumq2 += w * q * q;
-                    }
-                }
-                if (sumqx > 0 && sumq2 > 0) scale = sumqx / sumq2;
+                index[k] = __ldg(tab.map + u);  // negative: off the codebook, scanned below by the whole warp
             }
             shift = best_k;
         }
+    }
+    // the scans: one list at a time, all 32 lanes on it
+    bool all_on_grid = true;
+#pragma unroll
+    for (int k = 0; k < NG; ++k) {
+        const bool mine = !skipped && index[k] < 0;
+        const bool plus = IS_M ? (k == 0 ? shift < 2 : (shift % 2 == 0)) : shift == 1;
+        unsigned pending = __ballot_sync(kFull, mine);
+        while (pending) {
+            const int owner = __ffs(pending) - 1;
+            pending &= pending - 1;
+            const int list = __shfl_sync(kFull, -index[k] - 1, owner);
+            const float sc = __shfl_sync(kFull, scale, owner);
+            const bool pl = __shfl_sync(kFull, (int)plus, owner) != 0;
+            const float xx[3] = {pl ? x_p[0] : x_m[0], pl ? x_p[1] : x_m[1], pl ? x_p[2] : x_m[2]};
+            float xv[8], wv[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                xv[i] = __shfl_sync(kFull, xb[8 * k + i], owner);
+                wv[i] = __shfl_sync(kFull, weight[8 * k + i], owner);
+            }
+            const int g = best_neighbour_ternary(tab.neighbours + list, tab.grid, xv, wv, sc, xx, lane);
+            if (lane == owner) index[k] = g;
+        }
+        if (mine) all_on_grid = false;
+    }
+    if (!skipped && !all_on_grid) {
+        float sumqx = 0, sumq2 = 0;
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            const bool plus = IS_M ? (k == 0 ? shift < 2 : (shift % 2 == 0)) : shift == 1;
+            const float xx[3] = {plus ? x_p[0] : x_m[0], plus ? x_p[1] : x_m[1], plus ? x_p[2] : x_m[2]};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = weight[8 * k + i];
+                const float q = level_value(tab.grid, index[k], i, xx);
+                sumqx += w * q * xb[8 * k + i];
+                sumq2 += w * q * q;
+            }
+        }
+        if (sumqx > 0 && sumq2 > 0) scale = sumqx / sumq2;
     }
     if (skipped) { scale = 0.f; shift = IS_M ? 0 : 1; }
 
