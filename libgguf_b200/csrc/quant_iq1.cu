@@ -72,12 +72,10 @@ GGUF_D float level_value(const uint8_t *__restrict__ grid, int index, int i, con
 
 template <int BS>
 struct Scratch {
-    float xs[BS][kThreads];       // values, by element
-    float ws[BS][kThreads];       // weights, by element
-    float pa[BS + 1][kThreads];   // sort keys, then prefix sums of w*x (IQ1_S)
+    float ws[BS][kThreads];       // weights, by element; once they are no longer needed, the level of each element
+    float pa[BS + 1][kThreads];   // sort keys (the values), then prefix sums of w*x (IQ1_S)
     float pb[BS + 1][kThreads];   // prefix sums of w (IQ1_S)
     uint8_t order[BS][kThreads];  // element index at each sorted position
-    uint8_t level[BS][kThreads];  // level of each element
 };
 
 // Stable ascending insertion sort of the keys in s.pa[0..BS) with their element indices
@@ -100,7 +98,7 @@ GGUF_D void sort_block(Scratch<BS> &s, int t) {
 }
 
 template <bool IS_M>
-__global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
+__global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
                                                             uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
                                                             IqSearchTable tab) {
     constexpr int BS = IS_M ? 16 : 32, NG = BS / 8, W = 256 / BS, BYTES = IS_M ? 56 : 50;
@@ -147,7 +145,6 @@ __global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__rest
     if (!skipped) {
 #pragma unroll
         for (int i = 0; i < BS; ++i) {
-            s.xs[i][t] = xb[i];
             s.ws[i][t] = weight[i];
             s.pa[i][t] = xb[i];
             s.order[i][t] = (uint8_t)i;
@@ -158,12 +155,16 @@ __global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__rest
         int besti1 = -1, besti2 = -1, best_k = IS_M ? -1 : 0;
         if (!IS_M) {
             // prefix sums over the sorted order
+            // (the sorted values are the sort keys; each is read before its slot receives a prefix sum)
             float sx = 0.f, sw = 0.f;
+            float key = s.pa[0][t];
             s.pa[0][t] = 0.f;
             s.pb[0][t] = 0.f;
             for (int jj = 0; jj < BS; ++jj) {
                 const int i = s.order[jj][t];
-                sx = sx + s.ws[i][t] * s.xs[i][t];
+                const float x = key;
+                if (jj + 1 < BS) key = s.pa[jj + 1][t];
+                sx = sx + s.ws[i][t] * x;
                 sw = sw + s.ws[i][t];
                 s.pa[jj + 1][t] = sx;
                 s.pb[jj + 1][t] = sw;
@@ -194,7 +195,7 @@ __global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__rest
             for (int jj = 0; jj < BS; ++jj) {
                 const int i = s.order[jj][t];
                 wso[jj] = s.ws[i][t];
-                xso[jj] = s.xs[i][t];
+                xso[jj] = s.pa[jj][t];
                 if (i < BS / 2) lo_mask |= 1u << jj;
             }
             for (int i1 = 0; i1 <= BS; ++i1) {
@@ -225,10 +226,11 @@ __global__ void __launch_bounds__(kThreads) quant_iq1_kernel(const float *__rest
         if (skipped) {
             scale = 0.f;
         } else {
-            for (int jj = 0; jj < BS; ++jj) s.level[s.order[jj][t]][t] = (uint8_t)(jj < besti1 ? 0 : (jj < besti2 ? 1 : 2));
+            uint8_t (*level)[kThreads] = reinterpret_cast<uint8_t (*)[kThreads]>(&s.ws[0][0]);  // the weights are done with
+            for (int jj = 0; jj < BS; ++jj) level[s.order[jj][t]][t] = (uint8_t)(jj < besti1 ? 0 : (jj < besti2 ? 1 : 2));
             int L[BS];
 #pragma unroll
-            for (int i = 0; i < BS; ++i) L[i] = s.level[i][t];
+            for (int i = 0; i < BS; ++i) L[i] = level[i][t];
             if (scale < 0) {
 #pragma unroll
                 for (int i = 0; i < BS; ++i) L[i] = 2 - L[i];
