@@ -69,6 +69,52 @@ def _make_input(torch, device, kind, rows, cols, seed):
     raise ValueError(kind)
 
 
+def cpu_quantize_baseline(x_host, im_host, types, seconds_per_type=1.5):
+    """Upstream's CPU quantizers (REF build, and the AVX2 build when present) on the first rows of the same input,
+    all host threads: rows are doubled until a call lasts about `seconds_per_type`.  Melem/s per type and backend."""
+    import numpy as np
+    from oracle import reference
+    kinds = [k for k in ("ref", "avx2") if reference.available(k)]
+    if not kinds:
+        kinds = ["port"]
+    cores = os.cpu_count() or 1
+    per_type, totals = {}, {k: [0.0, 0.0] for k in kinds}
+    for kind in kinds:
+        chk = reference.load(kind)
+        for name in types:
+            code = CODE[name]
+            rs = chk.row_size(code, x_host.shape[1])
+            rows = min(x_host.shape[0], max(cores, 16))
+            one = np.ascontiguousarray(x_host[:1])  # first use builds the type's search tables: not timed
+            one_out = np.empty(rs, np.uint8)
+            chk._quantize(code, one.ctypes.data, one_out.ctypes.data, 0, 1, one.shape[1],
+                          im_host.ctypes.data if im_host is not None else None)
+            while True:
+                src = np.ascontiguousarray(x_host[:rows])
+                dst = np.empty(rows * rs, np.uint8)
+                t0 = time.perf_counter()
+                wrote = chk._quantize(code, src.ctypes.data, dst.ctypes.data, 0, rows, src.shape[1],
+                                      im_host.ctypes.data if im_host is not None else None)
+                dt = time.perf_counter() - t0
+                if wrote != rows * rs:
+                    raise RuntimeError(f"CPU {kind} quantize_chunk failed for {name}")
+                if dt >= seconds_per_type / 4 or rows >= x_host.shape[0]:
+                    break
+                rows = min(x_host.shape[0], rows * 4)
+            per_type.setdefault(name, {})[f"cpu_{kind}_Melem/s"] = round(rows * src.shape[1] / dt / 1e6, 1)
+            per_type[name][f"cpu_{kind}_rows"] = rows
+            totals[kind][0] += rows * src.shape[1]
+            totals[kind][1] += dt
+    first = kinds[0]
+    out = {"value": round(totals[first][0] / totals[first][1] / 1e6, 1), "unit": "Melem/s",
+           "cores": 1 if first == "port" else cores, "kind": "port" if first == "port" else "reference",
+           "sample": "libgguf_quantize_chunk on the first rows of the same input per type (rows grown until a call lasts "
+                     f"about {seconds_per_type / 4:.1f}-{seconds_per_type:.1f} s), all host threads; aggregate over the types"}
+    if "avx2" in kinds:
+        out["avx2_value"] = round(totals["avx2"][0] / totals["avx2"][1] / 1e6, 1)
+    return out, per_type
+
+
 def run(args, torch, dist, lib, ops, device, rank, world):
     import bench
     stream = torch.cuda.current_stream(device)
@@ -145,13 +191,19 @@ def run(args, torch, dist, lib, ops, device, rank, world):
     clocks = sampler.stop()
     launches = lib.libgguf_cuda_kernel_launch_count() - launches0
     value = len(types) * n / total_ms / 1e3
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu, cpu_rows = cpu_quantize_baseline(xs[0].cpu().numpy(), im.cpu().numpy() if im is not None else None, types)
+        for name, extra in cpu_rows.items():
+            table[name].update(extra)
     if rank == 0:
         print(json.dumps({
             "metric": "quant Melem/s", "value": value, "unit": "Melem/s", "n_gpus": world, "steps": reps, "warmup": max(3, args.warmup),
             "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{wl} {rows}x{cols} {kind}{' +imatrix' if weighted else ''}: {','.join(types)}",
                        "l2": f"{NSETS} rotating input/output buffer sets per kernel"},
-            "clocks": clocks, "gpu_launches": int(launches), "per_qtype": table, "peak_source": peak_kind}))
+            "clocks": clocks, "gpu_launches": int(launches), "per_qtype": table, "peak_source": peak_kind,
+            **({"cpu_baseline": cpu} if cpu else {})}))
 
 
 def run_dequant_all(args, torch, lib, ops, device, rank, world, hbm, peak_kind):
