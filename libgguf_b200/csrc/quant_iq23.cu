@@ -33,27 +33,27 @@ constexpr unsigned kFull = 0xffffffffu;
 
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
-    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4;
+    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4, PER = 4;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = true;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_XS> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5, PER = 6;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_S> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5, PER = 4;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_XXS> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6, PER = 6;
     static constexpr bool PARITY = true, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_S> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6, PER = 6;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 0.f;  // upstream tests `!max`
 };
@@ -210,10 +210,10 @@ constexpr unsigned long long kNoWinner = ~0ull;
 // a whole list stores its key, lanes that share a list combine theirs with a shared-memory
 // atomic minimum.  Distances are sums of non-negative terms, so their bit patterns order like
 // the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
-template <int GD, int TMAX>
+template <int GD, int TMAX, int PER>
 GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
                           const float *xs, const float *ws, const uint32_t *gridh, const uint16_t *__restrict__ lists) {
-    constexpr int AHEAD = 4;  // list entries are fetched this many steps early, across list boundaries
+    constexpr int AHEAD = PER == 2 ? 4 : 3;  // list entries are fetched this many steps early, across list boundaries
     const uint32_t share = (E + 31) >> 5;
     uint32_t e = umin((uint32_t)lane * share, E);
     const uint32_t end = umin(e + share, E);
@@ -232,23 +232,25 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, co
     bool whole = j == 0;
     float best_d2 = FLT_MAX;
     uint32_t best_at = 0xFFFFFFFFu;
-    // Entries are taken two at a time (two independent sums in flight); where a list or the lane's stretch ends on
-    // an odd entry the second one repeats the first and is ignored.  The fetch cursor forms the same pairs AHEAD
-    // steps in front of the evaluation cursor and hands them over as (first | second << 12 | pair << 31).
+    // Entries are taken PER at a time (PER independent ordered sums in flight); where a list or the lane's stretch
+    // ends inside a step the missing entries repeat the first one and are ignored.  The fetch cursor forms the same
+    // steps AHEAD of the evaluation cursor and hands them over packed two to a word.
     int ft = t;
     uint32_t fj = j, fn = tk.n, fe = e;
     const uint16_t *fnb = lists + tk.list + 1;
-    uint32_t ring[AHEAD];
-    auto fetch = [&]() -> uint32_t {
-        uint32_t rec = 0;
+    constexpr int RW = PER / 2;  // words per step: two 12-bit entries each, the count in bits 24.. of the first
+    uint32_t ring[AHEAD][RW];
+    auto fetch = [&](uint32_t (&rec)[RW]) {
+#pragma unroll
+        for (int q = 0; q < RW; ++q) rec[q] = 0;
         if (fe < end) {
-            const bool two = fj + 1 < fn && fe + 1 < end;
-            const uint32_t g0 = __ldg(fnb + fj);
-            const uint32_t g1 = __ldg(fnb + fj + (two ? 1 : 0));
-            rec = g0 | (g1 << 12) | (two ? 0x80000000u : 0u);
-            const uint32_t adv = two ? 2u : 1u;
-            fe += adv;
-            fj += adv;
+            const uint32_t cnt = umin(umin(fn - fj, end - fe), (uint32_t)PER);
+#pragma unroll
+            for (int q = 0; q < PER; ++q)
+                rec[q / 2] |= (uint32_t)__ldg(fnb + fj + ((uint32_t)q < cnt ? q : 0)) << (12 * (q & 1));
+            rec[0] |= cnt << 24;
+            fe += cnt;
+            fj += cnt;
             if (fj == fn && fe < end) {
                 ++ft;
                 fj = 0;
@@ -256,41 +258,47 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, co
                 fnb = lists + tasks[ft].list + 1;
             }
         }
-        return rec;
     };
 #pragma unroll
-    for (int d = 0; d < AHEAD; ++d) ring[d] = fetch();
+    for (int d = 0; d < AHEAD; ++d) fetch(ring[d]);
     while (e < end) {
-        {
-            {
-                const uint32_t rec = ring[0];
+        uint32_t rec[RW];
 #pragma unroll
-                for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
-                ring[AHEAD - 1] = fetch();
-                const uint32_t g0 = rec & 0xFFFu, g1 = (rec >> 12) & 0xFFFu, two = rec >> 31;
-                const float d2a = neighbour_d2<GD>(gridh, (int)g0, tk.scale, xv, wv);
-                const float d2b = neighbour_d2<GD>(gridh, (int)g1, tk.scale, xv, wv);
-                if (d2a < best_d2) { best_d2 = d2a; best_at = (j << 16) | g0; }
-                if (two && d2b < best_d2) { best_d2 = d2b; best_at = ((j + 1) << 16) | g1; }
-                e += 1 + two;
-                j += 1 + two;
-                if (j == tk.n) {
-                    if (best_d2 < FLT_MAX) {
-                        const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
-                        if (whole) winner[t] = key;
-                        else atomicMin(winner + t, key);
-                    }
-                    ++t;
-                    j = 0;
-                    whole = true;
-                    best_d2 = FLT_MAX;
-                    best_at = 0xFFFFFFFFu;
-                    if (e < end) {
-                        tk = tasks[t];
-                        load_staged<GD>(xs + tk.xoff, xv);
-                        load_staged<GD>(ws + tk.xoff, wv);
-                    }
-                }
+        for (int q = 0; q < RW; ++q) rec[q] = ring[0][q];
+#pragma unroll
+        for (int d = 0; d + 1 < AHEAD; ++d) {
+#pragma unroll
+            for (int q = 0; q < RW; ++q) ring[d][q] = ring[d + 1][q];
+        }
+        fetch(ring[AHEAD - 1]);
+        const uint32_t cnt = rec[0] >> 24;
+        uint32_t g[PER];
+        float d2[PER];
+#pragma unroll
+        for (int q = 0; q < PER; ++q) g[q] = (rec[q / 2] >> (12 * (q & 1))) & 0xFFFu;
+#pragma unroll
+        for (int q = 0; q < PER; ++q) d2[q] = neighbour_d2<GD>(gridh, (int)g[q], tk.scale, xv, wv);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) {
+            if ((uint32_t)q < cnt && d2[q] < best_d2) { best_d2 = d2[q]; best_at = ((j + q) << 16) | g[q]; }
+        }
+        e += cnt;
+        j += cnt;
+        if (j == tk.n) {
+            if (best_d2 < FLT_MAX) {
+                const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
+                if (whole) winner[t] = key;
+                else atomicMin(winner + t, key);
+            }
+            ++t;
+            j = 0;
+            whole = true;
+            best_d2 = FLT_MAX;
+            best_at = 0xFFFFFFFFu;
+            if (e < end) {
+                tk = tasks[t];
+                load_staged<GD>(xs + tk.xoff, xv);
+                load_staged<GD>(ws + tk.xoff, wv);
             }
         }
     }
@@ -482,7 +490,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 }
             }
             __syncwarp();
-            if (all >> 10) balanced_scan<GD, TMAX>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, lists);
+            if (all >> 10) balanced_scan<GD, TMAX, T::PER>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, lists);
             __syncwarp();
             slot = slot0;
 #pragma unroll
