@@ -98,7 +98,7 @@ GGUF_D void sort_block(Scratch<BS> &s, int t) {
 }
 
 template <bool IS_M>
-__global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
+__global__ void __launch_bounds__(kThreads, IS_M ? 6 : 7) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
                                                             uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
                                                             IqSearchTable tab) {
     constexpr int BS = IS_M ? 16 : 32, NG = BS / 8, W = 256 / BS, BYTES = IS_M ? 56 : 50;
@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
         float best_score = -FLT_MAX;
         scale = max;
         int besti1 = -1, besti2 = -1, best_k = IS_M ? -1 : 0;
-        if (!IS_M) {
+        if constexpr (!IS_M) {
             // prefix sums over the sorted order
             // (the sorted values are the sort keys; each is read before its slot receives a prefix sum)
             float sx = 0.f, sw = 0.f;
@@ -198,28 +198,42 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
                 xso[jj] = s.pa[jj][t];
                 if (i < BS / 2) lo_mask |= 1u << jj;
             }
-            for (int i1 = 0; i1 <= BS; ++i1) {
-                for (int i2 = i1; i2 <= BS; ++i2) {
-                    float qx0 = 0, qx1 = 0, qx2 = 0, qx3 = 0, q20 = 0, q21 = 0, q22 = 0, q23 = 0;
+            // Upstream adds the 16 terms of each of the eight sums from scratch for every split (i1, i2), in sorted
+            // order.  The terms of the positions below i2 do not depend on i2 and those below i1 not on i1 either,
+            // so the chains over them are carried from split to split (one more term each time) and only the tail
+            // from i2 on (level 2) is added again: the same additions in the same order, 969 term steps instead of 2448.
+            struct Sums { float qx0, qx1, qx2, qx3, q20, q21, q22, q23; };
+            auto add_term = [&](Sums &S, float w, float x, bool lo, float xp, float xm) {
+                const float ap = w * xp * x, am = w * xm * x;
+                const float bp = w * xp * xp, bm = w * xm * xm;
+                S.qx0 += ap; S.qx1 += lo ? ap : am; S.qx2 += lo ? am : ap; S.qx3 += am;
+                S.q20 += bp; S.q21 += lo ? bp : bm; S.q22 += lo ? bm : bp; S.q23 += bm;
+            };
 #pragma unroll
-                    for (int jj = 0; jj < BS; ++jj) {
-                        const int lv = jj < i1 ? 0 : (jj < i2 ? 1 : 2);
-                        const float xp = lv == 0 ? x_p[0] : lv == 1 ? x_p[1] : x_p[2];
-                        const float xm = lv == 0 ? x_m[0] : lv == 1 ? x_m[1] : x_m[2];
-                        const float ap = wso[jj] * xp * xso[jj], am = wso[jj] * xm * xso[jj];
-                        const float bp = wso[jj] * xp * xp, bm = wso[jj] * xm * xm;
-                        const bool lo = (lo_mask >> jj) & 1;
-                        qx0 += ap; qx1 += lo ? ap : am; qx2 += lo ? am : ap; qx3 += am;
-                        q20 += bp; q21 += lo ? bp : bm; q22 += lo ? bm : bp; q23 += bm;
+            for (int jj = 0; jj < BS; ++jj) s.pb[jj][t] = wso[jj];  // sorted weights, for the positions indexed by i1 / i2
+            Sums below_i1 = {0, 0, 0, 0, 0, 0, 0, 0};                 // positions < i1 at level 0
+            for (int i1 = 0; i1 <= BS; ++i1) {
+                Sums below_i2 = below_i1;                             // ... then positions i1 .. i2-1 at level 1
+                for (int i2 = i1; i2 <= BS; ++i2) {
+                    Sums S = below_i2;
+#define GGUF_IQ1M_TAIL(JJ) case JJ: add_term(S, wso[JJ], xso[JJ], (lo_mask >> JJ) & 1, x_p[2], x_m[2]); [[fallthrough]];
+                    switch (i2) {
+                        GGUF_IQ1M_TAIL(0) GGUF_IQ1M_TAIL(1) GGUF_IQ1M_TAIL(2) GGUF_IQ1M_TAIL(3) GGUF_IQ1M_TAIL(4) GGUF_IQ1M_TAIL(5)
+                        GGUF_IQ1M_TAIL(6) GGUF_IQ1M_TAIL(7) GGUF_IQ1M_TAIL(8) GGUF_IQ1M_TAIL(9) GGUF_IQ1M_TAIL(10) GGUF_IQ1M_TAIL(11)
+                        GGUF_IQ1M_TAIL(12) GGUF_IQ1M_TAIL(13) GGUF_IQ1M_TAIL(14) GGUF_IQ1M_TAIL(15)
+                        default: break;
                     }
-                    const float sqx[4] = {qx0, qx1, qx2, qx3}, sq2[4] = {q20, q21, q22, q23};
+#undef GGUF_IQ1M_TAIL
+                    const float sqx[4] = {S.qx0, S.qx1, S.qx2, S.qx3}, sq2[4] = {S.q20, S.q21, S.q22, S.q23};
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         if (sq2[k] > 0 && sqx[k] * sqx[k] > best_score * sq2[k]) {
                             scale = sqx[k] / sq2[k]; best_score = scale * sqx[k]; besti1 = i1; besti2 = i2; best_k = k;
                         }
                     }
+                    if (i2 < BS) add_term(below_i2, s.pb[i2][t], s.pa[i2][t], (lo_mask >> i2) & 1, x_p[1], x_m[1]);
                 }
+                if (i1 < BS) add_term(below_i1, s.pb[i1][t], s.pa[i1][t], (lo_mask >> i1) & 1, x_p[0], x_m[0]);
             }
             if (besti1 < 0 || besti2 < 0 || best_k < 0) skipped = true;
         }
