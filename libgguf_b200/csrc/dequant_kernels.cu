@@ -1291,7 +1291,7 @@ template <class D>
 struct TableBytes<D, std::void_t<decltype(D::kTableBytes)>> { static constexpr int value = D::kTableBytes; };
 
 template <int TYPE, class OutT>
-__global__ void __launch_bounds__(kThreads) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
+__global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                int64_t nblocks) {
     using D = Fast<TYPE>;
     constexpr int TILE_BLOCKS = kTileElems / D::ELEMS;
