@@ -116,12 +116,15 @@ GGUF_D uint32_t nonzero_nibbles(uint32_t v) {
 // lies between the two ends.
 GGUF_D uint32_t fp4_word_bracketed(const float *x, const float *y, const Fp4Bracket &k, uint32_t &other) {
     float lo_a[4], hi_a[4], lo_b[4], hi_b[4];
+    const float2 klo = make_float2(k.lo, k.lo), khi = make_float2(k.hi, k.hi);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        lo_a[i] = x[i] * k.lo;
-        hi_a[i] = y[i] * k.lo;
-        lo_b[i] = x[i] * k.hi;
-        hi_b[i] = y[i] * k.hi;
+    for (int i = 0; i < 4; i += 2) {  // two neighbouring elements per multiply instruction (nothing is added to the products)
+        const float2 xx = make_float2(x[i], x[i + 1]), yy = make_float2(y[i], y[i + 1]);
+        const float2 a = __fmul2_rn(xx, klo), b = __fmul2_rn(yy, klo), c = __fmul2_rn(xx, khi), d = __fmul2_rn(yy, khi);
+        lo_a[i] = a.x; lo_a[i + 1] = a.y;
+        hi_a[i] = b.x; hi_a[i + 1] = b.y;
+        lo_b[i] = c.x; lo_b[i + 1] = c.y;
+        hi_b[i] = d.x; hi_b[i + 1] = d.y;
     }
     const uint32_t a = drop_negative_zero(cvt_e2m1x8(lo_a, hi_a)), b = drop_negative_zero(cvt_e2m1x8(lo_b, hi_b));
     other = a ^ b;
