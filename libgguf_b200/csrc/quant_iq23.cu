@@ -689,7 +689,9 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
     const int64_t grid = (nblocks + kThreads - 1) / kThreads;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
     const size_t smem = ((size_t)tab.grid_size * T::GD / 2 + (kThreads / 32) * (2 * 32 * XP + TMAX * 7)) * sizeof(float);
-    static const cudaError_t attr = cudaFuncSetAttribute(quant_iq23_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+    // a per-device setting: made on every launch (microseconds against a kernel of milliseconds) so that every GPU
+    // of a process that drives several has it
+    const cudaError_t attr = cudaFuncSetAttribute(quant_iq23_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (attr != cudaSuccess) return attr;
     quant_iq23_kernel<TYPE><<<(unsigned)grid, kThreads, smem, stream>>>(src, qw, static_cast<uint8_t *>(dst), nblocks, n_per_row, tab);
     count_launch();

@@ -101,7 +101,8 @@ def test_missing_importance_weights_are_derived_from_the_tensor(gguf, checker, k
     assert np.array_equal(gguf.auto_imatrix(wide).view(np.uint32), weights.view(np.uint32))
     for qtype in (16, 19):
         dst = np.zeros(150 * gguf.row_size(qtype, 512), np.uint8)
-        with ConversionPipeline([0], slots=2, chunk_bytes=40 << 10) as pipe:
+        # two workers, on two GPUs where the box has them: per-device kernel settings must hold on every device
+        with ConversionPipeline([0, 1 % torch.cuda.device_count()], slots=2, chunk_bytes=40 << 10) as pipe:
             pipe.quantize([(qtype, src, None, dst)])
         want = checker.quantize_rows(wide, qtype, weights)
         assert np.array_equal(dst, np.ascontiguousarray(want).view(np.uint8).reshape(-1))
