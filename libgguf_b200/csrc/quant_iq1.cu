@@ -98,7 +98,7 @@ GGUF_D void sort_block(Scratch<BS> &s, int t) {
 }
 
 template <bool IS_M>
-__global__ void __launch_bounds__(kThreads, IS_M ? 6 : 7) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
+__global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const float *__restrict__ src, const float *__restrict__ qw,
                                                             uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
                                                             IqSearchTable tab) {
     constexpr int BS = IS_M ? 16 : 32, NG = BS / 8, W = 256 / BS, BYTES = IS_M ? 56 : 50;
