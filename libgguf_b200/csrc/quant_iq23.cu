@@ -282,8 +282,9 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, co
         for (int q = 0; q < PER; ++q) {
             if ((uint32_t)q < cnt && d2[q] < best_d2) { best_d2 = d2[q]; best_at = ((j + q) << 16) | g[q]; }
         }
-        e += cnt;
-        j += cnt;
+        const uint32_t adv = umax(cnt, 1u);  // cnt is never 0 while e < end (the cursors advance together); never spin on it
+        e += adv;
+        j += adv;
         if (j == tk.n) {
             if (best_d2 < FLT_MAX) {
                 const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
@@ -455,11 +456,15 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
             for (int k = 0; k < NG; ++k) {
                 nk[k] = 0;
                 if (g[k] < 0) {
-                    off |= 1u << k;
                     const uint32_t v = (uint32_t)(-g[k] - 1);
-                    nk[k] = v & 511u;
-                    g[k] = (int)(v >> 9);  // the list's offset until the winner replaces it
-                    total_n += nk[k];
+                    if ((v & 511u) == 0) {
+                        g[k] = 0;  // an empty list (no codebook has one) is not queued
+                    } else {
+                        off |= 1u << k;
+                        nk[k] = v & 511u;
+                        g[k] = (int)(v >> 9);  // the list's offset until the winner replaces it
+                        total_n += nk[k];
+                    }
                 }
             }
             // slots and positions: one inclusive scan over (entries << 10 | scans)
