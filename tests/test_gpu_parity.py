@@ -96,6 +96,26 @@ def test_importance_weighted_rows_match_checker(gguf, checker, name):
     np.testing.assert_array_equal(gguf.quantize_rows(x, qtype, im), checker.quantize_rows(x, qtype, im))
 
 
+@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_S", "IQ3_XXS", "IQ1_S"])
+def test_config4_slice_of_the_lattice_types(gguf, checker, name):
+    """BASELINE configuration 4 at its own width: a 256-row slice of the 4096 x 11008 Student-t matrix with the
+    chi-square importance weights, plus rows whose blocks are partly zero (lanes that queue no scans next to lanes
+    that queue long ones) and one row of large outliers."""
+    qtype = inputs.QTYPES[name]
+    if not supported_by(checker, qtype):
+        pytest.skip("checker has no quantizer for this type")
+    x, im = inputs.config4(256, 11008)
+    x = x.copy()
+    x[3, 256:1024] = 0.0
+    x[4, ::2] = 0.0
+    x[5, 32:64] = 0.0
+    x[6, ::97] *= np.float32(400.0)
+    want = checker.quantize_rows(x, qtype, im)
+    got = gguf.quantize_rows(x, qtype, im)
+    bad_rows = np.flatnonzero((want != got).any(axis=-1))
+    assert bad_rows.size == 0, f"{bad_rows.size} rows differ, first {bad_rows[:5]}"
+
+
 @pytest.mark.parametrize("name", ALL)
 def test_ragged_sizes_and_chunk_offsets(gguf, checker, name):
     """1 block, 1 row, row counts that do not fill a CTA, and start offsets into a larger matrix."""
