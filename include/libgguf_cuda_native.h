@@ -131,6 +131,15 @@ LIBGGUF_CUDA_API void libgguf_cuda_host_copy(void *dst, const void *src, size_t 
  * device, and waits for the upload.  Optional: the row functions do it on first use. */
 LIBGGUF_CUDA_API int libgguf_cuda_prepare_qtype(int64_t qtype);
 
+/* Inspection, no upstream counterpart in the ABI: the host copy of the search tables the quantizer of an IQ1 / IQ2 / IQ3
+ * type uses (the same data upstream builds into iq2_data / iq3_data, csrc/common/libgguf_iq_tables.cpp:36-417,
+ * :487-666).  grid: grid_size x dims coordinate bytes (2 * code + 1); map: lattice index -> grid index, or
+ * -(offset + 1) where neighbours[offset] is a count followed by that many grid indices ordered by (distance, index).
+ * The pointers stay valid for the life of the process.  Needs no device; any out pointer may be NULL. */
+LIBGGUF_CUDA_API int libgguf_cuda_iq_search_table(int64_t qtype, int32_t *grid_size, int32_t *dims, const uint8_t **grid,
+                                                  const int32_t **map, int64_t *map_size, const uint16_t **neighbours,
+                                                  int64_t *neighbours_len);
+
 /* Self-test, no upstream counterpart: the MXFP4 / NVFP4 quantizers pick each element's level by threshold
  * comparisons instead of upstream's 16-way scan (libgguf_common.h:321-335).  This runs both on every one of the
  * 2^32 float bit patterns at block scale `scale` on the current device (about a second) and stores how many

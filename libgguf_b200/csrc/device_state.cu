@@ -8,6 +8,7 @@
 #include <utility>
 #include <vector>
 
+#include "../../include/libgguf_cuda_native.h"
 #include "device_state.h"
 #include "gguf_common.cuh"
 #include "gguf_tables.cuh"
@@ -137,3 +138,20 @@ void device_state_release_all() {
 }
 
 }  // namespace gguf
+
+// Host view of one quantizer's search tables (no device involved).
+extern "C" int libgguf_cuda_iq_search_table(int64_t qtype, int32_t *grid_size, int32_t *dims, const uint8_t **grid,
+                                            const int32_t **map, int64_t *map_size, const uint16_t **neighbours,
+                                            int64_t *neighbours_len) {
+    const int id = gguf::table_for_type((int)qtype);
+    if (id < 0) return LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE;
+    const gguf::IqHostTable &t = gguf::iq_host_table(id);
+    if (grid_size) *grid_size = t.grid_size;
+    if (dims) *dims = t.dims;
+    if (grid) *grid = t.grid.data();
+    if (map) *map = t.map.data();
+    if (map_size) *map_size = (int64_t)t.map.size();
+    if (neighbours) *neighbours = t.neighbours.data();
+    if (neighbours_len) *neighbours_len = (int64_t)t.neighbours.size();
+    return LIBGGUF_CUDA_STATUS_SUCCESS;
+}

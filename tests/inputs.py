@@ -1,8 +1,11 @@
 """Seeded input generators shared by the golden-fixture script and the tests.
 
 `pattern_rows` reproduces the patterns of upstream bench/check_exact.py:80-118 (the inputs behind
-upstream's frozen tests/golden/manifest.json); the `config_*` functions are the synthetic
-stand-ins for the BASELINE configurations."""
+upstream's frozen tests/golden/manifest.json).  The `*_matrix` / `conversion_tensor` functions are the
+synthetic stand-ins for model weights that the benchmark workloads use: every one is a seeded NumPy
+generator, so the CPU checker and the GPU see identical bits, and a row slice of the full-size matrix is
+obtained by generating the full matrix and slicing it (`rows=` only changes the height for the cheap
+generators whose first rows do not depend on it).  bench.py imports this module for its inputs."""
 from __future__ import annotations
 
 import numpy as np
@@ -58,32 +61,63 @@ def pattern_rows(pattern: str, rows: int, width: int, seed: int = 0) -> np.ndarr
 
 
 def imatrix_for(width: int, seed: int = 1) -> np.ndarray:
-    """Per-column importance weights, chi-square(4)/4 as in BASELINE config 4."""
+    """Per-column importance weights, chi-square(4)/4 (the importance matrix of the lattice-quantizer workload)."""
     return (np.random.default_rng(seed).chisquare(4, width).astype(np.float32) / np.float32(4)).astype(np.float32)
 
 
-def config1(rows: int = 4096, width: int = 4096) -> np.ndarray:
+def q4k_matrix(rows: int = 4096, width: int = 4096) -> np.ndarray:
+    """Q4_K round-trip workload: 4096 x 4096 i.i.d. N(0, 0.02), seed 0 (first rows independent of `rows`)."""
     return (np.random.default_rng(0).standard_normal((rows, width), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
 
 
-def config4(rows: int = 4096, width: int = 11008) -> tuple[np.ndarray, np.ndarray]:
+def decode_sweep_matrix(rows: int = 14336, width: int = 4096) -> np.ndarray:
+    """Decode-sweep workload: a 14336 x 4096 weight matrix, i.i.d. N(0, 0.02), seed 0; it is quantized by the checker
+    per type and the encoded bytes are what the decoders are timed and checked on."""
+    return (np.random.default_rng(0).standard_normal((rows, width), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+
+
+def lattice_matrix(rows: int = 4096, width: int = 11008) -> tuple[np.ndarray, np.ndarray]:
+    """Lattice-quantizer (IQ) workload: 4096 x 11008 Student-t(5) * 0.02, seed 0, with the chi-square(4)/4
+    importance weights of `imatrix_for(width, 1)`."""
     x = (np.random.default_rng(0).standard_t(5, (rows, width)).astype(np.float32) * np.float32(0.02)).astype(np.float32)
     return x, imatrix_for(width, 1)
 
 
-def config5(rows: int = 8192, width: int = 8192, seed: int = 0) -> np.ndarray:
-    """Laplace(0, 0.01) rounded to bf16 and widened; 1% of 32-element blocks get one +-50 sigma outlier."""
-    rng = np.random.default_rng(seed)
-    x = rng.laplace(0.0, 0.01, (rows, width)).astype(np.float32)
+def _round_to_bf16(x: np.ndarray) -> np.ndarray:
     u = x.view(np.uint32)
     u = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)) << np.uint32(16)
-    x = u.view(np.float32).copy()
+    return u.view(np.float32)
+
+
+def microscaling_matrix(rows: int = 8192, width: int = 8192, seed: int = 0) -> np.ndarray:
+    """MXFP4 / NVFP4 workload: Laplace(0, 0.01) rounded to bf16 and widened back to fp32; 1% of the 32-element
+    blocks get one element set to +-50 sigma (sigma = 0.01 * sqrt 2)."""
+    rng = np.random.default_rng(seed)
+    x = _round_to_bf16(rng.laplace(0.0, 0.01, (rows, width)).astype(np.float32)).copy()
     nblocks = rows * width // 32
     chosen = rng.choice(nblocks, size=max(1, nblocks // 100), replace=False)
     pos = rng.integers(0, 32, size=chosen.size)
     sign = rng.choice(np.array([-1.0, 1.0], dtype=np.float32), size=chosen.size)
     flat = x.reshape(-1)
     flat[chosen * 32 + pos] = sign * np.float32(50 * 0.01 * np.sqrt(2.0))
-    u = flat.view(np.uint32)
-    flat[:] = (((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)) << np.uint32(16)).view(np.float32)
+    flat[:] = _round_to_bf16(flat)
     return flat.reshape(rows, width)
+
+
+def conversion_tensor(name: str, rows: int, width: int, first_rows: int | None = None) -> np.ndarray:
+    """One tensor of the synthetic Llama-3-8B-shaped conversion set: i.i.d. N(0, 0.02) from a generator seeded by the
+    tensor's name, with ceil(0.1% of the columns) scaled by 20 as outlier channels.  `first_rows` returns only the
+    first rows of the tensor (same values as in the whole tensor: the normal draws are row-major and the outlier
+    columns are drawn from a second generator)."""
+    import zlib
+    seed = zlib.crc32(name.encode())
+    take = rows if first_rows is None else min(rows, first_rows)
+    x = (np.random.default_rng(seed).standard_normal((take, width), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    cols = np.random.default_rng(seed + 1).choice(width, size=-(-width // 1000), replace=False)
+    x[:, cols] *= np.float32(20.0)
+    return x
+
+
+# shape classes of the conversion set (name of a representative tensor, rows, width)
+CONVERSION_SHAPES = (("blk.0.attn_q", 4096, 4096), ("blk.0.attn_k", 1024, 4096), ("blk.0.ffn_gate", 14336, 4096),
+                     ("blk.0.ffn_down", 4096, 14336), ("token_embd", 128256, 4096))

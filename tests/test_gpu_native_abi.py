@@ -71,7 +71,7 @@ def test_quantize_on_a_side_stream_and_leading_dims(ops, checker):
 
 
 def test_imatrix_is_honoured_for_optional_types(ops, checker):
-    x, im = inputs.config4(8, 1024)
+    x, im = inputs.lattice_matrix(8, 1024)
     q = ops.quantize(torch.from_numpy(x).cuda(), 12, torch.from_numpy(im).cuda())
     np.testing.assert_array_equal(q.cpu().numpy(), checker.quantize_rows(x, 12, im))
     assert not np.array_equal(q.cpu().numpy(), checker.quantize_rows(x, 12))

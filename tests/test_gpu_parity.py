@@ -92,19 +92,19 @@ def test_importance_weighted_rows_match_checker(gguf, checker, name):
     qtype = inputs.QTYPES[name]
     if not supported_by(checker, qtype):
         pytest.skip("checker has no quantizer for this type")
-    x, im = inputs.config4(32, 2048)
+    x, im = inputs.lattice_matrix(32, 2048)
     np.testing.assert_array_equal(gguf.quantize_rows(x, qtype, im), checker.quantize_rows(x, qtype, im))
 
 
 @pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_S", "IQ3_XXS", "IQ1_S"])
-def test_config4_slice_of_the_lattice_types(gguf, checker, name):
-    """BASELINE configuration 4 at its own width: a 256-row slice of the 4096 x 11008 Student-t matrix with the
+def test_lattice_workload_slice_at_full_width(gguf, checker, name):
+    """The lattice-quantizer benchmark workload at its own width: a 256-row slice of the 4096 x 11008 Student-t matrix with the
     chi-square importance weights, plus rows whose blocks are partly zero (lanes that queue no scans next to lanes
     that queue long ones) and one row of large outliers."""
     qtype = inputs.QTYPES[name]
     if not supported_by(checker, qtype):
         pytest.skip("checker has no quantizer for this type")
-    x, im = inputs.config4(256, 11008)
+    x, im = inputs.lattice_matrix(256, 11008)
     x = x.copy()
     x[3, 256:1024] = 0.0
     x[4, ::2] = 0.0
@@ -149,11 +149,11 @@ def test_ragged_sizes_and_chunk_offsets(gguf, checker, name):
     assert (dec[:5] == -7).all() and (dec[11:] == -7).all()
 
 
-def test_config1_q4k_roundtrip_properties(gguf, checker):
-    """BASELINE config 1 at full size (4096 x 4096, N(0, 0.02), seed 0): bytes against the checker
+def test_q4k_roundtrip_workload_properties(gguf, checker):
+    """The Q4_K round-trip workload at full size (4096 x 4096, N(0, 0.02), seed 0): bytes against the checker
     on a 256-row slice; on the whole matrix, chunk independence (any row range encodes to the same
     bytes as in the full call) and idempotence of decode -> encode -> decode."""
-    x = inputs.config1()
+    x = inputs.q4k_matrix()
     enc = gguf.quantize_rows(x, 12)
     np.testing.assert_array_equal(enc[1000:1256], checker.quantize_rows(x[1000:1256], 12))
     np.testing.assert_array_equal(enc[17:83], gguf.quantize_rows(x[17:83], 12))
