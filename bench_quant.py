@@ -220,7 +220,7 @@ def run_dequant_all(args, torch, lib, ops, device, rank, world, hbm, peak_kind):
     launches0 = lib.libgguf_cuda_kernel_launch_count()
     for name in sorted(CODE, key=lambda n: CODE[n]):
         code, (bel, bby) = CODE[name], BLOCK[name]
-        enc = [ops.quantize(x, code, imatrix=im if name.startswith("IQ") else None)]
+        enc = [ops.quantize_weighted(x, code, im) if name.startswith("IQ") else ops.quantize(x, code)]
         enc += [enc[0].clone() for _ in range(NSETS - 1)]
         outs = [torch.empty((rows, cols), dtype=torch.float16, device=device) for _ in range(NSETS)]
 

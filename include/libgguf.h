@@ -68,6 +68,44 @@ enum ggml_type {
     GGML_TYPE_COUNT = 42
 };
 
+/* Not used by any function below; declared because programs written against the upstream header name
+ * them (upstream include/libgguf.h:63-100).  ggml_prec is the precision tag of a tensor operation. */
+enum ggml_prec {
+    GGML_PREC_DEFAULT = 0,
+    GGML_PREC_F32 = 10
+};
+
+/* File-level type tag of a model ("general.file_type"): the type most tensors are stored in. */
+enum ggml_ftype {
+    GGML_FTYPE_UNKNOWN = -1,
+    GGML_FTYPE_ALL_F32 = 0,
+    GGML_FTYPE_MOSTLY_F16 = 1,
+    GGML_FTYPE_MOSTLY_Q4_0 = 2,
+    GGML_FTYPE_MOSTLY_Q4_1 = 3,
+    GGML_FTYPE_MOSTLY_Q4_1_SOME_F16 = 4,
+    GGML_FTYPE_MOSTLY_Q8_0 = 7,
+    GGML_FTYPE_MOSTLY_Q5_0 = 8,
+    GGML_FTYPE_MOSTLY_Q5_1 = 9,
+    GGML_FTYPE_MOSTLY_Q2_K = 10,
+    GGML_FTYPE_MOSTLY_Q3_K = 11,
+    GGML_FTYPE_MOSTLY_Q4_K = 12,
+    GGML_FTYPE_MOSTLY_Q5_K = 13,
+    GGML_FTYPE_MOSTLY_Q6_K = 14,
+    GGML_FTYPE_MOSTLY_IQ2_XXS = 15,
+    GGML_FTYPE_MOSTLY_IQ2_XS = 16,
+    GGML_FTYPE_MOSTLY_IQ3_XXS = 17,
+    GGML_FTYPE_MOSTLY_IQ1_S = 18,
+    GGML_FTYPE_MOSTLY_IQ4_NL = 19,
+    GGML_FTYPE_MOSTLY_IQ3_S = 20,
+    GGML_FTYPE_MOSTLY_IQ2_S = 21,
+    GGML_FTYPE_MOSTLY_IQ4_XS = 22,
+    GGML_FTYPE_MOSTLY_IQ1_M = 23,
+    GGML_FTYPE_MOSTLY_BF16 = 24,
+    GGML_FTYPE_MOSTLY_MXFP4 = 25,
+    GGML_FTYPE_MOSTLY_NVFP4 = 26,
+    GGML_FTYPE_MOSTLY_Q1_0 = 27
+};
+
 /* Bytes of one encoded row of n_per_row elements; 0 if the type has no row encoding or
  * n_per_row is not a positive multiple of the type's block size.
  * Replaces upstream csrc/libgguf.cpp:21-88. */

@@ -62,3 +62,33 @@ def test_host_copy_pool_copies_every_byte():
         lib.libgguf_cuda_host_copy(dst.ctypes.data, src.ctypes.data + offset, size)
         assert np.array_equal(dst[:size], src[offset:offset + size])
         assert (dst[size:] == 0xA5).all()
+
+
+def test_public_header_compiles_as_c_and_keeps_upstreams_enums(tmp_path):
+    """A C program written against upstream's include/libgguf.h (:16-100: ggml_type, ggml_prec, ggml_ftype) compiles
+    against this repository's header, links to the library, and sees the same enum values."""
+    import shutil
+    import subprocess
+    from libgguf_b200 import _native
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        import pytest
+        pytest.skip("no C compiler")
+    src = tmp_path / "t.c"
+    src.write_text('''
+#include <stdio.h>
+#include "libgguf.h"
+int main(void) {
+    enum ggml_ftype f = GGML_FTYPE_MOSTLY_Q4_K;
+    enum ggml_prec p = GGML_PREC_F32;
+    printf("%d %d %d %d %d %zu %s\\n", (int)f, (int)p, (int)GGML_FTYPE_UNKNOWN, (int)GGML_FTYPE_MOSTLY_Q1_0, (int)GGML_TYPE_COUNT,
+           libgguf_row_size(GGML_TYPE_Q4_K, 4096), libgguf_type_name(GGML_TYPE_IQ2_XXS));
+    return 0;
+}
+''')
+    exe = tmp_path / "t"
+    lib_dir = _native.LIB_PATH.parent
+    subprocess.run([cc, "-std=c99", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(src), "-o", str(exe),
+                    "-L", str(lib_dir), f"-l:{_native.LIB_PATH.name}", f"-Wl,-rpath,{lib_dir}"], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out == ["12", "10", "-1", "27", "42", "2304", "iq2_xxs"]

@@ -14,6 +14,13 @@ sys.path.insert(0, str(GOLDEN_DIR))
 import converter_models as cm  # noqa: E402
 
 GOLDEN = json.loads((GOLDEN_DIR / "converter_golden.json").read_text())["entries"]
+UPSTREAM_CONVERTER = Path(__file__).parents[1] / "oracle" / "_ref" / "quantize_gguf_ref"
+
+
+@pytest.fixture(scope="module")
+def checker():
+    from oracle import reference
+    return reference.load("ref" if reference.available("ref") else "port")
 
 
 @pytest.fixture(scope="module")
@@ -39,9 +46,47 @@ def test_files_equal_upstreams(gguf, checkpoints, entry, tmp_path, capsys):
     assert capsys.readouterr().out.strip().splitlines()[1:] == gold["summary"]
 
 
-def test_llama_checkpoint_and_load_time_decode(gguf, tmp_path):
+def test_load_time_decode_of_a_file_upstream_wrote(gguf, checker, checkpoints, tmp_path):
+    """A GGUF file written by upstream's own converter (CPU backend): every tensor read with this repository's reader
+    and decoded on the GPU must equal the checker's decode of the stored bytes (fp32 bits; fp16 = its RNE rounding)."""
+    import subprocess
+    torch = pytest.importorskip("torch")
+    if not UPSTREAM_CONVERTER.exists():
+        pytest.skip("oracle/_ref/quantize_gguf_ref not built (make -C oracle converter)")
+    from libgguf_b200.gguf_file import read_gguf
+    from libgguf_b200.libgguf_cuda import load
+    for name, options in (("flux_bf16", ["--qtype", "Q4_K_M"]), ("wan_f16", ["--qtype", "Q3_K_M", "--policy", "dynamic"])):
+        if name not in checkpoints:
+            name = sorted(checkpoints)[0]
+        dst = str(tmp_path / f"{name}-upstream.gguf")
+        subprocess.run([str(UPSTREAM_CONVERTER), "--src", checkpoints[name], "--dst", dst, "--backend", "cpu", "--overwrite"] + options,
+                       check=True, capture_output=True)
+        g = read_gguf(dst, gguf.row_size)
+        decoded = 0
+        for tname, info in g.tensors.items():
+            raw = np.array(g.tensor_bytes(tname))
+            n = info.shape[-1]
+            if info.qtype == 0:
+                want = raw.view(np.float32)
+            elif info.qtype == 1:
+                want = raw.view(np.float16).astype(np.float32)
+            elif info.qtype == 30:
+                want = (raw.view(np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+            else:
+                want = checker.dequantize_rows(raw.reshape(-1, gguf.row_size(info.qtype, n)), info.qtype, n)
+                decoded += 1
+            t = load.load_tensor(g, tname, device="cuda", dtype=torch.float32)
+            assert tuple(t.shape) == info.shape
+            assert np.array_equal(t.cpu().numpy().reshape(-1).view(np.uint32), np.ascontiguousarray(want, np.float32).reshape(-1).view(np.uint32)), tname
+            h = load.load_tensor(g, tname, device="cuda", dtype=torch.float16)
+            assert torch.equal(h.cpu().reshape(-1).view(torch.int16),
+                               torch.from_numpy(np.ascontiguousarray(want, np.float32).reshape(-1)).to(torch.float16).view(torch.int16)), tname
+        assert decoded > 0
+
+
+def test_llama_checkpoint_and_load_time_decode(gguf, checker, tmp_path):
     """Extension types end to end: a Llama-style checkpoint to IQ4_XS / Q4_K_M, read back, decoded on the GPU and
-    compared with decoding the same bytes through the row API."""
+    compared with the checker's decode of the same stored bytes."""
     torch = pytest.importorskip("torch")
     from libgguf_b200 import quantize_gguf as qg
     from libgguf_b200.gguf_file import read_gguf
@@ -57,8 +102,8 @@ def test_llama_checkpoint_and_load_time_decode(gguf, tmp_path):
             info = g.tensors[name]
             t = load.load_tensor(g, name, device="cuda", dtype=torch.float32)
             assert tuple(t.shape) == info.shape
-            want = gguf.dequantize_rows(np.array(g.tensor_bytes(name)).reshape(-1, gguf.row_size(info.qtype, info.shape[-1])), info.qtype,
-                                        info.shape[-1]) if info.qtype not in (0,) else np.array(g.tensor_bytes(name)).view(np.float32)
+            want = checker.dequantize_rows(np.array(g.tensor_bytes(name)).reshape(-1, gguf.row_size(info.qtype, info.shape[-1])), info.qtype,
+                                           info.shape[-1]) if info.qtype not in (0,) else np.array(g.tensor_bytes(name)).view(np.float32)
             assert np.array_equal(t.cpu().numpy().reshape(-1).view(np.uint32), np.asarray(want, dtype=np.float32).reshape(-1).view(np.uint32))
         half = load.load_tensor(g, "lm_head.weight", device="cuda", dtype=torch.float16)
         assert half.dtype == torch.float16 and tuple(half.shape) == (512, 256)

@@ -70,11 +70,21 @@ def test_quantize_on_a_side_stream_and_leading_dims(ops, checker):
     np.testing.assert_array_equal(q.cpu().numpy(), checker.quantize_rows(x, 12))
 
 
-def test_imatrix_is_honoured_for_optional_types(ops, checker):
+def test_optional_imatrix_upstream_behaviour_and_the_weighted_op(ops, checker):
+    """`quantize` is upstream's op: a type that can do without importance weights ignores them
+    (upstream cuda_quantize.cu:37-49); `quantize_weighted` applies them like the CPU quantizer does."""
     x, im = inputs.lattice_matrix(8, 1024)
-    q = ops.quantize(torch.from_numpy(x).cuda(), 12, torch.from_numpy(im).cuda())
-    np.testing.assert_array_equal(q.cpu().numpy(), checker.quantize_rows(x, 12, im))
-    assert not np.array_equal(q.cpu().numpy(), checker.quantize_rows(x, 12))
+    xt, imt = torch.from_numpy(x).cuda(), torch.from_numpy(im).cuda()
+    plain = checker.quantize_rows(x, 12)
+    weighted = checker.quantize_rows(x, 12, im)
+    assert not np.array_equal(plain, weighted)
+    np.testing.assert_array_equal(ops.quantize(xt, 12, imt).cpu().numpy(), plain)
+    np.testing.assert_array_equal(torch.ops._C_gguf.quantize(xt, 12, imt).cpu().numpy(), plain)
+    np.testing.assert_array_equal(ops.quantize_weighted(xt, 12, imt).cpu().numpy(), weighted)
+    # a type that needs the weights reads them through either entry point
+    need = checker.quantize_rows(x, 16, im)
+    np.testing.assert_array_equal(ops.quantize(xt, 16, imt).cpu().numpy(), need)
+    np.testing.assert_array_equal(ops.quantize_weighted(xt, 16, imt).cpu().numpy(), need)
 
 
 def test_argument_rejection(ops):

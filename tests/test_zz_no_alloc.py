@@ -4,9 +4,9 @@ Some users of this library cannot allocate GPU memory when they quantize -- they
 framework that owns the whole device through its own pool, under a fixed memory budget, or in a
 loop that cannot afford an allocator call -- so the library offers one entry point whose scratch
 is a fixed array inside the library.  This test drives it through the C ABI twice in a row and
-requires the bytes to equal those of the regular entry point both times (the array is shared and
-keeps old contents, so the second call is the one that would show stale data), then checks the
-refusals.  The file is named so that pytest collects it after every other test."""
+requires the bytes to equal those of the regular entry point and of the CPU checker both times
+(the array is shared and keeps old contents, so the second call is the one that would show stale
+data), then checks the refusals.  The file is named so that pytest collects it after every other test."""
 import numpy as np
 import pytest
 
@@ -26,8 +26,14 @@ def _quantize(fn_name, x, im, qtype):
     return out.cpu().numpy()
 
 
+@pytest.fixture(scope="module")
+def checker():
+    from oracle import reference
+    return reference.load("ref" if reference.available("ref") else "port")
+
+
 @pytest.mark.parametrize("qtype", [2, 3, 6, 7])
-def test_static_scratch_entry_point_matches_regular_entry_point_twice(qtype):
+def test_static_scratch_entry_point_matches_regular_entry_point_twice(qtype, checker):
     rng = np.random.default_rng(qtype)
     im = torch.from_numpy((rng.chisquare(4, 1024) / 4).astype(np.float32)).cuda()
     # first call: many rows with large values, so that the shared array is left full of big numbers
@@ -38,6 +44,7 @@ def test_static_scratch_entry_point_matches_regular_entry_point_twice(qtype):
         got = _quantize("libgguf_cuda_quantize_weighted_rows_static", x, im, qtype)
         want = _quantize("libgguf_cuda_quantize_f32_rows_on_stream", x, im, qtype)
         np.testing.assert_array_equal(got, want)  # integer bytes: the tolerance of the other parity tests is zero
+        np.testing.assert_array_equal(got, checker.quantize_rows(x.cpu().numpy(), qtype, im.cpu().numpy()))
 
 
 def test_static_scratch_entry_point_refusals():
