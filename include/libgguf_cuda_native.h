@@ -116,11 +116,20 @@ LIBGGUF_CUDA_API const char *libgguf_cuda_thread_last_error(void);
 /* Number of kernels this library has launched in this process (all devices, all threads). */
 LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
 
-/* No upstream counterpart.  The quantizers that stage their input with bulk asynchronous copies bound every wait
- * for a copy; a wait that runs out makes the CTA count it and return (its part of the output is then not written).
- * Stores the count of such events on the current device since the library was loaded; 0 on a healthy device.
- * Blocking (waits for the device). */
+/* No upstream counterpart.  The quantizers that stage their input with bulk asynchronous copies (TQ1_0, TQ2_0, Q1_0)
+ * bound every wait for a copy; a wait that runs out makes the CTA count it, wait once more (bounded) for the copies it
+ * still has in flight and return: its part of the output is then NOT written.  Stores the count of such events on the
+ * current device since the library was loaded; 0 on a healthy device.  Blocking (waits for the device).
+ * The calls of this library that synchronise by themselves -- libgguf_quantize_chunk and the conversion pipeline --
+ * read the counter around their own work and report failure (0 bytes / the shard is redone on another GPU, or the
+ * batch fails) when it moved.  A caller of the asynchronous row functions checks it after its own synchronisation. */
 LIBGGUF_CUDA_API int libgguf_cuda_staging_timeouts(uint64_t *count);
+
+/* Test hook, no upstream counterpart: the number of polling rounds a consumer of a staged tile spends before it gives
+ * up, on the current device.  0 makes every consumer give up at once although its copy is on its way (the kernel then
+ * takes the give-up path: count, drain, return), which is how the tests exercise the failure reporting without
+ * losing a copy; a negative value restores the default.  Blocking. */
+LIBGGUF_CUDA_API int libgguf_cuda_set_staging_wait_limit(int limit);
 
 /* No upstream counterpart.  memcpy split over the library's pool of host copy threads (LIBGGUF_CUDA_COPY_THREADS,
  * default 8 on hosts with 16 or more CPUs); the host-pointer chunk functions of libgguf.h use it to fill and drain

@@ -71,6 +71,7 @@ NATIVE_ABI = {
     "libgguf_cuda_thread_last_error": (c_char_p, []),
     "libgguf_cuda_kernel_launch_count": (c_uint64, []),
     "libgguf_cuda_staging_timeouts": (c_int, [c_void_p]),
+    "libgguf_cuda_set_staging_wait_limit": (c_int, [c_int]),
     "libgguf_cuda_host_copy": (None, [c_void_p, c_void_p, c_size_t]),
     "libgguf_cuda_prepare_qtype": (c_int, [c_int64]),
     "libgguf_cuda_quantize_weighted_rows_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),

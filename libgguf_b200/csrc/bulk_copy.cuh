@@ -1,7 +1,10 @@
 // Bulk asynchronous copies global -> shared (the TMA engine's untiled form, cp.async.bulk) completing on an
 // mbarrier.  One thread issues a copy of any multiple of 16 bytes between 16-byte aligned addresses; the threads
 // that consume the data wait on the barrier's phase.  Every wait is bounded: a copy that does not land within
-// the limit makes the kernel record it in a device-global counter and return instead of spinning.
+// the limit makes the kernel record it in a device-global counter, stop issuing copies, give the copies it still
+// has in flight one more bounded wait each (a CTA must not exit with a bulk copy into its shared memory pending)
+// and return instead of spinning.  The host reads the counter after the stream has been synchronised and reports
+// the call as failed when it moved.
 #pragma once
 
 #include <stdint.h>
@@ -33,9 +36,9 @@ GGUF_D void mbarrier_arrive(uint64_t *bar) {
 // Waits for the phase with parity `parity` to complete; false when the limit ran out.  A try_wait suspends the
 // thread for a hardware-defined time slice, so the limit is many milliseconds, far beyond any copy.
 constexpr int kBulkWaitLimit = 1 << 18;
-GGUF_D bool mbarrier_wait(uint64_t *bar, uint32_t parity) {
+GGUF_D bool mbarrier_wait(uint64_t *bar, uint32_t parity, int limit = kBulkWaitLimit) {
     const uint32_t addr = smem_addr(bar);
-    for (int i = 0; i < kBulkWaitLimit; ++i) {
+    for (int i = 0; i < limit; ++i) {
         uint32_t done;
         asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                      : "=r"(done) : "r"(addr), "r"(parity) : "memory");

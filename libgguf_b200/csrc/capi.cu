@@ -240,6 +240,16 @@ extern "C" size_t libgguf_quantize_chunk(enum ggml_type type, const float *src, 
         state = device_state_for((int)type, dev);
         if (!state) return 0;
     }
+    // bulk-staged quantizers: a CTA that gave up on a staged copy left rows unwritten; the counter tells
+    const bool watch_staging = uses_bulk_staging((int)type);
+    unsigned long long timeouts_before = 0;
+    if (watch_staging && read_staging_timeouts(&timeouts_before) != cudaSuccess) { cudaGetLastError(); return 0; }
+    auto staging_ok = [&]() {
+        if (!watch_staging) return true;
+        unsigned long long now = 0;
+        if (read_staging_timeouts(&now) != cudaSuccess) { cudaGetLastError(); return false; }
+        return now == timeouts_before;
+    };
     const size_t in_row = (size_t)n_per_row * 4;
     const float *d_im = nullptr;
     if (imatrix && !storage) {
@@ -257,7 +267,7 @@ extern "C" size_t libgguf_quantize_chunk(enum ggml_type type, const float *src, 
                 return launch_quantize((int)type, (const float *)d_in, d_im, d_out, nr, n_per_row, state, stream);
             });
         if (err != cudaSuccess) { cudaGetLastError(); return 0; }
-        return (size_t)nrows * row_size;
+        return staging_ok() ? (size_t)nrows * row_size : 0;
     }
     int64_t rows_per_piece = (int64_t)(kStageBytes / in_row);
     if (rows_per_piece < 1) rows_per_piece = 1;
@@ -275,7 +285,7 @@ extern "C" size_t libgguf_quantize_chunk(enum ggml_type type, const float *src, 
         if (err == cudaSuccess) err = cudaStreamSynchronize(st.stream);
         if (err != cudaSuccess) { cudaGetLastError(); return 0; }
     }
-    return (size_t)nrows * row_size;
+    return staging_ok() ? (size_t)nrows * row_size : 0;
 }
 
 extern "C" size_t libgguf_dequantize_chunk(enum ggml_type type, const void *src, float *dst, int64_t start, int64_t nrows,

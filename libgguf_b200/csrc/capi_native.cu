@@ -36,7 +36,6 @@ using namespace gguf;
 namespace gguf {
 cudaError_t selftest_fp4(float e, int mode, int ebyte, unsigned long long *device_counters, cudaStream_t stream);
 int64_t static_scratch_max_rows();
-cudaError_t read_staging_timeouts(unsigned long long *count);
 cudaError_t launch_quantize_legacy_weighted_static(int type, const float *src, const float *qw, void *dst, int64_t nrows,
                                                    int64_t n_per_row, cudaStream_t stream);
 }  // namespace gguf
@@ -187,6 +186,12 @@ int libgguf_cuda_staging_timeouts(uint64_t *count) {
     const cudaError_t error = gguf::read_staging_timeouts(&value);
     if (error != cudaSuccess) return cuda_fail(nullptr, error);
     *count = value;
+    return ok(nullptr);
+}
+
+int libgguf_cuda_set_staging_wait_limit(int limit) {
+    const cudaError_t error = gguf::set_staging_wait_limit(limit);
+    if (error != cudaSuccess) return cuda_fail(nullptr, error);
     return ok(nullptr);
 }
 

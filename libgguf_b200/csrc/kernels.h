@@ -17,6 +17,14 @@ bool quantize_supported(int type);
 cudaError_t launch_sumsq_columns(const float *rows, int64_t nrows, int64_t n, float *acc, cudaStream_t stream);
 cudaError_t launch_widen(int src_dtype, const void *src, float *dst, int64_t n, cudaStream_t stream);
 
+// Quantizers that stage their input with bulk asynchronous copies (TQ1_0, TQ2_0, Q1_0) count, on the device, the
+// waits for a copy that ran out; a CTA that gave up leaves its part of the output unwritten.  Host paths that
+// synchronise the stream read the counter of the current device before and after and fail the call when it moved.
+bool uses_bulk_staging(int type);
+cudaError_t read_staging_timeouts(unsigned long long *count);
+// limit < 0 restores the default; 0 makes every consumer give up at once (test hook, current device)
+cudaError_t set_staging_wait_limit(int limit);
+
 // Launch accounting (exposed through libgguf_cuda_kernel_launch_count).
 void count_launch();
 

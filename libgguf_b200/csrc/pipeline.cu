@@ -123,6 +123,7 @@ struct Batch {
     std::string error;
     bool failed = false;
     std::vector<char> worker_failed;
+    bool any_bulk_staged = false;  // some tensor's quantizer stages its input with bulk copies (see kernels.h)
 };
 
 bool grow_dev(void **p, size_t *cap, size_t need) {
@@ -225,10 +226,27 @@ void worker(libgguf_cuda_pipeline *pipe, Batch *batch, int widx) {
     }
     if (!ok) err = "failed to set up streams on device " + std::to_string(dev);
     const auto t_begin = std::chrono::steady_clock::now();
+    // the device's count of staged copies that never arrived, as it stood before this worker's first shard
+    unsigned long long timeouts_before = 0;
+    if (ok && batch->any_bulk_staged && read_staging_timeouts(&timeouts_before) != cudaSuccess) {
+        cudaGetLastError();
+        ok = false;
+        err = "cannot read the staging counter of device " + std::to_string(dev);
+    }
 
     auto finish = [&](Slot &s) -> bool {
         if (!s.busy) return true;
         if (!wait_slot(s, pipe->wait_timeout_ms, err)) return false;
+        if (uses_bulk_staging((int)batch->tensors[s.shard.tensor].qtype)) {
+            // a CTA that gave up on a staged copy returned without writing its rows: the shard has to be redone
+            unsigned long long now = 0;
+            if (read_staging_timeouts(&now) != cudaSuccess || now != timeouts_before) {
+                cudaGetLastError();
+                err = "a staged copy did not arrive within its wait limit on device " + std::to_string(dev) +
+                      " (libgguf_cuda_staging_timeouts); the shard's output is incomplete";
+                return false;
+            }
+        }
         if (s.copy_out_to) std::memcpy(s.copy_out_to, s.h_out, s.shard.out_bytes);
         s.busy = false;
         s.copy_out_to = nullptr;
@@ -453,6 +471,7 @@ int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libg
     batch.src_pinned.resize(n_tensors);
     batch.dst_pinned.resize(n_tensors);
     for (int i = 0; i < n_tensors; ++i) {
+        batch.any_bulk_staged = batch.any_bulk_staged || uses_bulk_staging((int)tensors[i].qtype);
         batch.src_pinned[i] = is_pinned(tensors[i].src);
         batch.dst_pinned[i] = is_pinned(tensors[i].dst);
     }

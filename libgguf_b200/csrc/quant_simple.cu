@@ -607,6 +607,10 @@ constexpr int kTernBlocks = kTernThreads / 8;   // blocks per tile
 
 // Copies that did not land within the wait limit, all launches of this process on the device.
 __device__ unsigned long long g_staging_timeouts;
+// try_wait rounds a consumer spends on a staged tile before it gives up.  The host can lower it (down to 0: give up
+// at once) so that the give-up path can be exercised without a copy that is really lost; the drain waits keep the
+// full limit.
+__device__ int g_staging_wait_limit = kBulkWaitLimit;
 
 // TQ1_0 / TQ2_0: 256-element blocks, d = max |x| (upstream tq1_0.cpp:16-98, tq2_0.cpp:16-53).
 // Persistent CTAs walk tiles of sixteen blocks (16 KB, contiguous) with a stride of the grid size; one thread
@@ -642,14 +646,19 @@ __global__ void __launch_bounds__(kTernThreads) quant_ternary_kernel(const float
     int64_t t = blockIdx.x;
     grid_dependents_may_launch();
     grid_dependency_wait();
+    const int wait_limit = g_staging_wait_limit;
     if (t < ntiles && threadIdx.x == 0) prefetch(t, 0);
     for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
         const int64_t tnext = t + gridDim.x;
         if (tnext < ntiles && threadIdx.x == 0) prefetch(tnext, (it + 1) & 1);
         // slot it & 1 is on its (it / 2)-th use: wait for that phase
-        const bool arrived = mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u);
+        const bool arrived = mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u, wait_limit);
         // also orders the previous tile's flush before this tile's writes to the stage
         if (!__syncthreads_and(arrived)) {
+            // Gave up: no further copies are issued.  Two may still be in flight, this tile's and the next one's;
+            // each gets one more bounded wait before the CTA leaves its shared memory behind.
+            mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u);
+            if (tnext < ntiles) mbarrier_wait(&landed[(it + 1) & 1], (uint32_t)((it + 1) >> 1) & 1u);
             if (threadIdx.x == 0) atomicAdd(&g_staging_timeouts, 1ull);
             return;
         }
@@ -790,12 +799,16 @@ __global__ void __launch_bounds__(32) quant_q1_kernel(const float *__restrict__ 
     int64_t t = blockIdx.x;
     grid_dependents_may_launch();
     grid_dependency_wait();
+    const int wait_limit = g_staging_wait_limit;
     if (t < ntiles) prefetch(t, 0);
     for (int it = 0; t < ntiles; t += gridDim.x, ++it) {
         const int64_t tnext = t + gridDim.x;
         if (tnext < ntiles) prefetch(tnext, (it + 1) & 1);
-        const bool arrived = mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u);
+        const bool arrived = mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u, wait_limit);
         if (!__all_sync(kFull, arrived)) {
+            // as in the ternary kernel: stop, wait once more (bounded) for the copies of both slots, then leave
+            mbarrier_wait(&landed[it & 1], (uint32_t)(it >> 1) & 1u);
+            if (tnext < ntiles) mbarrier_wait(&landed[(it + 1) & 1], (uint32_t)((it + 1) >> 1) & 1u);
             if (lane == 0) atomicAdd(&g_staging_timeouts, 1ull);
             return;
         }
@@ -882,6 +895,13 @@ cudaError_t launch32(const float *src, void *dst, int64_t nelems, const float *m
 cudaError_t read_staging_timeouts(unsigned long long *count) {
     return cudaMemcpyFromSymbol(count, g_staging_timeouts, sizeof(*count));
 }
+
+cudaError_t set_staging_wait_limit(int limit) {
+    const int value = limit < 0 ? kBulkWaitLimit : limit;
+    return cudaMemcpyToSymbol(g_staging_wait_limit, &value, sizeof(value));
+}
+
+bool uses_bulk_staging(int type) { return type == GGML_TYPE_TQ1_0 || type == GGML_TYPE_TQ2_0 || type == GGML_TYPE_Q1_0; }
 
 cudaError_t launch_store(int type, const float *src, void *dst, int64_t nelems, cudaStream_t stream) {
     if (nelems <= 0) return cudaSuccess;

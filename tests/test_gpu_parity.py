@@ -272,12 +272,51 @@ def test_large_host_calls_go_through_the_pinned_ring_in_ragged_pieces(gguf, chec
 
 def test_bulk_copy_staging_never_ran_out_of_its_wait_limit(gguf):
     """The ternary quantizers stage their input with bulk asynchronous copies whose waits are bounded; a wait that
-    gives up is counted on the device.  After a pass over a ragged number of blocks the count must still be zero."""
+    gives up is counted on the device.  A pass over a ragged number of blocks must not move the count."""
     import ctypes
     from libgguf_b200._native import lib
+    before, count = ctypes.c_uint64(123), ctypes.c_uint64(123)
+    assert lib.libgguf_cuda_staging_timeouts(ctypes.byref(before)) == 0
     x = np.random.default_rng(5).standard_normal((1237, 768), dtype=np.float32)
-    for name in ("TQ1_0", "TQ2_0"):
+    for name in ("TQ1_0", "TQ2_0", "Q1_0"):
         gguf.quantize_rows(x, inputs.QTYPES[name])
-    count = ctypes.c_uint64(123)
     assert lib.libgguf_cuda_staging_timeouts(ctypes.byref(count)) == 0
-    assert count.value == 0
+    assert count.value == before.value
+
+
+@pytest.mark.parametrize("name", ["TQ1_0", "TQ2_0", "Q1_0"])
+def test_a_staged_copy_that_is_given_up_on_fails_the_call_instead_of_returning_partial_rows(gguf, checker, name):
+    """The consumers' wait limit is set to zero polling rounds, so every CTA gives up on its first tile although the
+    copy is on its way: the kernel counts it, waits (bounded, full limit) for the copies it has in flight and returns
+    without writing its rows.  Nothing hangs or faults, the context stays usable, and the host-pointer call and the
+    conversion pipeline must report failure rather than hand back unwritten bytes."""
+    import ctypes
+    from libgguf_b200._native import lib
+    from libgguf_b200.convert import ConversionPipeline
+    qtype = inputs.QTYPES[name]
+    x = np.random.default_rng(8).standard_normal((257, 1024), dtype=np.float32)
+    want = checker.quantize_rows(x, qtype)
+    before, after = ctypes.c_uint64(), ctypes.c_uint64()
+    assert lib.libgguf_cuda_staging_timeouts(ctypes.byref(before)) == 0
+    assert lib.libgguf_cuda_set_staging_wait_limit(0) == 0
+    try:
+        with pytest.raises(RuntimeError, match="wrote 0 bytes"):
+            gguf.quantize_rows(x, qtype)
+        assert lib.libgguf_cuda_staging_timeouts(ctypes.byref(after)) == 0
+        assert after.value > before.value
+        dst = np.zeros(want.size, np.uint8)
+        with ConversionPipeline([0], slots=2, chunk_bytes=256 << 10) as pipe:
+            with pytest.raises(RuntimeError, match="did not arrive within its wait limit"):
+                pipe.quantize([(qtype, x, None, dst)])
+    finally:
+        assert lib.libgguf_cuda_set_staging_wait_limit(-1) == 0
+    # the default limit is back: same device, same context, correct bytes
+    np.testing.assert_array_equal(gguf.quantize_rows(x, qtype), want)
+    dst = np.zeros(want.size, np.uint8)
+    with ConversionPipeline([0], slots=2, chunk_bytes=256 << 10) as pipe:
+        pipe.quantize([(qtype, x, None, dst)])
+    np.testing.assert_array_equal(dst.reshape(want.shape), want)
+    final = ctypes.c_uint64()
+    assert lib.libgguf_cuda_staging_timeouts(ctypes.byref(final)) == 0
+    # the pipeline's attempt under the zero limit added its own give-ups; the healthy calls added none
+    assert final.value >= after.value
