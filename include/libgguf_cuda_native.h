@@ -184,6 +184,12 @@ LIBGGUF_CUDA_API int libgguf_cuda_quantize_rows_from_on_stream(const void *devic
 LIBGGUF_CUDA_API int libgguf_cuda_accumulate_imatrix_on_stream(const float *device_rows, int64_t rows, int64_t n_per_row,
                                                                float *device_imatrix, void *stream);
 LIBGGUF_CUDA_API int libgguf_cuda_auto_imatrix(const float *host_rows, int64_t rows, int64_t n_per_row, float *host_imatrix);
+/* The same for a host matrix of F32, F16 or BF16 values (LIBGGUF_CUDA_DEQUANTIZE_DTYPE_* codes; 16-bit values cross the
+ * host link as they are and are widened on the GPU).  A caller that quantizes one tensor in several row pieces -- the
+ * converter front end, or one process per GPU each taking a row range -- calls this once for the WHOLE tensor and passes
+ * the result as the imatrix of every piece, so that the encoded bytes do not depend on how the tensor was cut. */
+LIBGGUF_CUDA_API int libgguf_cuda_auto_imatrix_typed(const void *host_rows, int source_dtype, int64_t rows, int64_t n_per_row,
+                                                     float *host_imatrix);
 
 /* ---- multi-GPU streaming conversion (replaces the single-GPU two-slot loop of upstream's converter,
  * csrc/quantize_gguf.cpp:1732-1931 and :2072-2146; the pool itself has no upstream counterpart) ----

@@ -89,6 +89,7 @@ NATIVE_ABI = {
     "libgguf_cuda_device_count": (c_int, [POINTER(c_int)]),
     "libgguf_cuda_accumulate_imatrix_on_stream": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
     "libgguf_cuda_auto_imatrix": (c_int, [c_void_p, c_int64, c_int64, c_void_p]),
+    "libgguf_cuda_auto_imatrix_typed": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p]),
     "libgguf_cuda_widen_on_stream": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p]),
     "libgguf_cuda_quantize_rows_from_on_stream": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "libgguf_cuda_pipeline_plan": (c_int64, [POINTER(TensorDesc), c_int, c_size_t, POINTER(ShardDesc), c_int64]),

@@ -115,6 +115,20 @@ class ConversionPipeline:
         return {"shards_per_device": list(shards), "seconds_per_device": list(secs), "requeued": requeued.value}
 
 
+def whole_tensor_imatrix(src: np.ndarray) -> np.ndarray:
+    """Column sums of squares over ALL rows of a 2-D source (float32, float16, or uint16 holding bfloat16 bits), added
+    in row order on the GPU: the importance weights upstream derives for a type that requires them when the caller
+    has none (upstream csrc/_libgguf_module.cpp:1210-1242, src/libgguf/__init__.py:186-189).  Whoever cuts a tensor into
+    row pieces computes this once and hands it to every piece."""
+    if src.dtype not in SOURCE_DTYPES or src.ndim != 2 or not src.flags.c_contiguous:
+        raise ValueError("src must be a C-contiguous 2-D array of float32, float16, or uint16 holding bfloat16 bits")
+    out = np.zeros(src.shape[1], dtype=np.float32)
+    status = lib.libgguf_cuda_auto_imatrix_typed(src.ctypes.data, SOURCE_DTYPES[src.dtype], src.shape[0], src.shape[1], out.ctypes.data)
+    if status != 0:
+        raise RuntimeError(f"libgguf_cuda_auto_imatrix_typed failed with status {status}")
+    return out
+
+
 def plan_shards(tensors: list[tuple[int, int, int]], chunk_bytes: int = 128 << 20, source_dtypes=None) -> list[tuple[int, int, int]]:
     """Shard list for tensors given as (qtype, rows, n_per_row); needs no GPU.  Returns (tensor, row0, rows).
     source_dtypes: optional list of 0 (float32), 1 (float16), 2 (bfloat16); a shard holds at most chunk_bytes of source."""
@@ -155,8 +169,15 @@ def rank_batch(tensors, world: int, rank: int, chunk_bytes: int = 128 << 20):
                          [SOURCE_DTYPES[s.dtype] for _, s, _, _ in tensors])
     mine = assign_shards(shards, [s.shape[1] for _, s, _, _ in tensors], world)[rank]
     batch = []
+    derived: dict[int, np.ndarray] = {}
     for tensor, row0, rows in mine:
         qtype, src, imatrix, dst = tensors[tensor]
+        if imatrix is None and lib.libgguf_quantize_requires_imatrix(int(qtype)) and rows != src.shape[0]:
+            # a row range of a tensor whose type needs importance weights: they come from the whole tensor, which
+            # every rank can compute for itself (no exchange), never from the rank's own slice
+            if tensor not in derived:
+                derived[tensor] = whole_tensor_imatrix(src)
+            imatrix = derived[tensor]
         rs = row_size(qtype, src.shape[1])
         batch.append((qtype, src[row0:row0 + rows], imatrix, dst[row0 * rs:(row0 + rows) * rs]))
     return batch

@@ -22,6 +22,7 @@
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <mutex>
@@ -155,13 +156,12 @@ bool wait_slot(Slot &s, int timeout_ms, std::string &err) {
     }
 }
 
-// Streams one tensor through the first GPU in row pieces and accumulates its column sums of squares in order.
-bool auto_imatrix_pass(libgguf_cuda_pipeline *pipe, const libgguf_cuda_tensor_desc &t, int dtype, float *out, std::string &err) {
-    const int dev = pipe->devices[0];
+// Streams one tensor through GPU `dev` in row pieces and accumulates its column sums of squares in order.
+bool auto_imatrix_pass(int dev, size_t chunk_bytes, const libgguf_cuda_tensor_desc &t, int dtype, float *out, std::string &err) {
     if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); err = "cannot select device " + std::to_string(dev); return false; }
     const size_t esz = dtype != LIBGGUF_CUDA_DEQUANTIZE_DTYPE_F32 ? 2 : 4;
     const size_t row_bytes = (size_t)t.n_per_row * esz;
-    int64_t piece = (int64_t)(pipe->chunk_bytes / row_bytes);
+    int64_t piece = (int64_t)(chunk_bytes / row_bytes);
     if (piece < 1) piece = 1;
     cudaStream_t stream = nullptr;
     void *d_src[2] = {nullptr, nullptr}, *d_wide = nullptr, *h_stage[2] = {nullptr, nullptr};
@@ -458,7 +458,7 @@ int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libg
         }
         auto_weights[i].assign((size_t)tensors[i].n_per_row, 0.f);
         std::string err;
-        if (!auto_imatrix_pass(pipe, tensors[i], source_dtypes ? source_dtypes[i] : 0, auto_weights[i].data(), err)) {
+        if (!auto_imatrix_pass(pipe->devices[0], pipe->chunk_bytes, tensors[i], source_dtypes ? source_dtypes[i] : 0, auto_weights[i].data(), err)) {
             pipe->last_error = err;
             return LIBGGUF_CUDA_STATUS_CUDA_ERROR;
         }
@@ -510,6 +510,22 @@ int libgguf_cuda_pipeline_quantize_typed(libgguf_cuda_pipeline *pipe, const libg
         return LIBGGUF_CUDA_STATUS_CUDA_ERROR;
     }
     return LIBGGUF_CUDA_STATUS_SUCCESS;
+}
+
+int libgguf_cuda_auto_imatrix_typed(const void *host_rows, int source_dtype, int64_t rows, int64_t n_per_row, float *host_imatrix) {
+    if (rows < 0 || n_per_row <= 0 || !host_imatrix || (rows > 0 && !host_rows) || !source_dtypes_valid(&source_dtype, 1))
+        return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;
+    int dev = 0;
+    const char *env = getenv("LIBGGUF_CUDA_DEVICE");
+    if (env && env[0]) dev = atoi(env);
+    else if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return LIBGGUF_CUDA_STATUS_CUDA_ERROR; }
+    libgguf_cuda_tensor_desc t = {};
+    t.src = (const float *)host_rows;
+    t.rows = rows;
+    t.n_per_row = n_per_row;
+    std::string err;
+    return auto_imatrix_pass(dev, size_t(64) << 20, t, source_dtype, host_imatrix, err) ? LIBGGUF_CUDA_STATUS_SUCCESS
+                                                                                       : LIBGGUF_CUDA_STATUS_CUDA_ERROR;
 }
 
 int libgguf_cuda_pipeline_stats(const libgguf_cuda_pipeline *pipe, int64_t *shards_per_device, double *seconds_per_device,

@@ -593,7 +593,7 @@ def convert(options: Options) -> dict:
     import time
 
     from ._native import lib
-    from .convert import ConversionPipeline   # needs the CUDA library; planning above does not
+    from .convert import ConversionPipeline, whole_tensor_imatrix   # needs the CUDA library; planning above does not
 
     clock = time.perf_counter
     began = clock()
@@ -615,6 +615,10 @@ def convert(options: Options) -> dict:
         fail("no CUDA device is available")
     # two pinned arenas per direction; large enough to keep every GPU's slots busy, small enough to allocate quickly
     cap = max(1 << 16, min(options.batch_bytes // 4, max(256 << 20, n_gpus * (128 << 20))))
+    # a piece is at least one row: the arenas must hold the widest row of the plan on either side
+    for p in plans:
+        if p.qtype != p.source_dtype:
+            cap = max(cap, _align(p.n_per_row * SOURCE_DTYPES[p.source_dtype][2]), _align(p.nbytes // p.n_rows))
     chunk = max(1 << 12, min(options.chunk_bytes, cap // (3 * n_gpus)))
     arenas, fd = [], os.open(options.src, os.O_RDONLY)
     readers = ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1))
@@ -645,15 +649,29 @@ def convert(options: Options) -> dict:
             for start in range(0, nbytes_in, READ_PIECE):
                 futures.append(readers.submit(read_into, raw[start:min(start + READ_PIECE, nbytes_in)], file_at + start))
             enc = arena_out.array[at_out:at_out + nbytes_out]
-            entries.append((int(Q[p.qtype]), raw.view(np_dtype).reshape(piece.rows, p.n_per_row), None, enc))
+            entries.append((int(Q[p.qtype]), raw.view(np_dtype).reshape(piece.rows, p.n_per_row), split_weights.get(p.key), enc))
             outputs.append(enc)
             at_in += _align(nbytes_in)
             at_out += _align(nbytes_out)
         return entries, outputs, futures
 
     counts = {"cuda_chunks": 0, "cuda_max_input": 0, "cuda_max_output": 0}
+    split_weights: dict[str, np.ndarray] = {}
+    finished = False
     try:
-        batches = list(_batches(_pieces(plans, cap), cap))
+        pieces = list(_pieces(plans, cap))
+        # A type that needs importance weights derives them from the WHOLE tensor (upstream compute_auto_imatrix,
+        # csrc/_libgguf_module.cpp:1210-1242).  A tensor that goes through in one piece gets them inside the pipeline;
+        # one that was cut gets them here, once, from the mapped source, and every piece is encoded with them, so the
+        # bytes do not depend on --gpus or --batch-mb.
+        for piece in pieces:
+            p = piece.plan
+            if piece.convert and not (piece.row0 == 0 and piece.last) and p.key not in split_weights \
+                    and lib.libgguf_quantize_requires_imatrix(int(Q[p.qtype])):
+                np_dtype = SOURCE_DTYPES[p.source_dtype][0]
+                whole = source[p.data_begin:p.data_end].view(np_dtype).reshape(p.n_rows, p.n_per_row)
+                split_weights[p.key] = whole_tensor_imatrix(whole)
+        batches = list(_batches(pieces, cap))
         arenas = [(_PinnedArena(lib, ctx, cap + 4096), _PinnedArena(lib, ctx, cap + 4096)) for _ in range(min(2, len(batches)))]
         with open(dst, "wb") as out, ConversionPipeline(list(range(n_gpus)), slots=3, chunk_bytes=chunk) as pipe:
             out.write(head)
@@ -682,7 +700,13 @@ def convert(options: Options) -> dict:
                     counts["cuda_chunks"] += 1
                     counts["cuda_max_input"] = max(counts["cuda_max_input"], entry[1].nbytes)
                     counts["cuda_max_output"] = max(counts["cuda_max_output"], entry[3].nbytes)
+        finished = True
     finally:
+        if not finished:   # never leave a half-written file behind
+            try:
+                os.unlink(dst)
+            except OSError:
+                pass
         readers.shutdown(wait=True)
         os.close(fd)
         for pair in arenas:

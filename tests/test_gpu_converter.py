@@ -124,3 +124,71 @@ def test_timings_line_has_upstreams_tokens(gguf, tmp_path, capsys):
                             "cuda_max_output"]
     assert all(re.fullmatch(r"\d+\.\d{3}s", tokens[k]) for k in list(tokens)[:8])
     assert int(tokens["tensors"]) >= int(tokens["cuda_tensors"]) > 0 and int(tokens["cuda_chunks"]) > 0
+
+
+def test_tensor_cut_into_pieces_keeps_whole_tensor_importance_weights(gguf, checker, tmp_path):
+    """IQ2_XXS needs importance weights; without an imatrix file they are the column sums of squares of the WHOLE tensor
+    (upstream compute_auto_imatrix, csrc/_libgguf_module.cpp:1210-1242).  A small --batch-mb cuts the 768-row tensors into
+    two pieces: the file must be byte-identical to the uncut conversion, and the cut tensor's bytes equal the checker's."""
+    from libgguf_b200 import quantize_gguf as qg
+    from libgguf_b200.gguf_file import read_gguf
+    tensors = cm.llama_like(layers=2)
+    src = str(tmp_path / "llama.safetensors")
+    cm.write_safetensors(src, tensors)
+    cut, whole = str(tmp_path / "cut.gguf"), str(tmp_path / "whole.gguf")
+    assert qg.main(["--src", src, "--dst", cut, "--qtype", "IQ2_XXS", "--gpus", "1", "--batch-mb", "1", "--chunk-mb", "1"]) == 0
+    assert qg.main(["--src", src, "--dst", whole, "--qtype", "IQ2_XXS", "--gpus", "1"]) == 0
+    assert Path(cut).read_bytes() == Path(whole).read_bytes()
+    g = read_gguf(cut, gguf.row_size)
+    name = "model.layers.1.mlp.gate_proj.weight"
+    values = dict((n, v) for n, _, v in tensors)[name]
+    bf16 = (values.astype(np.float32).view(np.uint32) >> 16).astype(np.uint32) << 16
+    widened = bf16.view(np.float32)
+    info = g.tensors[name]
+    assert info.qtype == 16 and info.shape == (768, 256)
+    np.testing.assert_array_equal(np.array(g.tensor_bytes(name)).reshape(768, -1), checker.quantize_rows(widened, 16))
+
+
+def test_rank_slices_of_a_tensor_use_the_whole_tensors_importance_weights(gguf, checker):
+    """One process per GPU: each rank encodes a row range.  For a type that needs importance weights and has none, every
+    rank derives them from the whole tensor, so the assembled bytes equal the single-call result."""
+    from libgguf_b200.convert import ConversionPipeline, rank_batch
+    x = np.random.default_rng(12).standard_normal((900, 512), dtype=np.float32)
+    want = checker.quantize_rows(x, 19)   # IQ1_S, weights = column sums of squares over all 900 rows
+    dst = np.zeros(want.size, np.uint8)
+    for rank in range(2):
+        batch = rank_batch([(19, x, None, dst)], 2, rank, chunk_bytes=256 << 10)
+        assert batch and all(im is not None for _, _, im, _ in batch)
+        with ConversionPipeline([0], slots=2, chunk_bytes=128 << 10) as pipe:
+            pipe.quantize(batch)
+    np.testing.assert_array_equal(dst.reshape(want.shape), want)
+
+
+def test_a_row_wider_than_the_batch_still_converts_and_failures_leave_no_file(gguf, checker, tmp_path):
+    from libgguf_b200 import quantize_gguf as qg
+    from libgguf_b200.gguf_file import read_gguf
+    rng = np.random.default_rng(3)
+    wide = (rng.standard_normal((3, 131072)) * 0.05).astype(np.float32)    # 512 KiB per row, batch arena 256 KiB
+    src = str(tmp_path / "wide.safetensors")
+    cm.write_safetensors(src, [("model.layers.0.mlp.down_proj.weight", "F32", wide), ("model.norm.weight", "F32", wide[0, :256])])
+    dst = str(tmp_path / "wide.gguf")
+    assert qg.main(["--src", src, "--dst", dst, "--qtype", "Q8_0", "--gpus", "1", "--batch-mb", "1"]) == 0
+    g = read_gguf(dst, gguf.row_size)
+    name = "model.layers.0.mlp.down_proj.weight"
+    np.testing.assert_array_equal(np.array(g.tensor_bytes(name)).reshape(3, -1), checker.quantize_rows(wide, 8))
+    # a conversion that fails half way removes what it had written
+    broken = str(tmp_path / "broken.gguf")
+    import libgguf_b200.convert as conv
+
+    class Failing(conv.ConversionPipeline):
+        def quantize(self, tensors):
+            raise RuntimeError("injected")
+
+    original = conv.ConversionPipeline
+    conv.ConversionPipeline = Failing
+    try:
+        with pytest.raises(RuntimeError, match="injected"):
+            qg.convert(qg.parse_args(["--src", src, "--dst", broken, "--qtype", "Q8_0", "--gpus", "1"]))
+    finally:
+        conv.ConversionPipeline = original
+    assert not Path(broken).exists()
