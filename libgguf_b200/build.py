@@ -76,7 +76,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
             list(pool.map(run, jobs))
     if jobs or not OUT.exists():
-        link = [nvcc, "-shared", "-o", str(OUT), *map(str, objects), "-cudart", "static", "-lpthread"]
+        # -Bsymbolic-functions: calls between this library's own exported functions stay inside it even when a
+        # program also links the upstream CPU library, which exports the same seven host-pointer names
+        link = [nvcc, "-shared", "-o", str(OUT), *map(str, objects), "-cudart", "static", "-lpthread",
+                "-Xlinker", "-Bsymbolic-functions"]
         run(link)
     return OUT
 

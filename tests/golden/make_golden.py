@@ -17,6 +17,7 @@ The tests check the oracle and the CUDA path against both files.
 from __future__ import annotations
 
 import argparse
+import os
 import hashlib
 import json
 import sys
@@ -39,8 +40,11 @@ def sha(a) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--upstream", default="/root/reference")
+    ap.add_argument("--upstream", default=os.environ.get("LIBGGUF_UPSTREAM_ROOT"),
+                    help="the upstream libgguf checkout (default: $LIBGGUF_UPSTREAM_ROOT)")
     args = ap.parse_args()
+    if not args.upstream:
+        ap.error("--upstream PATH (or LIBGGUF_UPSTREAM_ROOT) is required")
     manifest = json.loads((Path(args.upstream) / "tests/golden/manifest.json").read_text())
     entries = [{k: e[k] for k in ("qtype", "shape", "pattern", "encoded_nbytes", "encoded_sha256")} for e in manifest["entries"]]
     (HERE / "upstream_manifest.json").write_text(json.dumps({"source": "upstream tests/golden/manifest.json", "entries": entries}, indent=1) + "\n")
