@@ -125,6 +125,15 @@ LIBGGUF_CUDA_API uint64_t libgguf_cuda_kernel_launch_count(void);
  * batch fails) when it moved.  A caller of the asynchronous row functions checks it after its own synchronisation. */
 LIBGGUF_CUDA_API int libgguf_cuda_staging_timeouts(uint64_t *count);
 
+/* Checked mode, no upstream counterpart.  With LIBGGUF_B200_CHECKED=1 in the environment when the library is loaded,
+ * libgguf_quantize_chunk and libgguf_dequantize_chunk run every piece on the single-buffer path with 4 KiB guard bands
+ * directly before and after the device bytes a kernel may write (filled with a pattern before the launch, compared
+ * after it) and a band of 0xFF bytes directly after the device input (a read past the end then changes the result).
+ * Stores the number of guard bytes found changed since the library was loaded; returns LIBGGUF_CUDA_STATUS_SUCCESS
+ * when the mode is on and LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE (count 0) when it is off.  Nothing traps: it is the
+ * substitute for a memory checker where none can be run, used by the tests on ragged shapes. */
+LIBGGUF_CUDA_API int libgguf_cuda_checked_violations(uint64_t *count);
+
 /* Test hook, no upstream counterpart: the number of polling rounds a consumer of a staged tile spends before it gives
  * up, on the current device.  0 makes every consumer give up at once although its copy is on its way (the kernel then
  * takes the give-up path: count, drain, return), which is how the tests exercise the failure reporting without

@@ -72,6 +72,7 @@ NATIVE_ABI = {
     "libgguf_cuda_kernel_launch_count": (c_uint64, []),
     "libgguf_cuda_staging_timeouts": (c_int, [c_void_p]),
     "libgguf_cuda_set_staging_wait_limit": (c_int, [c_int]),
+    "libgguf_cuda_checked_violations": (c_int, [POINTER(c_uint64)]),
     "libgguf_cuda_host_copy": (None, [c_void_p, c_void_p, c_size_t]),
     "libgguf_cuda_prepare_qtype": (c_int, [c_int64]),
     "libgguf_cuda_quantize_weighted_rows_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),

@@ -159,6 +159,31 @@ extern "C" bool libgguf_quantize_requires_imatrix(enum ggml_type type) { return 
 // host-pointer chunk functions
 namespace {
 
+// ---- checked mode (LIBGGUF_B200_CHECKED=1) ------------------------------------------------------------------
+// The stand-in for a memory checker on hosts where none can be run: the host-pointer calls put guard bands of
+// kGuard bytes directly before and after the bytes a kernel may touch.  The bands around an output are filled with
+// a pattern before the launch and compared after it (a write outside the payload changes them); the band after an
+// input is filled with 0xFF (NaN patterns), so a read past the end changes the result and shows up in a byte
+// comparison with the CPU reference.  A violation is counted in a status word the host reads
+// (libgguf_cuda_checked_violations); nothing traps.  Large calls stay on the single-buffer path in this mode.
+constexpr size_t kGuard = 4096;
+constexpr unsigned char kGuardByte = 0xC5;
+std::atomic<uint64_t> g_guard_violations{0};
+
+bool checked_mode() {
+    static const bool on = [] {
+        const char *env = getenv("LIBGGUF_B200_CHECKED");
+        return env && env[0] && env[0] != '0';
+    }();
+    return on;
+}
+
+__global__ void guard_count_kernel(const unsigned char *front, const unsigned char *back, unsigned long long *bad) {
+    unsigned n = 0;
+    for (unsigned i = threadIdx.x; i < kGuard; i += blockDim.x) n += (front[i] != kGuardByte) + (back[i] != kGuardByte);
+    if (n) atomicAdd(bad, (unsigned long long)n);
+}
+
 // Grow-only staging buffers of one device for the host-pointer calls.
 struct HostCallStaging {
     std::mutex lock;
@@ -170,10 +195,27 @@ struct HostCallStaging {
     size_t im_cap = 0;
     cudaStream_t stream = nullptr;
     StageRing ring;  // large calls: pinned slots, host copies overlapped with the device
+    unsigned long long *d_bad = nullptr;  // checked mode: guard bytes found changed
+
+    // checked mode: read and clear the device counter after the stream has been synchronised
+    void collect_violations() {
+        if (!d_bad) return;
+        unsigned long long bad = 0;
+        if (cudaMemcpy(&bad, d_bad, sizeof(bad), cudaMemcpyDeviceToHost) == cudaSuccess && bad) {
+            g_guard_violations.fetch_add(bad);
+            cudaMemset(d_bad, 0, sizeof(bad));
+        }
+    }
+    bool ensure_counter() {
+        if (!checked_mode() || d_bad) return true;
+        if (cudaMalloc((void **)&d_bad, sizeof(*d_bad)) != cudaSuccess) { cudaGetLastError(); return false; }
+        return cudaMemset(d_bad, 0, sizeof(*d_bad)) == cudaSuccess;
+    }
 };
 HostCallStaging g_staging[kMaxDevices];
 
 bool grow(void **p, size_t *cap, size_t need) {
+    if (checked_mode()) need += 2 * kGuard;   // callers use guarded() to find the payload inside
     if (need <= *cap) return true;
     if (*p) cudaFree(*p);
     *p = nullptr;
@@ -181,6 +223,22 @@ bool grow(void **p, size_t *cap, size_t need) {
     if (cudaMalloc(p, need) != cudaSuccess) { cudaGetLastError(); return false; }
     *cap = need;
     return true;
+}
+// payload address inside a buffer obtained with grow()
+char *guarded(void *base) { return (char *)base + (checked_mode() ? kGuard : 0); }
+// before a launch: pattern around the output payload, NaN bytes after the input payload
+cudaError_t guards_arm(char *d_in, size_t in_bytes, char *d_out, size_t out_bytes, cudaStream_t stream) {
+    if (!checked_mode()) return cudaSuccess;
+    cudaError_t e = cudaMemsetAsync(d_out - kGuard, kGuardByte, kGuard, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_out + out_bytes, kGuardByte, kGuard, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(d_in + in_bytes, 0xFF, kGuard, stream);
+    return e;
+}
+// after the launch (same stream): count changed guard bytes; the caller synchronises the stream afterwards
+cudaError_t guards_check(char *d_out, size_t out_bytes, unsigned long long *d_bad, cudaStream_t stream) {
+    if (!checked_mode()) return cudaSuccess;
+    guard_count_kernel<<<1, 256, 0, stream>>>((const unsigned char *)d_out - kGuard, (const unsigned char *)d_out + out_bytes, d_bad);
+    return cudaGetLastError();
 }
 
 // Device used by the host-pointer calls: LIBGGUF_CUDA_DEVICE, else the current device.
@@ -203,7 +261,7 @@ constexpr size_t kPieceBytes = size_t(16) << 20;
 bool pipeline_enabled() {
     static const bool enabled = [] {
         const char *env = getenv("LIBGGUF_CUDA_HOST_PIPELINE");
-        return !(env && env[0] == '0');
+        return !(env && env[0] == '0') && !checked_mode();
     }();
     return enabled;
 }
@@ -274,16 +332,21 @@ extern "C" size_t libgguf_quantize_chunk(enum ggml_type type, const float *src, 
     if (rows_per_piece > nrows) rows_per_piece = nrows;
     if (!grow(&st.d_in, &st.in_cap, (size_t)rows_per_piece * in_row)) return 0;
     if (!grow(&st.d_out, &st.out_cap, (size_t)rows_per_piece * row_size)) return 0;
+    if (!st.ensure_counter()) return 0;
+    char *d_in = guarded(st.d_in), *d_out = guarded(st.d_out);
     for (int64_t r0 = 0; r0 < nrows; r0 += rows_per_piece) {
         const int64_t nr = nrows - r0 < rows_per_piece ? nrows - r0 : rows_per_piece;
-        cudaError_t err = cudaMemcpyAsync(st.d_in, in + r0 * n_per_row, (size_t)nr * in_row, cudaMemcpyHostToDevice, st.stream);
+        cudaError_t err = guards_arm(d_in, (size_t)nr * in_row, d_out, (size_t)nr * row_size, st.stream);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(d_in, in + r0 * n_per_row, (size_t)nr * in_row, cudaMemcpyHostToDevice, st.stream);
         if (err == cudaSuccess) {
-            if (storage) err = launch_store(type, (const float *)st.d_in, st.d_out, nr * n_per_row, st.stream);
-            else err = launch_quantize((int)type, (const float *)st.d_in, d_im, st.d_out, nr, n_per_row, state, st.stream);
+            if (storage) err = launch_store(type, (const float *)d_in, d_out, nr * n_per_row, st.stream);
+            else err = launch_quantize((int)type, (const float *)d_in, d_im, d_out, nr, n_per_row, state, st.stream);
         }
-        if (err == cudaSuccess) err = cudaMemcpyAsync(out + (size_t)r0 * row_size, st.d_out, (size_t)nr * row_size, cudaMemcpyDeviceToHost, st.stream);
+        if (err == cudaSuccess) err = guards_check(d_out, (size_t)nr * row_size, st.d_bad, st.stream);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(out + (size_t)r0 * row_size, d_out, (size_t)nr * row_size, cudaMemcpyDeviceToHost, st.stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(st.stream);
         if (err != cudaSuccess) { cudaGetLastError(); return 0; }
+        st.collect_violations();
     }
     return staging_ok() ? (size_t)nrows * row_size : 0;
 }
@@ -318,13 +381,18 @@ extern "C" size_t libgguf_dequantize_chunk(enum ggml_type type, const void *src,
     if (rows_per_piece > nrows) rows_per_piece = nrows;
     if (!grow(&st.d_in, &st.in_cap, (size_t)rows_per_piece * row_size)) return 0;
     if (!grow(&st.d_out, &st.out_cap, (size_t)rows_per_piece * out_row)) return 0;
+    if (!st.ensure_counter()) return 0;
+    char *d_in = guarded(st.d_in), *d_out = guarded(st.d_out);
     for (int64_t r0 = 0; r0 < nrows; r0 += rows_per_piece) {
         const int64_t nr = nrows - r0 < rows_per_piece ? nrows - r0 : rows_per_piece;
-        cudaError_t err = cudaMemcpyAsync(st.d_in, in + (size_t)r0 * row_size, (size_t)nr * row_size, cudaMemcpyHostToDevice, st.stream);
-        if (err == cudaSuccess) err = launch_dequantize((int)type, st.d_in, st.d_out, nr * n_per_row, 0, st.stream);
-        if (err == cudaSuccess) err = cudaMemcpyAsync(out + r0 * n_per_row, st.d_out, (size_t)nr * out_row, cudaMemcpyDeviceToHost, st.stream);
+        cudaError_t err = guards_arm(d_in, (size_t)nr * row_size, d_out, (size_t)nr * out_row, st.stream);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(d_in, in + (size_t)r0 * row_size, (size_t)nr * row_size, cudaMemcpyHostToDevice, st.stream);
+        if (err == cudaSuccess) err = launch_dequantize((int)type, d_in, d_out, nr * n_per_row, 0, st.stream);
+        if (err == cudaSuccess) err = guards_check(d_out, (size_t)nr * out_row, st.d_bad, st.stream);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(out + r0 * n_per_row, d_out, (size_t)nr * out_row, cudaMemcpyDeviceToHost, st.stream);
         if (err == cudaSuccess) err = cudaStreamSynchronize(st.stream);
         if (err != cudaSuccess) { cudaGetLastError(); return 0; }
+        st.collect_violations();
     }
     return (size_t)nrows * (size_t)n_per_row * sizeof(float);
 }
@@ -339,7 +407,8 @@ extern "C" void libgguf_quantize_free(void) {
             if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); continue; }
             if (st.stream) cudaStreamSynchronize(st.stream);
             st.ring.release();
-            cudaFree(st.d_in); cudaFree(st.d_out); cudaFree(st.d_imatrix);
+            cudaFree(st.d_in); cudaFree(st.d_out); cudaFree(st.d_imatrix); cudaFree(st.d_bad);
+            st.d_bad = nullptr;
             if (st.stream) cudaStreamDestroy(st.stream);
             st.d_in = st.d_out = nullptr;
             st.d_imatrix = nullptr;
@@ -350,6 +419,12 @@ extern "C" void libgguf_quantize_free(void) {
     device_state_release_all();
     if (have) cudaSetDevice(saved);
     cudaGetLastError();
+}
+
+extern "C" int libgguf_cuda_checked_violations(uint64_t *count) {
+    if (!count) return 1;  // LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT
+    *count = g_guard_violations.load();
+    return checked_mode() ? 0 : 2;  // LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE: the mode is off, nothing was checked
 }
 
 // Column sums of squares of a host matrix, staged through the GPU in row pieces (order preserved).

@@ -104,17 +104,39 @@ def microscaling_matrix(rows: int = 8192, width: int = 8192, seed: int = 0) -> n
     return flat.reshape(rows, width)
 
 
-def conversion_tensor(name: str, rows: int, width: int, first_rows: int | None = None) -> np.ndarray:
-    """One tensor of the synthetic Llama-3-8B-shaped conversion set: i.i.d. N(0, 0.02) from a generator seeded by the
-    tensor's name, with ceil(0.1% of the columns) scaled by 20 as outlier channels.  `first_rows` returns only the
-    first rows of the tensor (same values as in the whole tensor: the normal draws are row-major and the outlier
-    columns are drawn from a second generator)."""
+CONVERSION_BLOCK_ROWS = 1024
+
+
+def conversion_tensor(name: str, rows: int, width: int, first_rows: int | None = None, out: np.ndarray | None = None) -> np.ndarray:
+    """One tensor of the synthetic Llama-3-8B-shaped conversion set: i.i.d. N(0, 0.02) with ceil(0.1% of the columns)
+    scaled by 20 as outlier channels.  The generator is seeded by the tensor's name; rows come in blocks of 1024, block b
+    from `default_rng((seed, b))`, so that the blocks can be drawn by several threads (the embedding has 525 M values)
+    and the first rows of a tensor do not depend on how many rows are asked for (`first_rows`).  `out` (float32,
+    [rows or first_rows, width]) receives the values in place, e.g. a pinned buffer."""
     import zlib
+    from concurrent.futures import ThreadPoolExecutor
     seed = zlib.crc32(name.encode())
     take = rows if first_rows is None else min(rows, first_rows)
-    x = (np.random.default_rng(seed).standard_normal((take, width), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
-    cols = np.random.default_rng(seed + 1).choice(width, size=-(-width // 1000), replace=False)
-    x[:, cols] *= np.float32(20.0)
+    x = out if out is not None else np.empty((take, width), dtype=np.float32)
+    assert x.shape == (take, width) and x.dtype == np.float32
+    cols = np.random.default_rng((seed, 1 << 30)).choice(width, size=-(-width // 1000), replace=False)
+
+    def fill(b: int) -> None:
+        r0 = b * CONVERSION_BLOCK_ROWS
+        r1 = min(take, r0 + CONVERSION_BLOCK_ROWS)
+        block = x[r0:r1]
+        np.random.default_rng((seed, b)).standard_normal(block.shape, dtype=np.float32, out=block)
+        block *= np.float32(0.02)
+        block[:, cols] *= np.float32(20.0)
+
+    nblocks = -(-take // CONVERSION_BLOCK_ROWS)
+    if nblocks <= 2:
+        for b in range(nblocks):
+            fill(b)
+    else:
+        import os
+        with ThreadPoolExecutor(max_workers=min(nblocks, os.cpu_count() or 4, 16)) as pool:
+            list(pool.map(fill, range(nblocks)))
     return x
 
 
