@@ -1,6 +1,6 @@
 """safetensors -> GGUF conversion with every tensor encoded on the GPUs.
 
-    python -m libgguf_b200.quantize_gguf --src model.safetensors --qtype Q4_K_M [--dst out.gguf] [--gpus N] ...
+    python -m libgguf_b200.quantize_gguf --src model.safetensors --qtype Q4_K_M [--dst out.gguf] [--gpus N | --gpus 0,2,3] ...
 
 Planning follows upstream's native converter (csrc/quantize_gguf.cpp): header parse (:919-984), key prefix
 stripping (:986-1021), architecture detection (:1023-1070), which tensors may be quantized (:1072-1105), the mixed
@@ -419,6 +419,7 @@ class Options:
     exclude: list = field(default_factory=list)
     overwrite: bool = False
     gpus: int = 0                                            # 0 = all visible
+    devices: tuple = ()                                      # explicit device list (--gpus 0,2 or LIBGGUF_CUDA_DEVICES); wins over gpus
     chunk_bytes: int = 128 << 20
     batch_bytes: int = 4 << 30
     timings: bool = False
@@ -604,14 +605,13 @@ def convert(options: Options) -> dict:
     head = header_bytes(kv, infos)
     spent["metadata"] = clock() - began
     source = np.memmap(options.src, dtype=np.uint8, mode="r")
-    n_gpus = options.gpus
-    if n_gpus <= 0:
-        count = ctypes.c_int(0)
-        if lib.libgguf_cuda_device_count(ctypes.byref(count)) != 0 or count.value < 1:
-            fail("no CUDA device is available")
-        n_gpus = count.value
+    count = ctypes.c_int(0)
+    if lib.libgguf_cuda_device_count(ctypes.byref(count)) != 0 or count.value < 1:
+        fail("no CUDA device is available")
+    devices = resolve_devices(options.gpus, options.devices, count.value)
+    n_gpus = len(devices)
     ctx = ctypes.c_void_p()
-    if lib.libgguf_cuda_context_create(0, ctypes.byref(ctx)) != 0:
+    if lib.libgguf_cuda_context_create(devices[0], ctypes.byref(ctx)) != 0:
         fail("no CUDA device is available")
     # two pinned arenas per direction; large enough to keep every GPU's slots busy, small enough to allocate quickly
     cap = max(1 << 16, min(options.batch_bytes // 4, max(256 << 20, n_gpus * (128 << 20))))
@@ -673,7 +673,7 @@ def convert(options: Options) -> dict:
                 split_weights[p.key] = whole_tensor_imatrix(whole)
         batches = list(_batches(pieces, cap))
         arenas = [(_PinnedArena(lib, ctx, cap + 4096), _PinnedArena(lib, ctx, cap + 4096)) for _ in range(min(2, len(batches)))]
-        with open(dst, "wb") as out, ConversionPipeline(list(range(n_gpus)), slots=3, chunk_bytes=chunk) as pipe:
+        with open(dst, "wb") as out, ConversionPipeline(devices, slots=3, chunk_bytes=chunk) as pipe:
             out.write(head)
             out.write(b"\0" * (pad_to(len(head)) - len(head)))
             staged = stage(batches[0], arenas[0]) if batches else None
@@ -739,6 +739,38 @@ def summary_lines(result: dict) -> list[str]:
     return lines
 
 
+def parse_device_spec(text: str) -> tuple[int, tuple]:
+    """'--gpus' / LIBGGUF_CUDA_DEVICES value -> (count, explicit device list): '4' -> (4, ()), '0,2,3' -> (0, (0, 2, 3)).
+    A single number is a count; a list (a trailing comma makes one: '2,') names devices."""
+    text = text.strip()
+    if not text:
+        return 0, ()
+    try:
+        if "," in text:
+            devices = tuple(int(t) for t in text.split(",") if t.strip())
+            if not devices or any(d < 0 for d in devices) or len(set(devices)) != len(devices):
+                raise ValueError
+            return 0, devices
+        n = int(text)
+        if n < 0:
+            raise ValueError
+        return n, ()
+    except ValueError:
+        fail(f"invalid GPU selection '{text}': expected a count or a comma-separated list of distinct device numbers")
+
+
+def resolve_devices(gpus: int, devices: tuple, visible: int) -> list[int]:
+    """The device list a conversion uses, given the number of visible CUDA devices."""
+    if devices:
+        bad = [d for d in devices if d >= visible]
+        if bad:
+            fail(f"CUDA device {bad[0]} requested, but only {visible} device(s) are visible")
+        return list(devices)
+    if gpus > visible:
+        fail(f"{gpus} GPUs requested, but only {visible} device(s) are visible")
+    return list(range(gpus if gpus > 0 else visible))
+
+
 def parse_args(argv) -> Options:
     ap = argparse.ArgumentParser(prog="libgguf_b200.quantize_gguf", description="safetensors -> GGUF on the GPU pipeline")
     ap.add_argument("--src", required=True)
@@ -764,10 +796,12 @@ def parse_args(argv) -> Options:
     ap.add_argument("--cuda-batch-mb", type=int, default=0, help="largest shard in MiB (same as --chunk-mb)")
     ap.add_argument("--cuda-pipeline", default="1", help="ignored (always pipelined)")
     ap.add_argument("--timings", action="store_true", help="print the wall-clock time of the conversion to stderr")
-    ap.add_argument("--gpus", type=int, default=0, help="number of GPUs to stream through (default: all)")
+    ap.add_argument("--gpus", default="", help="GPUs to stream through: a count N (devices 0..N-1) or a comma-separated device "
+                    "list such as 0,2,3 (default: the list in LIBGGUF_CUDA_DEVICES, else all visible devices)")
     ap.add_argument("--chunk-mb", type=int, default=128, help="largest shard, MiB of source bytes")
     ap.add_argument("--batch-mb", type=int, default=4096, help="host memory held between file writes, MiB")
     a = ap.parse_args(argv)
+    gpu_count, gpu_list = parse_device_spec(str(a.gpus) if str(a.gpus).strip() else os.environ.get("LIBGGUF_CUDA_DEVICES", ""))
     if a.backend == "cpu":
         fail("CPU backend requested, but this converter encodes on CUDA devices only")
     if a.cuda_vram_bytes > 0:
@@ -781,7 +815,7 @@ def parse_args(argv) -> Options:
             fail("expected PATTERN=QTYPE for --tensor-type")
         overrides.append((pattern, parse_tensor_qtype_name(name)))
     return Options(src=a.src, qtype=a.qtype, dst=a.dst, policy=a.policy, tensor_overrides=overrides, include=a.include,
-                   exclude=a.exclude, overwrite=a.overwrite, gpus=a.gpus, chunk_bytes=a.chunk_mb << 20, batch_bytes=a.batch_mb << 20,
+                   exclude=a.exclude, overwrite=a.overwrite, gpus=gpu_count, devices=gpu_list, chunk_bytes=a.chunk_mb << 20, batch_bytes=a.batch_mb << 20,
                    timings=a.timings)
 
 

@@ -112,3 +112,31 @@ def test_reader_round_trips_the_writer(tmp_path):
     with pytest.raises(ValueError):
         (tmp_path / "bad.gguf").write_bytes(b"GGUX" + bytes(40))
         read_gguf(str(tmp_path / "bad.gguf"))
+
+
+def test_gpu_selection_by_count_list_and_environment(monkeypatch):
+    """--gpus N, --gpus a,b,c and LIBGGUF_CUDA_DEVICES (default: every visible device)."""
+    import pytest
+    from libgguf_b200 import quantize_gguf as qg
+    base = ["--src", "x.safetensors", "--qtype", "Q4_K_M"]
+    monkeypatch.delenv("LIBGGUF_CUDA_DEVICES", raising=False)
+    o = qg.parse_args(base)
+    assert (o.gpus, o.devices) == (0, ()) and qg.resolve_devices(o.gpus, o.devices, 8) == list(range(8))
+    o = qg.parse_args(base + ["--gpus", "3"])
+    assert qg.resolve_devices(o.gpus, o.devices, 8) == [0, 1, 2]
+    o = qg.parse_args(base + ["--gpus", "0,2,5"])
+    assert qg.resolve_devices(o.gpus, o.devices, 8) == [0, 2, 5]
+    o = qg.parse_args(base + ["--gpus", "4,"])
+    assert qg.resolve_devices(o.gpus, o.devices, 8) == [4]
+    monkeypatch.setenv("LIBGGUF_CUDA_DEVICES", "1,3")
+    o = qg.parse_args(base)
+    assert qg.resolve_devices(o.gpus, o.devices, 4) == [1, 3]
+    o = qg.parse_args(base + ["--gpus", "2"])          # the flag wins over the environment
+    assert qg.resolve_devices(o.gpus, o.devices, 4) == [0, 1]
+    for bad in ("a", "1,1", "-2", "0,-1"):
+        with pytest.raises(qg.ConversionError, match="invalid GPU selection"):
+            qg.parse_args(base + ["--gpus", bad])
+    with pytest.raises(qg.ConversionError, match="only 2 device"):
+        qg.resolve_devices(0, (0, 2), 2)
+    with pytest.raises(qg.ConversionError, match="only 2 device"):
+        qg.resolve_devices(4, (), 2)

@@ -170,7 +170,8 @@ def test_a_row_wider_than_the_batch_still_converts_and_failures_leave_no_file(gg
     rng = np.random.default_rng(3)
     wide = (rng.standard_normal((3, 131072)) * 0.05).astype(np.float32)    # 512 KiB per row, batch arena 256 KiB
     src = str(tmp_path / "wide.safetensors")
-    cm.write_safetensors(src, [("model.layers.0.mlp.down_proj.weight", "F32", wide), ("model.norm.weight", "F32", wide[0, :256])])
+    cm.write_safetensors(src, [("model.layers.0.mlp.down_proj.weight", "F32", wide), ("model.norm.weight", "F32", wide[0, :256]),
+                               ("model.layers.0.self_attn.q_proj.weight", "F32", np.ascontiguousarray(wide[:, :256]))])
     dst = str(tmp_path / "wide.gguf")
     assert qg.main(["--src", src, "--dst", dst, "--qtype", "Q8_0", "--gpus", "1", "--batch-mb", "1"]) == 0
     g = read_gguf(dst, gguf.row_size)
