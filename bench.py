@@ -403,7 +403,7 @@ def main() -> None:
                 "algorithmic_bytes_per_launch": algo_bytes[dominant], "launch_ms": dom_ms}
 
     # what the timed kernels wrote, against the CPU checker (outside every timed region)
-    verified = verify_sweep(torch, x_host, enc, out_sets, rows) if rank == 0 else None
+    verified = verify_sweep(torch, lib, x_host, enc, out_sets, rows, decode) if rank == 0 else None
 
     # end to end through the device-pointer C ABI with pinned host buffers, and the plain-copy ceiling beside it
     e2e = roofline_e2e = None
@@ -453,25 +453,29 @@ def main() -> None:
         dist.destroy_process_group()
 
 
-def verify_sweep(torch, x_host, enc, out_sets, rows) -> dict:
-    """The first 256 rows of every type: the bytes the sweep decodes equal the CPU checker's encoding of the same
-    input rows, and what the timed kernels left in their output buffers equals the checker's fp32 decode rounded to
+def verify_sweep(torch, lib, x_host, enc, out_sets, rows, decode) -> dict:
+    """After the timed region: every (type, output dtype) kernel of the sweep is launched once more on the buffers the
+    timed launches used (they share their output buffers, so only the last kernel's output survives the sweep itself),
+    and the first and the last 256 rows are compared with the CPU checker: the encoded bytes the sweep decodes equal
+    the checker's encoding of the same input rows, and the decode equals the checker's fp32 decode rounded to
     nearest-even (bit patterns).  The checker only checks here; nothing it computes is timed or shipped."""
     chk, kind = reference_checker()
     n = min(rows, 256)
     ok = True
     detail = {}
     for name, qtype, _, _ in SWEEP:
-        want = chk.quantize_rows(x_host[:n], qtype)
-        same_bytes = bool(np.array_equal(enc[name][:n].cpu().numpy(), want))
-        ref32 = torch.from_numpy(chk.dequantize_rows(want, qtype, WIDTH))
-        same_out = True
-        for dt, outs in out_sets.items():
-            for o in outs:
-                same_out = same_out and bool(torch.equal(o[:n].cpu().view(torch.int16), ref32.to(dt).view(torch.int16)))
-        detail[name] = same_bytes and same_out
-        ok = ok and detail[name]
-    return {"ok": ok, "rows_checked": n, "checker": kind, "per_qtype": detail}
+        good = True
+        for sl in (slice(0, n), slice(rows - n, rows)):
+            want = chk.quantize_rows(x_host[sl], qtype)
+            good = good and bool(np.array_equal(enc[name][sl].cpu().numpy(), want))
+            ref32 = torch.from_numpy(chk.dequantize_rows(want, qtype, WIDTH))
+            for dt, outs in out_sets.items():
+                decode(name, qtype, dt, 0)
+                torch.cuda.synchronize()
+                good = good and bool(torch.equal(outs[0][sl].cpu().view(torch.int16), ref32.to(dt).view(torch.int16)))
+        detail[name] = good
+        ok = ok and good
+    return {"ok": ok, "rows_checked": 2 * n, "checker": kind, "per_qtype": detail}
 
 
 class _Slot:
