@@ -863,10 +863,38 @@ constexpr Table<uint32_t, N> make_signs() {
     }
     return t;
 }
+// The sign patterns for the 16-bit selection path: for each half of the eight elements, a word whose byte j is
+// 0x80 when element j is negative (it is XORed into the plane of high bytes of four 16-bit outputs).
+template <int N>
+constexpr Table<uint2, N> make_sign_planes() {
+    Table<uint2, N> t{};
+    for (uint32_t i = 0; i < (uint32_t)N; ++i) {
+        uint32_t s = i;
+        if (N == 128) {
+            uint32_t parity = 0;
+            for (int k = 0; k < 7; ++k) parity ^= (i >> k) & 1u;
+            s |= parity << 7;
+        }
+        uint32_t lo = 0, hi = 0;
+        for (int j = 0; j < 4; ++j) {
+            if ((s >> j) & 1u) lo |= 0x80u << (8 * j);
+            if ((s >> (4 + j)) & 1u) hi |= 0x80u << (8 * j);
+        }
+        t.v[i].x = lo;
+        t.v[i].y = hi;
+    }
+    return t;
+}
 template <class E, int NE, int NS>
 struct Tables {
     Table<E, NE> entry;
     Table<uint32_t, NS> signs;
+};
+template <class E, int NE, int NS>
+struct TablesWithPlanes {
+    Table<E, NE> entry;
+    Table<uint32_t, NS> signs;
+    Table<uint2, NS> planes;
 };
 }  // namespace selectors
 static __device__ __align__(16) const selectors::Tables<uint32_t, 256, 128> k_tab_IQ2XXS = {
@@ -875,10 +903,10 @@ static __device__ __align__(16) const selectors::Tables<uint32_t, 512, 128> k_ta
     selectors::make2(selectors::packed_IQ2XS), selectors::make_signs<128, false>()};
 static __device__ __align__(16) const selectors::Tables<uint32_t, 1024, 256> k_tab_IQ2S = {
     selectors::make2(selectors::packed_IQ2S), selectors::make_signs<256, false>()};
-static __device__ __align__(16) const selectors::Tables<uint16_t, 256, 128> k_tab_IQ3XXS = {
-    selectors::make3(selectors::packed_IQ3XXS), selectors::make_signs<128, true>()};
-static __device__ __align__(16) const selectors::Tables<uint16_t, 512, 256> k_tab_IQ3S = {
-    selectors::make3(selectors::packed_IQ3S), selectors::make_signs<256, true>()};
+static __device__ __align__(16) const selectors::TablesWithPlanes<uint16_t, 256, 128> k_tab_IQ3XXS = {
+    selectors::make3(selectors::packed_IQ3XXS), selectors::make_signs<128, true>(), selectors::make_sign_planes<128>()};
+static __device__ __align__(16) const selectors::TablesWithPlanes<uint16_t, 512, 256> k_tab_IQ3S = {
+    selectors::make3(selectors::packed_IQ3S), selectors::make_signs<256, true>(), selectors::make_sign_planes<256>()};
 static __device__ __align__(16) const selectors::Table<uint32_t, 2048> k_tab_IQ1S = selectors::make2(selectors::packed_IQ1S);
 
 // IQ1: v = scale * ((code + 1 - 1) + bias') with bias = -1 -+ 0.125 already holding the -1.  The codes 0..2 enter
@@ -925,6 +953,35 @@ GGUF_D void emit_signed3(uint32_t sel_a, uint32_t sel_b, uint32_t pick, uint32_t
                          float scale, float *v) {
     emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_a), __byte_perm(m0, m1, sel_a), pick), scale, v);
     emit4_biased(__byte_perm(__byte_perm(p0, p1, sel_b), __byte_perm(m0, m1, sel_b), pick >> 16), scale, v + 4);
+}
+
+// ---- 16-bit outputs by selection -----------------------------------------------------------------------------
+// When a group of elements can take only a handful of distinct values (three for IQ1, eight magnitudes for IQ3), the
+// fp16 / bf16 output needs no per-element arithmetic: the candidates are computed once per group with the same fp32
+// operations as in the arithmetic path and rounded to the output type once, their low bytes and their high bytes
+// are gathered into two "planes", and a codebook entry's nibbles -- one code per element -- are used directly as
+// the selector of a byte permute over each plane.  Two more permutes interleave the planes into 16-bit outputs.
+// A sign is one XOR on the plane of high bytes.
+template <class OutT>
+GGUF_D uint32_t pack16(float a, float b) {  // a in the low half
+    if constexpr (std::is_same<OutT, __half>::value) {
+        const __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+}
+// planes of the patterns packed in p01 (two of them) and p23: lo = their low bytes, hi = their high bytes
+GGUF_D void planes4(uint32_t p01, uint32_t p23, uint32_t &lo, uint32_t &hi) {
+    lo = __byte_perm(p01, p23, 0x6420u);
+    hi = __byte_perm(p01, p23, 0x7531u);
+}
+// four outputs: nibble j of sel (0..7) picks the pattern of element j from the eight in (lo_a, lo_b) / (hi_a, hi_b)
+GGUF_D void select4(uint32_t sel, uint32_t lo_a, uint32_t lo_b, uint32_t hi_a, uint32_t hi_b, uint32_t sign_plane, uint32_t *w) {
+    const uint32_t l = __byte_perm(lo_a, lo_b, sel), h = __byte_perm(hi_a, hi_b, sel) ^ sign_plane;
+    w[0] = __byte_perm(l, h, 0x5140u);
+    w[1] = __byte_perm(l, h, 0x7362u);
 }
 
 template <>
@@ -1015,6 +1072,25 @@ struct Fast<GGML_TYPE_IQ3_XXS> {
                          kIq3xxsMinus0, kIq3xxsMinus1, c.x, v + 8 * k);
         }
     }
+    // 16-bit outputs: |value| is one of db * {4, 12, ..., 52, 62}.  Sixteen elements per call like the arithmetic path:
+    // a thread that took a whole 32-element group would write 64 bytes, and a warp's 32-byte stores would then only
+    // half fill the 128-byte lines they touch (measured: 0.77 of the copy bandwidth against 0.85).
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ3XXS) *>(tab);
+        const int g = e0 >> 3, ib32 = g >> 2;  // g even: grid points 2g .. 2g+3
+        const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
+        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g);
+        uint32_t lo_a, lo_b, hi_a, hi_b;
+        planes4(pack16<OutT>(c.x * 4.f, c.x * 12.f), pack16<OutT>(c.x * 20.f, c.x * 28.f), lo_a, hi_a);
+        planes4(pack16<OutT>(c.x * 36.f, c.x * 44.f), pack16<OutT>(c.x * 52.f, c.x * 62.f), lo_b, hi_b);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint2 sp = t->planes.v[(aux >> (7 * ((g & 3) + k))) & 127];
+            select4(t->entry.v[(idx >> (16 * k)) & 0xFFu], lo_a, lo_b, hi_a, hi_b, sp.x, w + 4 * k);
+            select4(t->entry.v[(idx >> (16 * k + 8)) & 0xFFu], lo_a, lo_b, hi_a, hi_b, sp.y, w + 4 * k + 2);
+        }
+    }
 };
 
 template <>
@@ -1038,6 +1114,26 @@ struct Fast<GGML_TYPE_IQ3_S> {
             const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
             const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
             emit_signed3(t->entry.v[i1], t->entry.v[i2], t->signs.v[(sg >> (8 * k)) & 0xFFu], kIq3sPlus0, kIq3sPlus1, kIq3sMinus0, kIq3sMinus1, c.x, v + 8 * k);
+        }
+    }
+    // 16-bit outputs: |value| is one of db * {1, 3, ..., 15}; sixteen elements per call (see IQ3_XXS)
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ3S) *>(tab);
+        const int g = e0 >> 3, ib32 = g >> 2;
+        const uint32_t qh = b[66 + ib32];
+        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g), sg = lds_u16(b + 74 + g);
+        uint32_t lo_a, lo_b, hi_a, hi_b;
+        planes4(pack16<OutT>(c.x * 1.f, c.x * 3.f), pack16<OutT>(c.x * 5.f, c.x * 7.f), lo_a, hi_a);
+        planes4(pack16<OutT>(c.x * 9.f, c.x * 11.f), pack16<OutT>(c.x * 13.f, c.x * 15.f), lo_b, hi_b);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint2 sp = t->planes.v[(sg >> (8 * k)) & 0xFFu];
+            const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
+            const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
+            select4(t->entry.v[i1], lo_a, lo_b, hi_a, hi_b, sp.x, w + 4 * k);
+            select4(t->entry.v[i2], lo_a, lo_b, hi_a, hi_b, sp.y, w + 4 * k + 2);
         }
     }
 };
@@ -1064,6 +1160,22 @@ struct Fast<GGML_TYPE_IQ1_S> {
             emit_iq1(sel[idx], c.x, c.y, v + 8 * k);
         }
     }
+    // 16-bit outputs: the 32 elements of a group take one of dl * (code + bias), code 0..2
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
+        const int g = e0 >> 3, ib = g >> 2;
+        const uint32_t qh = lds_u16(b + 34 + 2 * ib), low = lds_u16(b + 2 + g);
+        uint32_t lo, hi;
+        planes4(pack16<OutT>(c.x * (0.f + c.y), c.x * (1.f + c.y)), pack16<OutT>(c.x * (2.f + c.y), 0.f), lo, hi);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint32_t e = sel[((low >> (8 * k)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8)];
+            select4(e, lo, 0u, hi, 0u, 0u, w + 4 * k);
+            select4(e >> 16, lo, 0u, hi, 0u, 0u, w + 4 * k + 2);
+        }
+    }
 };
 
 template <>
@@ -1088,6 +1200,22 @@ struct Fast<GGML_TYPE_IQ1_M> {
             const uint32_t idx = ((low >> (8 * k)) & 0xFFu) | ((qh << (k ? 4 : 8)) & 0x700u);
             const float bias = (qh & (k ? 0x80u : 0x08u)) ? -1.125f : -0.875f;
             emit_iq1(sel[idx], c.x, bias, v + 8 * k);
+        }
+    }
+    // 16-bit outputs: each grid point's eight elements take one of dl * (code + bias), code 0..2
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const uint32_t *sel = static_cast<const uint32_t *>(tab);
+        const int g = e0 >> 3;
+        const uint32_t qh = b[32 + (g >> 1)], low = lds_u16(b + g);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t e = sel[((low >> (8 * k)) & 0xFFu) | ((qh << (k ? 4 : 8)) & 0x700u)];
+            const float bias = (qh & (k ? 0x80u : 0x08u)) ? -1.125f : -0.875f;
+            uint32_t lo, hi;
+            planes4(pack16<OutT>(c.x * (0.f + bias), c.x * (1.f + bias)), pack16<OutT>(c.x * (2.f + bias), 0.f), lo, hi);
+            select4(e, lo, 0u, hi, 0u, 0u, w + 4 * k);
+            select4(e >> 16, lo, 0u, hi, 0u, 0u, w + 4 * k + 2);
         }
     }
 };
@@ -1290,6 +1418,17 @@ struct TableBytes { static constexpr int value = 0; };
 template <class D>
 struct TableBytes<D, std::void_t<decltype(D::kTableBytes)>> { static constexpr int value = D::kTableBytes; };
 
+// Decoders with a selection path for 16-bit outputs provide run16<OutT>(block, e0, constants, words, table), which
+// writes CALL16 (default: the arithmetic path's call size) packed outputs.
+template <class D, class OutT, class = void>
+struct HasRun16 : std::false_type {};
+template <class D, class OutT>
+struct HasRun16<D, OutT, std::void_t<decltype(&D::template run16<OutT>)>> : std::true_type {};
+template <class D, class = void>
+struct Call16Elems { static constexpr int value = CallElems<D>::value; };
+template <class D>
+struct Call16Elems<D, decltype((void)D::CALL16)> { static constexpr int value = D::CALL16; };
+
 template <int TYPE, class OutT>
 __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                int64_t nblocks) {
@@ -1345,7 +1484,8 @@ __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t
     }
     __syncthreads();
     // call c = u*kThreads + tid: position inside the block (e0) does not depend on u
-    constexpr int CALL = CallElems<D>::value;
+    constexpr bool SELECT16 = sizeof(OutT) == 2 && HasRun16<D, OutT>::value;
+    constexpr int CALL = SELECT16 ? Call16Elems<D>::value : CallElems<D>::value;
     constexpr int CALLS_PER_BLOCK = D::ELEMS / CALL;
     constexpr int CALLS_PER_THREAD = kTileElems / CALL / kThreads;  // 2 or 1
     static_assert(kThreads % CALLS_PER_BLOCK == 0, "a thread keeps its position inside the block across iterations");
@@ -1357,13 +1497,144 @@ __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t
 #pragma unroll
     for (int u = 0; u < CALLS_PER_THREAD; ++u) {
         constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
-        if (blk0 + u * BLOCK_STEP < nb) {
+        if constexpr (SELECT16) {
+            if (blk0 + u * BLOCK_STEP < nb) {
+                uint32_t w[CALL / 2];
+                D::template run16<OutT>(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], w, table);
+#pragma unroll
+                for (int h = 0; h < CALL / 16; ++h)
+                    st_v8(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, *reinterpret_cast<const uint32_t(*)[8]>(w + 8 * h));
+            }
+        } else if (blk0 + u * BLOCK_STEP < nb) {
             float v[CALL];
             if constexpr (TABLE_BYTES > 0) D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v, table);
             else D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
 #pragma unroll
             for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
         }
+    }
+}
+
+// ---- decoding by selection: 16-bit outputs of the types with at most four distinct values per group ----------
+// A TQ1_0 element is d * (digit - 1) with digit in {0, 1, 2}: a block has three possible outputs.  For fp16 / bf16
+// output they are computed once per block (the same fp32 products as in the arithmetic path, rounded to the output
+// type once) and every element becomes a byte permute that picks one of the three 16-bit patterns; no
+// per-element floating point, no conversion.  The permute selectors come from a 256-entry table: for each byte
+// value, its five base-3 digits (upstream dequant.cpp:345-383: digit n of byte v is ((v * 3^n mod 256) * 3) >> 8)
+// already written as selector bytes (low nibble 2t, high nibble 2t + 1 pick the two bytes of pattern t).
+// A thread owns eight consecutive bytes of a block and writes, digit by digit, the eight elements each digit
+// yields (they sit 32, 16 or 4 apart in the block); a thread that owned consecutive elements would need a
+// different digit of sixteen different bytes instead.
+namespace tq1 {
+constexpr uint32_t digit(uint32_t v, int n) {
+    uint32_t q = v;
+    for (int i = 0; i < n; ++i) q = (q * 3u) & 0xFFu;
+    return (q * 3u) >> 8;
+}
+struct SelectorTable { uint2 v[256]; };
+constexpr SelectorTable make_table() {
+    SelectorTable t{};
+    for (uint32_t v = 0; v < 256; ++v) {
+        uint32_t lo = 0;
+        for (int n = 0; n < 4; ++n) lo |= (34u * digit(v, n) + 16u) << (8 * n);
+        t.v[v].x = lo;
+        t.v[v].y = 34u * digit(v, 4) + 16u;
+    }
+    return t;
+}
+}  // namespace tq1
+static __device__ __align__(16) const tq1::SelectorTable k_tq1_selectors = tq1::make_table();
+
+constexpr int kTq1Threads = 224;  // 128 tasks over bytes 0..31, 64 over bytes 32..47, 32 over bytes 48..51 of 32 blocks
+constexpr int kTq1OutStride = 512 + 64;  // bytes of a block's outputs in shared memory; the pad keeps neighbouring blocks on different banks
+
+template <class OutT>
+__global__ void __launch_bounds__(kTq1Threads, 8) dequant_tq1_select_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
+                                                                           int64_t nblocks) {
+    static_assert(sizeof(OutT) == 2, "selection works on 16-bit patterns");
+    constexpr int TILE_BLOCKS = kTileElems / 256, BYTES = 54;
+    constexpr int TILE_VECS = (TILE_BLOCKS * BYTES + 15) / 16;
+    __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 16];
+    __shared__ __align__(16) uint2 table[256];
+    // The outputs of a task are runs of 16 bytes (32 for the last region) scattered over its block; they are
+    // gathered here and leave as whole 32-byte pieces, so that every global store instruction of a warp fills the
+    // 128-byte lines it touches (written straight from the tasks, the stores half fill them: 0.84 of the copy
+    // bandwidth instead of the figure this kernel reaches).
+    __shared__ __align__(32) uint8_t staged[TILE_BLOCKS * kTq1OutStride];
+    const int tid = threadIdx.x;
+    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
+    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
+    grid_dependents_may_launch();
+    {   // constant data: does not wait for the previous kernel
+        const uint4 *g = reinterpret_cast<const uint4 *>(&k_tq1_selectors);
+        if (tid < 128) reinterpret_cast<uint4 *>(table)[tid] = __ldg(g + tid);
+    }
+    grid_dependency_wait();
+    const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * BYTES);  // 16-byte aligned by contract
+    const int nvec = (nb * BYTES + 15) >> 4;
+    if (tid < nvec) reinterpret_cast<uint4 *>(tile)[tid] = __ldcs(g16 + tid);  // at most 108 vectors
+    __syncthreads();
+
+    // task -> block, first byte, element offset of digit 0, element stride between digits
+    int blk, at, first, stride;
+    if (tid < 128) { blk = tid >> 2; at = 8 * (tid & 3); first = at; stride = 32; }
+    else if (tid < 192) { blk = (tid - 128) >> 1; at = 32 + 8 * (tid & 1); first = 160 + 8 * (tid & 1); stride = 16; }
+    else { blk = tid - 192; at = 48; first = 240; stride = 4; }
+    if (blk < nb) {
+        const uint8_t *b = tile + blk * BYTES;
+        // the block's three outputs as 16-bit patterns
+        const float d = half_hw(lds_u16(b + 52));
+        const uint32_t lut_a = pack16<OutT>(d * -1.0f, d * 0.0f), lut_b = pack16<OutT>(d * 1.0f, d * 1.0f);
+        uint8_t *out = staged + blk * kTq1OutStride + 2 * first;
+        const uint32_t w0 = lds_u32_a2(b + at);
+        if (tid >= 192) {
+            // four bytes, four digits each: elements 240 + 4 n + j, sixteen consecutive outputs
+            uint2 e[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) e[i] = table[(w0 >> (8 * i)) & 0xFFu];
+            uint32_t w[8];
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
+                w[2 * n] = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
+                w[2 * n + 1] = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
+            }
+            reinterpret_cast<uint4 *>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<uint4 *>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        } else {
+            // eight bytes, four at a time (few live registers); each digit of four bytes gives four consecutive outputs
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t wq = half ? lds_u32_a2(b + at + 4) : w0;
+                uint2 e[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) e[i] = table[(wq >> (8 * i)) & 0xFFu];
+#pragma unroll
+                for (int n = 0; n < 5; ++n) {
+                    uint2 o;
+                    if (n < 4) {
+                        const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
+                        o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
+                        o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
+                    } else {
+                        o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].y, e[1].y, 0x40u));
+                        o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].y, e[3].y, 0x40u));
+                    }
+                    *reinterpret_cast<uint2 *>(out + 2 * n * stride + 8 * half) = o;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // 16 pieces of 32 bytes per block, consecutive lanes on consecutive pieces
+    uint8_t *gout = reinterpret_cast<uint8_t *>(dst + b0 * 256);
+#pragma unroll 1
+    for (int piece = tid; piece < nb * 16; piece += kTq1Threads) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(staged + (piece >> 4) * kTq1OutStride + (piece & 15) * 32);
+        const uint4 lo = p[0], hi = p[1];
+        asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(gout + (size_t)piece * 32), "r"(lo.x), "r"(lo.y),
+                     "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                     : "memory");
     }
 }
 
@@ -1376,6 +1647,14 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
     if (grid <= 0) return cudaSuccess;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
     const int aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    if constexpr (TYPE == GGML_TYPE_TQ1_0 && sizeof(OutT) == 2) {
+        if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            const cudaError_t launched = launch_overlapped(dequant_tq1_select_kernel<OutT>, (unsigned)grid, kTq1Threads, stream,
+                                                           static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks);
+            count_launch();
+            return launched != cudaSuccess ? launched : cudaGetLastError();
+        }
+    }
     if constexpr (Fast<TYPE>::kEnabled) {
         if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
             const cudaError_t launched = launch_overlapped(dequant_fast_kernel<TYPE, OutT>, (unsigned)grid, kThreads, stream,
