@@ -451,8 +451,28 @@ def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_
     chunk = 128 << 20
     tensors = [(t.qtype, t.rows, t.cols) for t in plan]
     code = SOURCE_DTYPES[np.dtype(np.uint16 if src_dtype == "bf16" else (np.float16 if src_dtype == "f16" else np.float32))]
+    rates = None
     if per_process:
-        shards = assign_shards(plan_shards(tensors, chunk, [code] * len(plan)), [t.cols for t in plan], world)[rank]
+        # Start-up probe of every rank's own host link (all ranks copying at once, the way the conversion runs), exchanged
+        # once: the static shares follow the measured rates, like the in-process pool's pull queue finds by itself.  This
+        # is planning input; no tensor data crosses between ranks.
+        probe_src = pinned[(14336, 4096)].view(torch.uint8)[: 128 << 20]
+        probe_dst = torch.empty(probe_src.numel(), dtype=torch.uint8, device=device)
+        probe_dst.copy_(probe_src, non_blocking=True)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(4):
+            probe_dst.copy_(probe_src, non_blocking=True)
+        b.record()
+        torch.cuda.synchronize()
+        mine = torch.tensor([4 * probe_src.numel() / (a.elapsed_time(b) * 1e-3) / 1e9], device=device, dtype=torch.float64)
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        rates = [round(float(g.item()), 1) for g in gathered]
+        del probe_dst
+        shards = assign_shards(plan_shards(tensors, chunk, [code] * len(plan)), [t.cols for t in plan], world, rates)[rank]
     else:
         shards = [(i, 0, t.rows) for i, t in enumerate(plan)]
     pool_bytes = sum(rows * row_size(plan[i].qtype, plan[i].cols) for i, _, rows in shards)
@@ -499,6 +519,7 @@ def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_
            "tensors": len(plan), "source_dtype": src_dtype, "source_bytes_fp32_equivalent": in_bytes,
            "source_bytes_over_the_link": link_bytes, "output_bytes": out_bytes, "passes_timed": iterations,
            "all_times_s": [round(x, 4) for x in times], "pipeline_rank0": stats, "verified": ok,
+           "link_rates_GBps_per_rank": rates,
            "note": "one generated tensor per distinct shape, shared by the tensors of that shape (3.3 GB of pinned source)"}
     if link is not None:
         # what plain copies of the same bytes would take on this host link at this N (each direction alone; they overlap)

@@ -144,30 +144,38 @@ def plan_shards(tensors: list[tuple[int, int, int]], chunk_bytes: int = 128 << 2
     return [(s.tensor, s.row0, s.rows) for s in out]
 
 
-def assign_shards(shards: list[tuple[int, int, int]], widths: list[int], world: int) -> list[list[tuple[int, int, int]]]:
-    """Split a shard list over `world` processes (one per GPU) without any exchange: shards are taken in the given
-    (largest-first) order and each goes to the process with the fewest elements so far, lowest rank on ties.
+def assign_shards(shards: list[tuple[int, int, int]], widths: list[int], world: int,
+                  rates: list[float] | None = None) -> list[list[tuple[int, int, int]]]:
+    """Split a shard list over `world` processes (one per GPU) without any exchange of data: shards are taken in the
+    given (largest-first) order and each goes to the process that would finish it earliest, lowest rank on ties.
     Every process computes the same answer from the same plan, so no rank needs to talk to another.
-    `widths[t]` is n_per_row of tensor t."""
+    `widths[t]` is n_per_row of tensor t.  `rates` (optional, one positive number per process, e.g. the host-to-device
+    rate each process measured on its own link at start-up and all processes exchanged once) weights the shares: a
+    process behind a link of half the rate gets half the elements.  Without it every process counts the same."""
     if world < 1:
         raise ValueError("world must be positive")
-    load = [0] * world
+    if rates is None:
+        rates = [1.0] * world
+    if len(rates) != world or any(not (r > 0) for r in rates):
+        raise ValueError("rates must hold one positive number per process")
+    load = [0.0] * world
     out: list[list[tuple[int, int, int]]] = [[] for _ in range(world)]
     for shard in shards:
         tensor, _, rows = shard
-        r = min(range(world), key=lambda i: (load[i], i))
+        work = rows * widths[tensor]
+        r = min(range(world), key=lambda i: ((load[i] + work) / rates[i], i))
         out[r].append(shard)
-        load[r] += rows * widths[tensor]
+        load[r] += work
     return out
 
 
-def rank_batch(tensors, world: int, rank: int, chunk_bytes: int = 128 << 20):
+def rank_batch(tensors, world: int, rank: int, chunk_bytes: int = 128 << 20, rates: list[float] | None = None):
     """The slice of a conversion batch that process `rank` of `world` runs on its own GPU.
     tensors: list of (qtype, src float32 [rows, n], imatrix or None, dst uint8 [rows * row_size]); the result has the
     same form, with `src` and `dst` replaced by row-range views, and can be given to ConversionPipeline.quantize."""
     shards = plan_shards([(q, s.shape[0], s.shape[1]) for q, s, _, _ in tensors], chunk_bytes,
                          [SOURCE_DTYPES[s.dtype] for _, s, _, _ in tensors])
-    mine = assign_shards(shards, [s.shape[1] for _, s, _, _ in tensors], world)[rank]
+    mine = assign_shards(shards, [s.shape[1] for _, s, _, _ in tensors], world, rates)[rank]
     batch = []
     derived: dict[int, np.ndarray] = {}
     for tensor, row0, rows in mine:

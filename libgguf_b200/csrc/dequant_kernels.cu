@@ -863,38 +863,10 @@ constexpr Table<uint32_t, N> make_signs() {
     }
     return t;
 }
-// The sign patterns for the 16-bit selection path: for each half of the eight elements, a word whose byte j is
-// 0x80 when element j is negative (it is XORed into the plane of high bytes of four 16-bit outputs).
-template <int N>
-constexpr Table<uint2, N> make_sign_planes() {
-    Table<uint2, N> t{};
-    for (uint32_t i = 0; i < (uint32_t)N; ++i) {
-        uint32_t s = i;
-        if (N == 128) {
-            uint32_t parity = 0;
-            for (int k = 0; k < 7; ++k) parity ^= (i >> k) & 1u;
-            s |= parity << 7;
-        }
-        uint32_t lo = 0, hi = 0;
-        for (int j = 0; j < 4; ++j) {
-            if ((s >> j) & 1u) lo |= 0x80u << (8 * j);
-            if ((s >> (4 + j)) & 1u) hi |= 0x80u << (8 * j);
-        }
-        t.v[i].x = lo;
-        t.v[i].y = hi;
-    }
-    return t;
-}
 template <class E, int NE, int NS>
 struct Tables {
     Table<E, NE> entry;
     Table<uint32_t, NS> signs;
-};
-template <class E, int NE, int NS>
-struct TablesWithPlanes {
-    Table<E, NE> entry;
-    Table<uint32_t, NS> signs;
-    Table<uint2, NS> planes;
 };
 }  // namespace selectors
 static __device__ __align__(16) const selectors::Tables<uint32_t, 256, 128> k_tab_IQ2XXS = {
@@ -903,10 +875,10 @@ static __device__ __align__(16) const selectors::Tables<uint32_t, 512, 128> k_ta
     selectors::make2(selectors::packed_IQ2XS), selectors::make_signs<128, false>()};
 static __device__ __align__(16) const selectors::Tables<uint32_t, 1024, 256> k_tab_IQ2S = {
     selectors::make2(selectors::packed_IQ2S), selectors::make_signs<256, false>()};
-static __device__ __align__(16) const selectors::TablesWithPlanes<uint16_t, 256, 128> k_tab_IQ3XXS = {
-    selectors::make3(selectors::packed_IQ3XXS), selectors::make_signs<128, true>(), selectors::make_sign_planes<128>()};
-static __device__ __align__(16) const selectors::TablesWithPlanes<uint16_t, 512, 256> k_tab_IQ3S = {
-    selectors::make3(selectors::packed_IQ3S), selectors::make_signs<256, true>(), selectors::make_sign_planes<256>()};
+static __device__ __align__(16) const selectors::Tables<uint16_t, 256, 128> k_tab_IQ3XXS = {
+    selectors::make3(selectors::packed_IQ3XXS), selectors::make_signs<128, true>()};
+static __device__ __align__(16) const selectors::Tables<uint16_t, 512, 256> k_tab_IQ3S = {
+    selectors::make3(selectors::packed_IQ3S), selectors::make_signs<256, true>()};
 static __device__ __align__(16) const selectors::Table<uint32_t, 2048> k_tab_IQ1S = selectors::make2(selectors::packed_IQ1S);
 
 // IQ1: v = scale * ((code + 1 - 1) + bias') with bias = -1 -+ 0.125 already holding the -1.  The codes 0..2 enter
@@ -956,12 +928,14 @@ GGUF_D void emit_signed3(uint32_t sel_a, uint32_t sel_b, uint32_t pick, uint32_t
 }
 
 // ---- 16-bit outputs by selection -----------------------------------------------------------------------------
-// When a group of elements can take only a handful of distinct values (three for IQ1, eight magnitudes for IQ3), the
+// When a group of elements can take only a handful of distinct values (three for IQ1 and TQ1_0), the
 // fp16 / bf16 output needs no per-element arithmetic: the candidates are computed once per group with the same fp32
 // operations as in the arithmetic path and rounded to the output type once, their low bytes and their high bytes
 // are gathered into two "planes", and a codebook entry's nibbles -- one code per element -- are used directly as
 // the selector of a byte permute over each plane.  Two more permutes interleave the planes into 16-bit outputs.
-// A sign is one XOR on the plane of high bytes.
+// (Tried for IQ3 as well -- eight magnitudes per group, the sign as an XOR on the high-byte plane: 6.0 instead of 7.4
+// instructions per element and no faster; those decoders wait for their shared-memory gathers, three per eight
+// elements at about 3.4 bank wavefronts each, not for the arithmetic.)
 template <class OutT>
 GGUF_D uint32_t pack16(float a, float b) {  // a in the low half
     if constexpr (std::is_same<OutT, __half>::value) {
@@ -978,8 +952,8 @@ GGUF_D void planes4(uint32_t p01, uint32_t p23, uint32_t &lo, uint32_t &hi) {
     hi = __byte_perm(p01, p23, 0x7531u);
 }
 // four outputs: nibble j of sel (0..7) picks the pattern of element j from the eight in (lo_a, lo_b) / (hi_a, hi_b)
-GGUF_D void select4(uint32_t sel, uint32_t lo_a, uint32_t lo_b, uint32_t hi_a, uint32_t hi_b, uint32_t sign_plane, uint32_t *w) {
-    const uint32_t l = __byte_perm(lo_a, lo_b, sel), h = __byte_perm(hi_a, hi_b, sel) ^ sign_plane;
+GGUF_D void select4(uint32_t sel, uint32_t lo_a, uint32_t lo_b, uint32_t hi_a, uint32_t hi_b, uint32_t *w) {
+    const uint32_t l = __byte_perm(lo_a, lo_b, sel), h = __byte_perm(hi_a, hi_b, sel);
     w[0] = __byte_perm(l, h, 0x5140u);
     w[1] = __byte_perm(l, h, 0x7362u);
 }
@@ -1072,25 +1046,6 @@ struct Fast<GGML_TYPE_IQ3_XXS> {
                          kIq3xxsMinus0, kIq3xxsMinus1, c.x, v + 8 * k);
         }
     }
-    // 16-bit outputs: |value| is one of db * {4, 12, ..., 52, 62}.  Sixteen elements per call like the arithmetic path:
-    // a thread that took a whole 32-element group would write 64 bytes, and a warp's 32-byte stores would then only
-    // half fill the 128-byte lines they touch (measured: 0.77 of the copy bandwidth against 0.85).
-    template <class OutT>
-    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
-        const auto *t = static_cast<const decltype(k_tab_IQ3XXS) *>(tab);
-        const int g = e0 >> 3, ib32 = g >> 2;  // g even: grid points 2g .. 2g+3
-        const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
-        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g);
-        uint32_t lo_a, lo_b, hi_a, hi_b;
-        planes4(pack16<OutT>(c.x * 4.f, c.x * 12.f), pack16<OutT>(c.x * 20.f, c.x * 28.f), lo_a, hi_a);
-        planes4(pack16<OutT>(c.x * 36.f, c.x * 44.f), pack16<OutT>(c.x * 52.f, c.x * 62.f), lo_b, hi_b);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const uint2 sp = t->planes.v[(aux >> (7 * ((g & 3) + k))) & 127];
-            select4(t->entry.v[(idx >> (16 * k)) & 0xFFu], lo_a, lo_b, hi_a, hi_b, sp.x, w + 4 * k);
-            select4(t->entry.v[(idx >> (16 * k + 8)) & 0xFFu], lo_a, lo_b, hi_a, hi_b, sp.y, w + 4 * k + 2);
-        }
-    }
 };
 
 template <>
@@ -1114,26 +1069,6 @@ struct Fast<GGML_TYPE_IQ3_S> {
             const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
             const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
             emit_signed3(t->entry.v[i1], t->entry.v[i2], t->signs.v[(sg >> (8 * k)) & 0xFFu], kIq3sPlus0, kIq3sPlus1, kIq3sMinus0, kIq3sMinus1, c.x, v + 8 * k);
-        }
-    }
-    // 16-bit outputs: |value| is one of db * {1, 3, ..., 15}; sixteen elements per call (see IQ3_XXS)
-    template <class OutT>
-    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
-        const auto *t = static_cast<const decltype(k_tab_IQ3S) *>(tab);
-        const int g = e0 >> 3, ib32 = g >> 2;
-        const uint32_t qh = b[66 + ib32];
-        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g), sg = lds_u16(b + 74 + g);
-        uint32_t lo_a, lo_b, hi_a, hi_b;
-        planes4(pack16<OutT>(c.x * 1.f, c.x * 3.f), pack16<OutT>(c.x * 5.f, c.x * 7.f), lo_a, hi_a);
-        planes4(pack16<OutT>(c.x * 9.f, c.x * 11.f), pack16<OutT>(c.x * 13.f, c.x * 15.f), lo_b, hi_b);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int l = (g & 3) + k;
-            const uint2 sp = t->planes.v[(sg >> (8 * k)) & 0xFFu];
-            const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
-            const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
-            select4(t->entry.v[i1], lo_a, lo_b, hi_a, hi_b, sp.x, w + 4 * k);
-            select4(t->entry.v[i2], lo_a, lo_b, hi_a, hi_b, sp.y, w + 4 * k + 2);
         }
     }
 };
@@ -1172,8 +1107,8 @@ struct Fast<GGML_TYPE_IQ1_S> {
         for (int k = 0; k < 2; ++k) {
             const int l = (g & 3) + k;
             const uint32_t e = sel[((low >> (8 * k)) & 0xFFu) | (((qh >> (3 * l)) & 7u) << 8)];
-            select4(e, lo, 0u, hi, 0u, 0u, w + 4 * k);
-            select4(e >> 16, lo, 0u, hi, 0u, 0u, w + 4 * k + 2);
+            select4(e, lo, 0u, hi, 0u, w + 4 * k);
+            select4(e >> 16, lo, 0u, hi, 0u, w + 4 * k + 2);
         }
     }
 };
@@ -1214,8 +1149,8 @@ struct Fast<GGML_TYPE_IQ1_M> {
             const float bias = (qh & (k ? 0x80u : 0x08u)) ? -1.125f : -0.875f;
             uint32_t lo, hi;
             planes4(pack16<OutT>(c.x * (0.f + bias), c.x * (1.f + bias)), pack16<OutT>(c.x * (2.f + bias), 0.f), lo, hi);
-            select4(e, lo, 0u, hi, 0u, 0u, w + 4 * k);
-            select4(e >> 16, lo, 0u, hi, 0u, 0u, w + 4 * k + 2);
+            select4(e, lo, 0u, hi, 0u, w + 4 * k);
+            select4(e >> 16, lo, 0u, hi, 0u, w + 4 * k + 2);
         }
     }
 };
@@ -1546,8 +1481,11 @@ constexpr SelectorTable make_table() {
 static __device__ __align__(16) const tq1::SelectorTable k_tq1_selectors = tq1::make_table();
 
 constexpr int kTq1Threads = 224;  // 128 tasks over bytes 0..31, 64 over bytes 32..47, 32 over bytes 48..51 of 32 blocks
-constexpr int kTq1OutStride = 512 + 64;  // bytes of a block's outputs in shared memory; the pad keeps neighbouring blocks on different banks
 
+// The tasks store their 16-byte runs straight to global memory (a warp's store covers 64-byte pieces, 512 bytes apart).
+// Gathering the tile's outputs in shared memory first, so that every store fills whole 128-byte lines, was measured and
+// is slower (0.63 against 0.84 of the copy bandwidth): the extra pass through shared memory costs more than the
+// half-filled lines.
 template <class OutT>
 __global__ void __launch_bounds__(kTq1Threads, 8) dequant_tq1_select_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                            int64_t nblocks) {
@@ -1556,11 +1494,6 @@ __global__ void __launch_bounds__(kTq1Threads, 8) dequant_tq1_select_kernel(cons
     constexpr int TILE_VECS = (TILE_BLOCKS * BYTES + 15) / 16;
     __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 16];
     __shared__ __align__(16) uint2 table[256];
-    // The outputs of a task are runs of 16 bytes (32 for the last region) scattered over its block; they are
-    // gathered here and leave as whole 32-byte pieces, so that every global store instruction of a warp fills the
-    // 128-byte lines it touches (written straight from the tasks, the stores half fill them: 0.84 of the copy
-    // bandwidth instead of the figure this kernel reaches).
-    __shared__ __align__(32) uint8_t staged[TILE_BLOCKS * kTq1OutStride];
     const int tid = threadIdx.x;
     const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
     const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
@@ -1580,61 +1513,51 @@ __global__ void __launch_bounds__(kTq1Threads, 8) dequant_tq1_select_kernel(cons
     if (tid < 128) { blk = tid >> 2; at = 8 * (tid & 3); first = at; stride = 32; }
     else if (tid < 192) { blk = (tid - 128) >> 1; at = 32 + 8 * (tid & 1); first = 160 + 8 * (tid & 1); stride = 16; }
     else { blk = tid - 192; at = 48; first = 240; stride = 4; }
-    if (blk < nb) {
-        const uint8_t *b = tile + blk * BYTES;
-        // the block's three outputs as 16-bit patterns
-        const float d = half_hw(lds_u16(b + 52));
-        const uint32_t lut_a = pack16<OutT>(d * -1.0f, d * 0.0f), lut_b = pack16<OutT>(d * 1.0f, d * 1.0f);
-        uint8_t *out = staged + blk * kTq1OutStride + 2 * first;
-        const uint32_t w0 = lds_u32_a2(b + at);
-        if (tid >= 192) {
-            // four bytes, four digits each: elements 240 + 4 n + j, sixteen consecutive outputs
-            uint2 e[4];
+    if (blk >= nb) return;
+    const uint8_t *b = tile + blk * BYTES;
+    // the block's three outputs as 16-bit patterns
+    const float d = half_hw(lds_u16(b + 52));
+    const uint32_t lut_a = pack16<OutT>(d * -1.0f, d * 0.0f), lut_b = pack16<OutT>(d * 1.0f, d * 1.0f);
+    OutT *out = dst + (b0 + blk) * 256 + first;
+    const uint32_t w0 = lds_u32_a2(b + at);
+    if (tid >= 192) {
+        // four bytes, four digits each: elements 240 + 4 n + j, sixteen consecutive outputs
+        uint2 e[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) e[i] = table[(w0 >> (8 * i)) & 0xFFu];
-            uint32_t w[8];
+        for (int i = 0; i < 4; ++i) e[i] = table[(w0 >> (8 * i)) & 0xFFu];
+        uint32_t w[8];
 #pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
-                w[2 * n] = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
-                w[2 * n + 1] = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
-            }
-            reinterpret_cast<uint4 *>(out)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            reinterpret_cast<uint4 *>(out)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-        } else {
-            // eight bytes, four at a time (few live registers); each digit of four bytes gives four consecutive outputs
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const uint32_t wq = half ? lds_u32_a2(b + at + 4) : w0;
-                uint2 e[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) e[i] = table[(wq >> (8 * i)) & 0xFFu];
-#pragma unroll
-                for (int n = 0; n < 5; ++n) {
-                    uint2 o;
-                    if (n < 4) {
-                        const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
-                        o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
-                        o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
-                    } else {
-                        o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].y, e[1].y, 0x40u));
-                        o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].y, e[3].y, 0x40u));
-                    }
-                    *reinterpret_cast<uint2 *>(out + 2 * n * stride + 8 * half) = o;
-                }
-            }
+        for (int n = 0; n < 4; ++n) {
+            const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
+            w[2 * n] = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
+            w[2 * n + 1] = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
         }
+        st_v8(out, w);
+        return;
     }
-    __syncthreads();
-    // 16 pieces of 32 bytes per block, consecutive lanes on consecutive pieces
-    uint8_t *gout = reinterpret_cast<uint8_t *>(dst + b0 * 256);
-#pragma unroll 1
-    for (int piece = tid; piece < nb * 16; piece += kTq1Threads) {
-        const uint4 *p = reinterpret_cast<const uint4 *>(staged + (piece >> 4) * kTq1OutStride + (piece & 15) * 32);
-        const uint4 lo = p[0], hi = p[1];
-        asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(gout + (size_t)piece * 32), "r"(lo.x), "r"(lo.y),
-                     "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
-                     : "memory");
+    const uint32_t w1 = lds_u32_a2(b + at + 4);
+    uint2 e[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        e[i] = table[(w0 >> (8 * i)) & 0xFFu];
+        e[4 + i] = table[(w1 >> (8 * i)) & 0xFFu];
+    }
+#pragma unroll
+    for (int n = 0; n < 5; ++n) {
+        uint4 o;
+        if (n < 4) {
+            const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
+            o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
+            o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
+            o.z = __byte_perm(lut_a, lut_b, __byte_perm(e[4].x, e[5].x, pick));
+            o.w = __byte_perm(lut_a, lut_b, __byte_perm(e[6].x, e[7].x, pick));
+        } else {
+            o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].y, e[1].y, 0x40u));
+            o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].y, e[3].y, 0x40u));
+            o.z = __byte_perm(lut_a, lut_b, __byte_perm(e[4].y, e[5].y, 0x40u));
+            o.w = __byte_perm(lut_a, lut_b, __byte_perm(e[6].y, e[7].y, 0x40u));
+        }
+        __stcs(reinterpret_cast<uint4 *>(out + n * stride), o);
     }
 }
 

@@ -537,6 +537,41 @@ class _PinnedArena:
             self._handle = None
 
 
+# The pinned arenas of the last conversion, kept for the next one in this process (page-locking a gigabyte takes a few
+# tenths of a second, as long as the conversion of a small model): {"key": (device, size, pairs), "ctx": ..., "pairs": [...]}
+_ARENA_CACHE: dict = {}
+
+
+def _release_arena_cache() -> None:
+    from ._native import lib
+    for pair in _ARENA_CACHE.get("pairs", []):
+        for arena in pair:
+            arena.close()
+    if _ARENA_CACHE.get("ctx"):
+        lib.libgguf_cuda_context_destroy(_ARENA_CACHE["ctx"])
+    _ARENA_CACHE.clear()
+
+
+def _arenas(lib, device: int, size: int, pairs: int):
+    """`pairs` (input, output) arena pairs of `size` bytes each, page-locked through a library context on `device`."""
+    import atexit
+    import ctypes
+    key = (device, size, pairs)
+    if _ARENA_CACHE.get("key") == key:
+        return _ARENA_CACHE["pairs"]
+    first_use = not _ARENA_CACHE
+    _release_arena_cache()
+    ctx = ctypes.c_void_p()
+    if lib.libgguf_cuda_context_create(device, ctypes.byref(ctx)) != 0:
+        fail("no CUDA device is available")
+    _ARENA_CACHE.update(key=key, ctx=ctx, pairs=[])
+    for _ in range(pairs):
+        _ARENA_CACHE["pairs"].append((_PinnedArena(lib, ctx, size), _PinnedArena(lib, ctx, size)))
+    if first_use:
+        atexit.register(_release_arena_cache)
+    return _ARENA_CACHE["pairs"]
+
+
 def _align(n: int, to: int = 256) -> int:
     return (n + to - 1) // to * to
 
@@ -610,9 +645,6 @@ def convert(options: Options) -> dict:
         fail("no CUDA device is available")
     devices = resolve_devices(options.gpus, options.devices, count.value)
     n_gpus = len(devices)
-    ctx = ctypes.c_void_p()
-    if lib.libgguf_cuda_context_create(devices[0], ctypes.byref(ctx)) != 0:
-        fail("no CUDA device is available")
     # two pinned arenas per direction; large enough to keep every GPU's slots busy, small enough to allocate quickly
     cap = max(1 << 16, min(options.batch_bytes // 4, max(256 << 20, n_gpus * (128 << 20))))
     # a piece is at least one row: the arenas must hold the widest row of the plan on either side
@@ -620,9 +652,24 @@ def convert(options: Options) -> dict:
         if p.qtype != p.source_dtype:
             cap = max(cap, _align(p.n_per_row * SOURCE_DTYPES[p.source_dtype][2]), _align(p.nbytes // p.n_rows))
     chunk = max(1 << 12, min(options.chunk_bytes, cap // (3 * n_gpus)))
-    arenas, fd = [], os.open(options.src, os.O_RDONLY)
+    fd, out_fd = os.open(options.src, os.O_RDONLY), -1
     readers = ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1))
+    writers = ThreadPoolExecutor(max_workers=min(4, os.cpu_count() or 1))
     READ_PIECE = 16 << 20
+    # where every tensor's bytes go in the output file: known before anything is encoded, so finished pieces are
+    # written at their place by a pool of writer threads while the GPUs work on the next batch
+    data_start = pad_to(len(head))
+    tensor_at, at = {}, data_start
+    for p in plans:
+        tensor_at[p.key] = at
+        at += pad_to(p.nbytes)
+    file_size = at
+
+    def write_at(view, file_offset: int):
+        done, total = 0, len(view)
+        buffer = memoryview(view).cast("B")
+        while done < total:
+            done += os.pwrite(out_fd, buffer[done:total], file_offset + done)
 
     def read_into(view: np.ndarray, file_offset: int):
         done, total = 0, view.size
@@ -672,10 +719,12 @@ def convert(options: Options) -> dict:
                 whole = source[p.data_begin:p.data_end].view(np_dtype).reshape(p.n_rows, p.n_per_row)
                 split_weights[p.key] = whole_tensor_imatrix(whole)
         batches = list(_batches(pieces, cap))
-        arenas = [(_PinnedArena(lib, ctx, cap + 4096), _PinnedArena(lib, ctx, cap + 4096)) for _ in range(min(2, len(batches)))]
-        with open(dst, "wb") as out, ConversionPipeline(devices, slots=3, chunk_bytes=chunk) as pipe:
-            out.write(head)
-            out.write(b"\0" * (pad_to(len(head)) - len(head)))
+        arenas = _arenas(lib, devices[0], cap + 4096, 2)
+        out_fd = os.open(dst, os.O_WRONLY | os.O_CREAT | os.O_TRUNC, 0o644)
+        os.ftruncate(out_fd, file_size)       # the padding between tensors is the zeros of the extended file
+        write_at(head, 0)
+        writes = [[], []]                      # write futures of the batch that last used each arena pair
+        with ConversionPipeline(devices, slots=3, chunk_bytes=chunk) as pipe:
             staged = stage(batches[0], arenas[0]) if batches else None
             for i, batch in enumerate(batches):
                 entries, outputs, futures = staged
@@ -685,34 +734,43 @@ def convert(options: Options) -> dict:
                 t1 = clock()
                 if i + 1 < len(batches):   # the next batch's reads run while this one is encoded and written
                     staged = stage(batches[i + 1], arenas[(i + 1) & 1])
+                for f in writes[i & 1]:    # this pair's output arena is free once batch i - 2 has reached the file
+                    f.result()
+                t2 = clock()
                 if entries:
                     pipe.quantize(entries)
-                t2 = clock()
+                t3 = clock()
+                writes[i & 1] = []
                 for piece, enc in zip(batch, outputs):
                     p = piece.plan
-                    out.write(enc if enc is not None else source[p.data_begin:p.data_end])
-                    if piece.last:
-                        out.write(b"\0" * (pad_to(p.nbytes) - p.nbytes))
+                    data = enc if enc is not None else source[p.data_begin:p.data_end]
+                    base = tensor_at[p.key] + piece.row0 * (p.nbytes // p.n_rows)
+                    for start in range(0, len(data), READ_PIECE):
+                        writes[i & 1].append(writers.submit(write_at, data[start:min(start + READ_PIECE, len(data))], base + start))
                 spent["read"] += t1 - t0
-                spent["cuda_quant"] += t2 - t1
-                spent["write"] += clock() - t2
+                spent["write"] += t2 - t1
+                spent["cuda_quant"] += t3 - t2
                 for entry in entries:
                     counts["cuda_chunks"] += 1
                     counts["cuda_max_input"] = max(counts["cuda_max_input"], entry[1].nbytes)
                     counts["cuda_max_output"] = max(counts["cuda_max_output"], entry[3].nbytes)
+            t4 = clock()
+            for pending in writes:
+                for f in pending:
+                    f.result()
+            spent["write"] += clock() - t4
         finished = True
     finally:
+        readers.shutdown(wait=True)
+        writers.shutdown(wait=True)
+        os.close(fd)
+        if out_fd >= 0:
+            os.close(out_fd)
         if not finished:   # never leave a half-written file behind
             try:
                 os.unlink(dst)
             except OSError:
                 pass
-        readers.shutdown(wait=True)
-        os.close(fd)
-        for pair in arenas:
-            for arena in pair:
-                arena.close()
-        lib.libgguf_cuda_context_destroy(ctx)
     result["timings"] = dict(spent, total=clock() - began, tensors=len(plans), cuda_tensors=sum(1 for p in plans if p.qtype != p.source_dtype),
                              threads=min(8, os.cpu_count() or 1), scratch=cap, cuda_vram=chunk, **counts)
     return result

@@ -72,3 +72,26 @@ def test_assignment_is_deterministic_and_balanced():
         assert sum(loads) == 8_029_995_008
         assert max(loads) / (sum(loads) / world) < 1.02
     assert max_over_ranks(3.5) == 3.5
+
+
+def test_assignment_weighted_by_link_rates():
+    """Half of the GPUs behind links of half the rate (as measured on an 8-GPU host): the shares follow the rates, so
+    every process finishes at the same time, and every shard is still assigned exactly once."""
+    import pytest
+    plan = llama3_8b_plan()
+    shards = plan_shards([(t.qtype, t.rows, t.cols) for t in plan])
+    widths = [t.cols for t in plan]
+    rates = [27.0, 27.0, 27.5, 27.5, 55.0, 55.0, 54.0, 55.0]
+    parts = assign_shards(shards, widths, 8, rates)
+    assert parts == assign_shards(shards, widths, 8, list(rates))
+    assert sorted(s for part in parts for s in part) == sorted(shards)
+    loads = [sum(r * widths[t] for t, _, r in part) for part in parts]
+    finish = [l / r for l, r in zip(loads, rates)]
+    assert max(finish) / (sum(loads) / sum(rates)) < 1.03
+    assert loads[4] > 1.8 * loads[0]
+    # equal rates give the unweighted answer
+    assert assign_shards(shards, widths, 4, [3.0] * 4) == assign_shards(shards, widths, 4)
+    with pytest.raises(ValueError):
+        assign_shards(shards, widths, 2, [1.0])
+    with pytest.raises(ValueError):
+        assign_shards(shards, widths, 2, [1.0, 0.0])
