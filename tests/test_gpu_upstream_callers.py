@@ -69,12 +69,15 @@ def test_upstream_converter_on_this_library_writes_upstreams_files(checkpoints, 
     assert len(data) == gold["size"]
     assert hashlib.sha256(data).hexdigest() == gold["sha256"]
     tokens = dict(t.split("=") for line in r.stderr.splitlines() if line.startswith("Timings: ") for t in line.split()[1:])
-    assert int(tokens["cuda_tensors"]) > 0 and int(tokens["cuda_chunks"]) > 0, tokens
+    if entry.endswith(("/q1_0", "/q5_0", "/q5_1")):   # not in upstream's converter's CUDA type list (quantize_gguf.cpp:1666-1679): CPU path
+        assert int(tokens["cuda_tensors"]) == 0
+    else:
+        assert int(tokens["cuda_tensors"]) > 0 and int(tokens["cuda_chunks"]) > 0, tokens
 
 
 @pytest.mark.parametrize("name,options", [("flux_bf16", ["--qtype", "Q4_K_M"]), ("wan_f16", ["--qtype", "Q3_K_M", "--policy", "dynamic"]),
-                                          ("flux_f32", ["--qtype", "Q6_K"]), ("sd1_f16", ["--qtype", "Q5_0"]),
-                                          ("cosmos_bf16", ["--qtype", "Q1_0"])])
+                                          ("flux_f32", ["--qtype", "Q6_K"]), ("sd1_f16", ["--qtype", "Q4_K_M"]),
+                                          ("cosmos_bf16", ["--qtype", "Q3_K_L"]), ("flux_f32", ["--qtype", "Q2_K"])])
 def test_upstream_converter_verifies_this_librarys_bytes_against_its_cpu_quantizers(checkpoints, name, options, tmp_path):
     """--verify-cuda-tensors all (upstream csrc/quantize_gguf.cpp:2176-2181): upstream itself compares every chunk the
     CUDA context returned with its CPU worker pool's bytes and fails on the first difference."""

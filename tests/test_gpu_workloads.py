@@ -149,3 +149,42 @@ def test_conversion_tensors_through_the_pipeline_match_the_checker(gguf, checker
     with ConversionPipeline([0, 1 % ndev], slots=3, chunk_bytes=1 << 20) as pipe:
         pipe.quantize([(q4, bf, None, dst)])
     np.testing.assert_array_equal(dst.reshape(512, -1), checker.quantize_rows(widened, q4))
+
+
+# ------------------------------------------------------------------------------------------------
+# block scales at the edges of fp16, every type, all three output types
+_D_OFFSET = {"Q4_0": 0, "Q4_1": 0, "Q5_0": 0, "Q5_1": 0, "Q8_0": 0, "Q1_0": 0, "Q2_K": 80, "Q3_K": 108, "Q4_K": 0, "Q5_K": 0,
+             "Q6_K": 208, "TQ1_0": 52, "TQ2_0": 64, "IQ2_XXS": 0, "IQ2_XS": 0, "IQ2_S": 0, "IQ3_XXS": 0, "IQ3_S": 0, "IQ1_S": 0,
+             "IQ4_NL": 0, "IQ4_XS": 0}
+_BLOCK_BYTES = {"Q4_0": 18, "Q4_1": 20, "Q5_0": 22, "Q5_1": 24, "Q8_0": 34, "Q1_0": 18, "Q2_K": 84, "Q3_K": 110, "Q4_K": 144,
+                "Q5_K": 176, "Q6_K": 210, "TQ1_0": 54, "TQ2_0": 66, "IQ2_XXS": 66, "IQ2_XS": 74, "IQ2_S": 82, "IQ3_XXS": 98,
+                "IQ3_S": 110, "IQ1_S": 50, "IQ4_NL": 18, "IQ4_XS": 136}
+
+
+@pytest.mark.parametrize("name", sorted(_D_OFFSET))
+def test_decode_with_block_scales_at_the_edges_of_fp16(checker, name):
+    """Valid encodings whose fp16 block scale is overwritten with zero, minus zero, the smallest and largest subnormal,
+    the smallest normal, 65504, infinity and negative values: the 16-bit decoders that select precomputed patterns
+    (and the arithmetic ones) must still give the correctly rounded fp32 decode; where the fp32 value is NaN
+    (infinity times zero) the output must be NaN too."""
+    qtype = inputs.QTYPES[name]
+    width = 2048
+    x = np.random.default_rng(41).standard_normal((16, width), dtype=np.float32)
+    im = inputs.imatrix_for(width, seed=5) if checker.requires_imatrix(qtype) else None
+    enc = checker.quantize_rows(x, qtype, im).copy()
+    scales = np.array([0x0000, 0x8000, 0x0001, 0x03FF, 0x0400, 0x7BFF, 0x7C00, 0xFC00, 0xBC00, 0x8001, 0x3C00, 0xFBFF], np.uint16)
+    blocks = enc.reshape(-1, _BLOCK_BYTES[name])
+    pick = np.arange(blocks.shape[0]) % (len(scales) + 3)      # some blocks keep their own scale
+    for i, s in enumerate(scales):
+        rows = pick == i
+        blocks[rows, _D_OFFSET[name]] = s & 0xFF
+        blocks[rows, _D_OFFSET[name] + 1] = s >> 8
+    with np.errstate(all="ignore"):
+        ref32 = torch.from_numpy(checker.dequantize_rows(enc, qtype, width))
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        got = _decode_on_gpu(enc, qtype, width, dtype)
+        want = ref32.to(dtype)
+        nan = torch.isnan(want)
+        assert torch.equal(torch.isnan(got), nan), (name, dtype)
+        view = torch.int32 if dtype == torch.float32 else torch.int16
+        assert torch.equal(got.view(view)[~nan], want.view(view)[~nan]), (name, dtype)
