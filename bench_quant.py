@@ -456,7 +456,7 @@ def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_
         # Start-up probe of every rank's own host link (all ranks copying at once, the way the conversion runs), exchanged
         # once: the static shares follow the measured rates, like the in-process pool's pull queue finds by itself.  This
         # is planning input; no tensor data crosses between ranks.
-        probe_src = pinned[(14336, 4096)].view(torch.uint8)[: 128 << 20]
+        probe_src = pinned[(14336, 4096)].view(torch.uint8).reshape(-1)[: 128 << 20]
         probe_dst = torch.empty(probe_src.numel(), dtype=torch.uint8, device=device)
         probe_dst.copy_(probe_src, non_blocking=True)
         torch.cuda.synchronize()
