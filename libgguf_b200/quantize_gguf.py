@@ -653,8 +653,8 @@ def convert(options: Options) -> dict:
             cap = max(cap, _align(p.n_per_row * SOURCE_DTYPES[p.source_dtype][2]), _align(p.nbytes // p.n_rows))
     chunk = max(1 << 12, min(options.chunk_bytes, cap // (3 * n_gpus)))
     fd, out_fd = os.open(options.src, os.O_RDONLY), -1
-    readers = ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1))
-    writers = ThreadPoolExecutor(max_workers=min(4, os.cpu_count() or 1))
+    readers = ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1))
+    writers = ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1))
     READ_PIECE = 16 << 20
     # where every tensor's bytes go in the output file: known before anything is encoded, so finished pieces are
     # written at their place by a pool of writer threads while the GPUs work on the next batch
@@ -772,7 +772,7 @@ def convert(options: Options) -> dict:
             except OSError:
                 pass
     result["timings"] = dict(spent, total=clock() - began, tensors=len(plans), cuda_tensors=sum(1 for p in plans if p.qtype != p.source_dtype),
-                             threads=min(8, os.cpu_count() or 1), scratch=cap, cuda_vram=chunk, **counts)
+                             threads=min(16, os.cpu_count() or 1), scratch=cap, cuda_vram=chunk, **counts)
     return result
 
 
