@@ -435,8 +435,12 @@ def main() -> None:
                                             check=(rank == 0), cpu=(rank == 0 and world == 1 and not args.no_cpu_baseline))
         if world == 1 and roofline_e2e is not None:
             host_api = host_pointer_e2e(lib, x_host, roofline_e2e)
-        convert = bench_quant.convert_block(torch, dist if world > 1 else None, lib, device, rank, world,
-                                            link=roofline_e2e if world > 1 or args.gpus == 1 else None, gpus=args.gpus)
+        link = roofline_e2e if world > 1 or args.gpus == 1 else None
+        convert = bench_quant.convert_block(torch, dist if world > 1 else None, lib, device, rank, world, link=link, gpus=args.gpus,
+                                            keep_sources=True)
+        # the same set from a bf16 checkpoint: the 16-bit values cross the host link as they are and are widened on the GPU
+        convert["bf16_source"] = bench_quant.convert_block(torch, dist if world > 1 else None, lib, device, rank, world, link=link,
+                                                           gpus=args.gpus, src_dtype="bf16", reuse=convert.pop("_sources"))
     clocks = sampler.stop()
     if quant is not None and clocks.get("sm_mhz"):
         bench_quant.add_issue_fractions(quant, clocks["sm_mhz"])

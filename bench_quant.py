@@ -425,13 +425,16 @@ def run_convert_file(args, torch, lib, rank, world):
         shutil.rmtree(tmp, ignore_errors=True)
 
 
-def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_dtype="f32", iterations=2) -> dict:
+def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_dtype="f32", iterations=2, reuse=None,
+                  keep_sources=False) -> dict:
     """Whole-model conversion, pinned host source in, pinned host blocks out: the Llama-3-8B-shaped tensor set
     (226 tensors, 8.03 G elements, Q4_K_M mix).  One process: the in-process pool over `gpus` GPUs.  Under torchrun
     (one process per GPU): every rank derives its share of the shards from the plan alone and streams it through its
     own GPU; no rank talks to another except for the barrier and the max-over-ranks time (strong scaling).
     The values of one tensor per distinct shape are generated (tests/inputs.conversion_tensor) and shared by the
-    tensors of that shape; afterwards row ranges of the encoded output are compared with the CPU checker."""
+    tensors of that shape; afterwards row ranges of the encoded output are compared with the CPU checker.
+    `reuse`: the pinned fp32 sources of an earlier call (`keep_sources=True` returns them under "_sources"), from which a
+    16-bit run derives its sources instead of drawing the values again."""
     from libgguf_b200 import row_size
     from libgguf_b200.convert import SOURCE_DTYPES, ConversionPipeline, assign_shards, llama3_8b_plan, plan_shards
     inp = _inputs()
@@ -443,9 +446,14 @@ def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_
     names = {(rows, cols): name for name, rows, cols in inp.CONVERSION_SHAPES}
     sources, pinned = {}, {}
     for key in names:
+        if reuse is not None and src_dtype == "f32":
+            pinned[key] = reuse[key]
+            continue
         pinned[key] = torch.empty(key, dtype=src_torch).pin_memory()
         if src_dtype == "f32":   # drawn straight into the pinned buffer, blocks of rows on several threads
             inp.conversion_tensor(names[key], key[0], key[1], out=pinned[key].numpy())
+        elif reuse is not None:
+            pinned[key].copy_(reuse[key])
         else:
             pinned[key].copy_(torch.from_numpy(inp.conversion_tensor(names[key], key[0], key[1])).to(src_torch))
     for key, t in pinned.items():
@@ -523,6 +531,8 @@ def convert_block(torch, dist, lib, device, rank, world, link=None, gpus=1, src_
            "all_times_s": [round(x, 4) for x in times], "pipeline_rank0": stats, "verified": ok,
            "link_rates_GBps_per_rank": rates,
            "note": "one generated tensor per distinct shape, shared by the tensors of that shape (3.3 GB of pinned source)"}
+    if keep_sources and src_dtype == "f32":
+        out["_sources"] = pinned
     if link is not None:
         # what plain copies of the same bytes would take on this host link at this N (each direction alone; they overlap)
         t_link = max(link_bytes / (link["h2d_alone_GBps"] * 1e9), out_bytes / (link["d2h_alone_GBps"] * 1e9))
