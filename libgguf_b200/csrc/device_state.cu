@@ -62,8 +62,11 @@ template <class T>
 const T *upload(Slot &slot, const std::vector<T> &host) {
     void *p = nullptr;
     const size_t bytes = host.size() * sizeof(T);
-    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    if (bytes && cudaMemcpy(p, host.data(), bytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+    // 64 zero bytes follow every table: the lattice quantizers read their neighbour lists in aligned 32-byte windows,
+    // and the window over the last entries of the last list reaches past the data
+    if (cudaMalloc(&p, bytes + 64) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaMemset(static_cast<char *>(p) + bytes, 0, 64) != cudaSuccess ||
+        (bytes && cudaMemcpy(p, host.data(), bytes, cudaMemcpyHostToDevice) != cudaSuccess)) {
         cudaGetLastError();
         cudaFree(p);
         return nullptr;

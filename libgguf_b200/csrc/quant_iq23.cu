@@ -212,7 +212,8 @@ constexpr unsigned long long kNoWinner = ~0ull;
 // the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
 template <int GD, int TMAX, int PER>
 GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
-                          const float *xs, const float *ws, const uint32_t *gridh, const uint16_t *__restrict__ lists) {
+                          const float *xs, const float *ws, const uint32_t *gridh, const uint16_t *__restrict__ lists,
+                          uint32_t grid_mask) {
     constexpr int AHEAD = PER == 2 ? 4 : 3;  // list entries are fetched this many steps early, across list boundaries
     const uint32_t share = (E + 31) >> 5;
     uint32_t e = umin((uint32_t)lane * share, E);
@@ -240,14 +241,32 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, co
     const uint16_t *fnb = lists + tk.list + 1;
     constexpr int RW = PER / 2;  // words per step: two 12-bit entries each, the count in bits 24.. of the first
     uint32_t ring[AHEAD][RW];
+    // A step's PER consecutive 16-bit entries start at any even address.  They are read as the aligned 32-byte window
+    // that holds them (two 16-byte loads; a load per entry, with 32 lanes on 32 different lines, made the list fetches the
+    // largest user of the L1 / shared-memory pipe), shifted into place by word selects and one funnel shift per word, and
+    // repacked two 12-bit entries to a word.  Entries past the end of the list or of the lane's stretch are whatever
+    // follows in memory (the tables are padded); they are masked to a valid codebook index where they are used and
+    // their distances are ignored.
     auto fetch = [&](uint32_t (&rec)[RW]) {
 #pragma unroll
         for (int q = 0; q < RW; ++q) rec[q] = 0;
         if (fe < end) {
             const uint32_t cnt = umin(umin(fn - fj, end - fe), (uint32_t)PER);
+            const uintptr_t at = reinterpret_cast<uintptr_t>(fnb + fj);
+            const uint4 *win = reinterpret_cast<const uint4 *>(at & ~(uintptr_t)15);
+            const uint4 a = __ldg(win), b = __ldg(win + 1);
+            const uint32_t o = (uint32_t)at & 15u;   // even
+            uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            uint32_t u[6], t4[RW + 1];
 #pragma unroll
-            for (int q = 0; q < PER; ++q)
-                rec[q / 2] |= (uint32_t)__ldg(fnb + fj + ((uint32_t)q < cnt ? q : 0)) << (12 * (q & 1));
+            for (int k = 0; k < 6; ++k) u[k] = (o & 4u) ? w[k + 1] : w[k];
+#pragma unroll
+            for (int k = 0; k <= RW; ++k) t4[k] = (o & 8u) ? u[k + 2] : u[k];
+#pragma unroll
+            for (int q = 0; q < RW; ++q) {
+                const uint32_t v = __funnelshift_r(t4[q], t4[q + 1], (o & 2u) * 8u);
+                rec[q] = (v & 0xFFFu) | ((v >> 4) & 0xFFF000u);
+            }
             rec[0] |= cnt << 24;
             fe += cnt;
             fj += cnt;
@@ -275,7 +294,7 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, co
         uint32_t g[PER];
         float d2[PER];
 #pragma unroll
-        for (int q = 0; q < PER; ++q) g[q] = (rec[q / 2] >> (12 * (q & 1))) & 0xFFFu;
+        for (int q = 0; q < PER; ++q) g[q] = (rec[q / 2] >> (12 * (q & 1))) & grid_mask;
 #pragma unroll
         for (int q = 0; q < PER; ++q) d2[q] = neighbour_d2<GD>(gridh, (int)g[q], tk.scale, xv, wv);
 #pragma unroll
@@ -495,7 +514,8 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 }
             }
             __syncwarp();
-            if (all >> 10) balanced_scan<GD, TMAX, T::PER>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, lists);
+            if (all >> 10) balanced_scan<GD, TMAX, T::PER>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, lists,
+                                                            (uint32_t)tab.grid_size - 1u);
             __syncwarp();
             slot = slot0;
 #pragma unroll
