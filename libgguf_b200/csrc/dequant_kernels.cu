@@ -952,11 +952,15 @@ GGUF_D void planes4(uint32_t p01, uint32_t p23, uint32_t &lo, uint32_t &hi) {
     hi = __byte_perm(p01, p23, 0x7531u);
 }
 // four outputs: nibble j of sel (0..7) picks the pattern of element j from the eight in (lo_a, lo_b) / (hi_a, hi_b)
-GGUF_D void select4(uint32_t sel, uint32_t lo_a, uint32_t lo_b, uint32_t hi_a, uint32_t hi_b, uint32_t *w) {
-    const uint32_t l = __byte_perm(lo_a, lo_b, sel), h = __byte_perm(hi_a, hi_b, sel);
+GGUF_D void select4(uint32_t sel, uint32_t lo_a, uint32_t lo_b, uint32_t hi_a, uint32_t hi_b, uint32_t *w, uint32_t sign_plane = 0u) {
+    const uint32_t l = __byte_perm(lo_a, lo_b, sel), h = __byte_perm(hi_a, hi_b, sel) ^ sign_plane;
     w[0] = __byte_perm(l, h, 0x5140u);
     w[1] = __byte_perm(l, h, 0x7362u);
 }
+
+// Four sign bits (bit j = element j negative) -> 0x80 in byte j, to be XORed into a plane of high bytes.  The four
+// shifted copies the multiplication adds up occupy disjoint bit positions (7 k + j), so nothing carries.
+GGUF_D uint32_t sign_plane4(uint32_t s4) { return ((s4 * 0x00204081u) & 0x01010101u) << 7; }
 
 template <>
 struct Fast<GGML_TYPE_IQ2_XXS> {
@@ -978,6 +982,24 @@ struct Fast<GGML_TYPE_IQ2_XXS> {
         for (int k = 0; k < 2; ++k)
             emit_signed2(t->entry.v[(pair >> (8 * k)) & 0xFFu], t->signs.v[(aux1 >> (7 * (l + k))) & 127], c.x, v + 8 * k);
     }
+    // 16-bit outputs by selection: |value| is one of db * {8, 25, 43}; the sign planes are computed from the sign bits
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ2XXS) *>(tab);
+        const uint8_t *q = b + 2 + 8 * (e0 >> 5);
+        const uint32_t aux1 = lds_u32_a2(q + 4);
+        const int l = (e0 >> 3) & 3;  // 0 or 2
+        const uint32_t pair = lds_u16(q + l);
+        uint32_t lo, hi;
+        planes4(pack16<OutT>(c.x * 8.f, c.x * 25.f), pack16<OutT>(c.x * 43.f, 0.f), lo, hi);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t e = t->entry.v[(pair >> (8 * k)) & 0xFFu];
+            const uint32_t sg = iq_signs_from_index((aux1 >> (7 * (l + k))) & 127u);
+            select4(e, lo, 0u, hi, 0u, w + 4 * k, sign_plane4(sg & 15u));
+            select4(e >> 16, lo, 0u, hi, 0u, w + 4 * k + 2, sign_plane4(sg >> 4));
+        }
+    }
 };
 
 template <>
@@ -996,6 +1018,20 @@ struct Fast<GGML_TYPE_IQ2_XS> {
         for (int k = 0; k < 2; ++k) {
             const uint32_t q = lds_u16(b + 2 + 2 * ((e0 >> 3) + k));
             emit_signed2(t->entry.v[q & 511u], t->signs.v[q >> 9], c.x, v + 8 * k);
+        }
+    }
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ2XS) *>(tab);
+        uint32_t lo, hi;
+        planes4(pack16<OutT>(c.x * 8.f, c.x * 25.f), pack16<OutT>(c.x * 43.f, 0.f), lo, hi);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t q = lds_u16(b + 2 + 2 * ((e0 >> 3) + k));
+            const uint32_t e = t->entry.v[q & 511u];
+            const uint32_t sg = iq_signs_from_index(q >> 9);
+            select4(e, lo, 0u, hi, 0u, w + 4 * k, sign_plane4(sg & 15u));
+            select4(e >> 16, lo, 0u, hi, 0u, w + 4 * k + 2, sign_plane4(sg >> 4));
         }
     }
 };
@@ -1022,6 +1058,23 @@ struct Fast<GGML_TYPE_IQ2_S> {
             emit_signed2(t->entry.v[idx], t->signs.v[(signs >> (8 * k)) & 0xFFu], c.x, v + 8 * k);
         }
     }
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ2S) *>(tab);
+        const int g = e0 >> 3, ib32 = g >> 2;
+        const uint32_t qh = b[66 + ib32];
+        const uint32_t low = lds_u16(b + 2 + g), signs = lds_u16(b + 2 + 32 + g);  // g is even
+        uint32_t lo, hi;
+        planes4(pack16<OutT>(c.x * 8.f, c.x * 25.f), pack16<OutT>(c.x * 43.f, 0.f), lo, hi);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint32_t e = t->entry.v[((low >> (8 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 0x300u)];
+            const uint32_t sg = (signs >> (8 * k)) & 0xFFu;
+            select4(e, lo, 0u, hi, 0u, w + 4 * k, sign_plane4(sg & 15u));
+            select4(e >> 16, lo, 0u, hi, 0u, w + 4 * k + 2, sign_plane4(sg >> 4));
+        }
+    }
 };
 
 template <>
@@ -1044,6 +1097,25 @@ struct Fast<GGML_TYPE_IQ3_XXS> {
             const uint32_t signs = t->signs.v[(aux >> (7 * ((g & 3) + k))) & 127];
             emit_signed3(t->entry.v[(idx >> (16 * k)) & 0xFFu], t->entry.v[(idx >> (16 * k + 8)) & 0xFFu], signs, kIq3xxsPlus0, kIq3xxsPlus1,
                          kIq3xxsMinus0, kIq3xxsMinus1, c.x, v + 8 * k);
+        }
+    }
+    // 16-bit outputs by selection: |value| is one of db * {4, 12, ..., 52, 62} (eight patterns in four planes), the sign
+    // an XOR on the plane of high bytes, computed from the sign bits (a table of ready-made planes cost a third
+    // shared-memory gather per eight elements and made this path slower than the arithmetic one).
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ3XXS) *>(tab);
+        const int g = e0 >> 3, ib32 = g >> 2;  // g even: grid points 2g .. 2g+3
+        const uint32_t aux = lds_u32_a2(b + 2 + 64 + 4 * ib32);
+        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g);
+        uint32_t lo_a, lo_b, hi_a, hi_b;
+        planes4(pack16<OutT>(c.x * 4.f, c.x * 12.f), pack16<OutT>(c.x * 20.f, c.x * 28.f), lo_a, hi_a);
+        planes4(pack16<OutT>(c.x * 36.f, c.x * 44.f), pack16<OutT>(c.x * 52.f, c.x * 62.f), lo_b, hi_b);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const uint32_t s = iq_signs_from_index((aux >> (7 * ((g & 3) + k))) & 127u);
+            select4(t->entry.v[(idx >> (16 * k)) & 0xFFu], lo_a, lo_b, hi_a, hi_b, w + 4 * k, sign_plane4(s & 15u));
+            select4(t->entry.v[(idx >> (16 * k + 8)) & 0xFFu], lo_a, lo_b, hi_a, hi_b, w + 4 * k + 2, sign_plane4(s >> 4));
         }
     }
 };
@@ -1069,6 +1141,26 @@ struct Fast<GGML_TYPE_IQ3_S> {
             const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
             const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
             emit_signed3(t->entry.v[i1], t->entry.v[i2], t->signs.v[(sg >> (8 * k)) & 0xFFu], kIq3sPlus0, kIq3sPlus1, kIq3sMinus0, kIq3sMinus1, c.x, v + 8 * k);
+        }
+    }
+    // 16-bit outputs by selection (see IQ3_XXS): |value| is one of db * {1, 3, ..., 15}
+    template <class OutT>
+    static GGUF_D void run16(const uint8_t *b, int e0, float2 c, uint32_t *w, const void *tab) {
+        const auto *t = static_cast<const decltype(k_tab_IQ3S) *>(tab);
+        const int g = e0 >> 3, ib32 = g >> 2;
+        const uint32_t qh = b[66 + ib32];
+        const uint32_t idx = lds_u32_a2(b + 2 + 2 * g), sg = lds_u16(b + 74 + g);
+        uint32_t lo_a, lo_b, hi_a, hi_b;
+        planes4(pack16<OutT>(c.x * 1.f, c.x * 3.f), pack16<OutT>(c.x * 5.f, c.x * 7.f), lo_a, hi_a);
+        planes4(pack16<OutT>(c.x * 9.f, c.x * 11.f), pack16<OutT>(c.x * 13.f, c.x * 15.f), lo_b, hi_b);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int l = (g & 3) + k;
+            const uint32_t s = (sg >> (8 * k)) & 0xFFu;
+            const uint32_t i1 = ((idx >> (16 * k)) & 0xFFu) | ((qh << (8 - 2 * l)) & 256u);
+            const uint32_t i2 = ((idx >> (16 * k + 8)) & 0xFFu) | ((qh << (7 - 2 * l)) & 256u);
+            select4(t->entry.v[i1], lo_a, lo_b, hi_a, hi_b, w + 4 * k, sign_plane4(s & 15u));
+            select4(t->entry.v[i2], lo_a, lo_b, hi_a, hi_b, w + 4 * k + 2, sign_plane4(s >> 4));
         }
     }
 };
@@ -1123,6 +1215,16 @@ struct Fast<GGML_TYPE_IQ1_M> {
         const int ib = g16 >> 1;
         const uint32_t sc = lds_u16(b + 48 + 2 * (ib >> 1));
         return make_float2(half_hw(dbits) * (float)(2 * ((sc >> (6 * (ib & 1) + 3 * (g16 & 1))) & 7) + 1), 0.f);
+    }
+    // groups g and g + 8 (g < 8): the block scale, scattered over the top nibbles of the four scale words, is put
+    // together once for both
+    static GGUF_D void prep_pair(const uint8_t *b, int g, float2 *out) {
+        const uint32_t s0 = lds_u16(b + 48), s1 = lds_u16(b + 50), s2 = lds_u16(b + 52), s3 = lds_u16(b + 54);
+        const float d = half_hw((s0 >> 12) | ((s1 >> 8) & 0x00f0u) | ((s2 >> 4) & 0x0f00u) | (s3 & 0xf000u));
+        const int sh = 6 * ((g >> 1) & 1) + 3 * (g & 1);
+        const uint32_t a = g < 4 ? s0 : s1, c = g < 4 ? s2 : s3;   // scale word (g / 2) / 2 and the one two words on
+        out[g] = make_float2(d * (float)(2 * ((a >> sh) & 7) + 1), 0.f);
+        out[g + 8] = make_float2(d * (float)(2 * ((c >> sh) & 7) + 1), 0.f);
     }
     static constexpr int kTableBytes = sizeof(k_tab_IQ1S);
     static GGUF_D const void *table() { return &k_tab_IQ1S; }
