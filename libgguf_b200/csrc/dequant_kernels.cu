@@ -1466,24 +1466,29 @@ struct Call16Elems { static constexpr int value = CallElems<D>::value; };
 template <class D>
 struct Call16Elems<D, decltype((void)D::CALL16)> { static constexpr int value = D::CALL16; };
 
+// Tiles a CTA of the fast kernel decodes.  The decoders that copy a codebook table to shared memory (1-8 KB per CTA,
+// as much as half of the 16 KB a tile's 16-bit output has) take two, so that the table, the launch and the wait for
+// the previous kernel are paid once for 16384 elements; both tiles' loads are issued before the first is decoded.
+// For the other types one tile per CTA measured fastest.
+template <class D>
+struct TilesPerCta { static constexpr int value = TableBytes<D>::value > 0 ? 2 : 1; };
+
 template <int TYPE, class OutT>
 __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                int64_t nblocks) {
     using D = Fast<TYPE>;
+    constexpr int TILES = TilesPerCta<D>::value;
     constexpr int TILE_BLOCKS = kTileElems / D::ELEMS;
     constexpr int TILE_BYTES = TILE_BLOCKS * D::BYTES;
     constexpr int TILE_VECS = (TILE_BYTES + 15) / 16;
     constexpr int TILE_GROUPS = kTileElems / D::GROUP;
     constexpr int GROUPS_PER_BLOCK = D::ELEMS / D::GROUP;
-    __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 32];
-    __shared__ float2 consts[TILE_GROUPS];
+    static_assert(TILE_BYTES % 16 == 0, "every tile starts on a 16-byte boundary");
+    __shared__ __align__(16) uint8_t tiles[TILES][TILE_VECS * 16 + 32];
+    __shared__ float2 all_consts[TILES][TILE_GROUPS];
 
     const int tid = threadIdx.x;
-    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
-    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
-    const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
-    const int nvec = (nb * D::BYTES + 15) >> 4;
-    uint4 *s16 = reinterpret_cast<uint4 *>(tile);
+    const int64_t first_block = (int64_t)blockIdx.x * TILES * TILE_BLOCKS;
     constexpr int TABLE_BYTES = TableBytes<D>::value;
     static_assert(TABLE_BYTES % 16 == 0, "the table moves as 16-byte vectors");
     __shared__ __align__(16) uint8_t table[TABLE_BYTES ? TABLE_BYTES : 16];
@@ -1497,26 +1502,41 @@ __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t
         }
     }
     grid_dependency_wait();
+    int nbs[TILES];
 #pragma unroll
-    for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
-        const int i = k * kThreads + tid;
-        if (i < nvec) s16[i] = __ldcs(g16 + i);
+    for (int ti = 0; ti < TILES; ++ti) {
+        const int64_t b0 = first_block + (int64_t)ti * TILE_BLOCKS;
+        nbs[ti] = b0 >= nblocks ? 0 : (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
+        const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * D::BYTES);  // 16-byte aligned by contract
+        const int nvec = (nbs[ti] * D::BYTES + 15) >> 4;
+        uint4 *s16 = reinterpret_cast<uint4 *>(tiles[ti]);
+#pragma unroll
+        for (int k = 0; k < (TILE_VECS + kThreads - 1) / kThreads; ++k) {
+            const int i = k * kThreads + tid;
+            if (i < nvec) s16[i] = __ldcs(g16 + i);
+        }
     }
     __syncthreads();
-    if constexpr (HasPrepPair<D>::value) {
-        constexpr int PAIRS = GROUPS_PER_BLOCK / 2;
 #pragma unroll
-        for (int k = 0; k < (TILE_GROUPS / 2 + kThreads - 1) / kThreads; ++k) {
-            const int p = k * kThreads + tid;
-            const int blk = p / PAIRS;
-            if (blk < nb) D::prep_pair(tile + blk * D::BYTES, p % PAIRS, consts + blk * GROUPS_PER_BLOCK);
-        }
-    } else {
+    for (int ti = 0; ti < TILES; ++ti) {
+        const uint8_t *tile = tiles[ti];
+        float2 *consts = all_consts[ti];
+        const int nb = nbs[ti];
+        if constexpr (HasPrepPair<D>::value) {
+            constexpr int PAIRS = GROUPS_PER_BLOCK / 2;
 #pragma unroll
-        for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
-            const int g = k * kThreads + tid;
-            const int blk = g / GROUPS_PER_BLOCK;
-            if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
+            for (int k = 0; k < (TILE_GROUPS / 2 + kThreads - 1) / kThreads; ++k) {
+                const int p = k * kThreads + tid;
+                const int blk = p / PAIRS;
+                if (blk < nb) D::prep_pair(tile + blk * D::BYTES, p % PAIRS, consts + blk * GROUPS_PER_BLOCK);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < (TILE_GROUPS + kThreads - 1) / kThreads; ++k) {
+                const int g = k * kThreads + tid;
+                const int blk = g / GROUPS_PER_BLOCK;
+                if (blk < nb) consts[g] = D::prep(tile + blk * D::BYTES, g % GROUPS_PER_BLOCK);
+            }
         }
     }
     __syncthreads();
@@ -1528,26 +1548,30 @@ __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t
     static_assert(kThreads % CALLS_PER_BLOCK == 0, "a thread keeps its position inside the block across iterations");
     const int e0 = (tid % CALLS_PER_BLOCK) * CALL;
     const int blk0 = tid / CALLS_PER_BLOCK;
-    OutT *out = dst + b0 * D::ELEMS + (int64_t)blk0 * D::ELEMS + e0;
-    const uint8_t *bp = tile + blk0 * D::BYTES;
-    const float2 *cp = consts + (blk0 * D::ELEMS + e0) / D::GROUP;
 #pragma unroll
-    for (int u = 0; u < CALLS_PER_THREAD; ++u) {
-        constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
-        if constexpr (SELECT16) {
-            if (blk0 + u * BLOCK_STEP < nb) {
-                uint32_t w[CALL / 2];
-                D::template run16<OutT>(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], w, table);
+    for (int ti = 0; ti < TILES; ++ti) {
+        const int nb = nbs[ti];
+        OutT *out = dst + (first_block + (int64_t)ti * TILE_BLOCKS) * D::ELEMS + (int64_t)blk0 * D::ELEMS + e0;
+        const uint8_t *bp = tiles[ti] + blk0 * D::BYTES;
+        const float2 *cp = all_consts[ti] + (blk0 * D::ELEMS + e0) / D::GROUP;
 #pragma unroll
-                for (int h = 0; h < CALL / 16; ++h)
-                    st_v8(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, *reinterpret_cast<const uint32_t(*)[8]>(w + 8 * h));
+        for (int u = 0; u < CALLS_PER_THREAD; ++u) {
+            constexpr int BLOCK_STEP = kThreads / CALLS_PER_BLOCK;
+            if constexpr (SELECT16) {
+                if (blk0 + u * BLOCK_STEP < nb) {
+                    uint32_t w[CALL / 2];
+                    D::template run16<OutT>(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], w, table);
+#pragma unroll
+                    for (int h = 0; h < CALL / 16; ++h)
+                        st_v8(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, *reinterpret_cast<const uint32_t(*)[8]>(w + 8 * h));
+                }
+            } else if (blk0 + u * BLOCK_STEP < nb) {
+                float v[CALL];
+                if constexpr (TABLE_BYTES > 0) D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v, table);
+                else D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
+#pragma unroll
+                for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
             }
-        } else if (blk0 + u * BLOCK_STEP < nb) {
-            float v[CALL];
-            if constexpr (TABLE_BYTES > 0) D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v, table);
-            else D::run(bp + u * BLOCK_STEP * D::BYTES, e0, cp[u * BLOCK_STEP * GROUPS_PER_BLOCK], v);
-#pragma unroll
-            for (int h = 0; h < CALL / 16; ++h) store16<OutT>(out + (int64_t)u * BLOCK_STEP * D::ELEMS + 16 * h, v + 16 * h);
         }
     }
 }
@@ -1588,26 +1612,32 @@ constexpr int kTq1Threads = 224;  // 128 tasks over bytes 0..31, 64 over bytes 3
 // Gathering the tile's outputs in shared memory first, so that every store fills whole 128-byte lines, was measured and
 // is slower (0.63 against 0.84 of the copy bandwidth): the extra pass through shared memory costs more than the
 // half-filled lines.
+constexpr int kTq1TilesPerCta = 2;  // the table copy, the launch and the wait for the previous kernel are paid once for two tiles
+
 template <class OutT>
-__global__ void __launch_bounds__(kTq1Threads, 8) dequant_tq1_select_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
+__global__ void __launch_bounds__(kTq1Threads, 6) dequant_tq1_select_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
                                                                            int64_t nblocks) {
     static_assert(sizeof(OutT) == 2, "selection works on 16-bit patterns");
     constexpr int TILE_BLOCKS = kTileElems / 256, BYTES = 54;
     constexpr int TILE_VECS = (TILE_BLOCKS * BYTES + 15) / 16;
-    __shared__ __align__(16) uint8_t tile[TILE_VECS * 16 + 16];
+    __shared__ __align__(16) uint8_t tiles[kTq1TilesPerCta][TILE_VECS * 16 + 16];
     __shared__ __align__(16) uint2 table[256];
     const int tid = threadIdx.x;
-    const int64_t b0 = (int64_t)blockIdx.x * TILE_BLOCKS;
-    const int nb = (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
     grid_dependents_may_launch();
     {   // constant data: does not wait for the previous kernel
         const uint4 *g = reinterpret_cast<const uint4 *>(&k_tq1_selectors);
         if (tid < 128) reinterpret_cast<uint4 *>(table)[tid] = __ldg(g + tid);
     }
     grid_dependency_wait();
-    const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * BYTES);  // 16-byte aligned by contract
-    const int nvec = (nb * BYTES + 15) >> 4;
-    if (tid < nvec) reinterpret_cast<uint4 *>(tile)[tid] = __ldcs(g16 + tid);  // at most 108 vectors
+    const int64_t first_block = (int64_t)blockIdx.x * kTq1TilesPerCta * TILE_BLOCKS;
+#pragma unroll
+    for (int ti = 0; ti < kTq1TilesPerCta; ++ti) {   // both tiles' loads are in flight before the first is decoded
+        const int64_t b0 = first_block + ti * TILE_BLOCKS;
+        const int nb = b0 >= nblocks ? 0 : (int)(nblocks - b0 < TILE_BLOCKS ? nblocks - b0 : TILE_BLOCKS);
+        const uint4 *g16 = reinterpret_cast<const uint4 *>(src + b0 * BYTES);  // 16-byte aligned by contract (1728 bytes per tile)
+        const int nvec = (nb * BYTES + 15) >> 4;
+        if (tid < nvec) reinterpret_cast<uint4 *>(tiles[ti])[tid] = __ldcs(g16 + tid);  // at most 108 vectors
+    }
     __syncthreads();
 
     // task -> block, first byte, element offset of digit 0, element stride between digits
@@ -1615,51 +1645,55 @@ __global__ void __launch_bounds__(kTq1Threads, 8) dequant_tq1_select_kernel(cons
     if (tid < 128) { blk = tid >> 2; at = 8 * (tid & 3); first = at; stride = 32; }
     else if (tid < 192) { blk = (tid - 128) >> 1; at = 32 + 8 * (tid & 1); first = 160 + 8 * (tid & 1); stride = 16; }
     else { blk = tid - 192; at = 48; first = 240; stride = 4; }
-    if (blk >= nb) return;
-    const uint8_t *b = tile + blk * BYTES;
-    // the block's three outputs as 16-bit patterns
-    const float d = half_hw(lds_u16(b + 52));
-    const uint32_t lut_a = pack16<OutT>(d * -1.0f, d * 0.0f), lut_b = pack16<OutT>(d * 1.0f, d * 1.0f);
-    OutT *out = dst + (b0 + blk) * 256 + first;
-    const uint32_t w0 = lds_u32_a2(b + at);
-    if (tid >= 192) {
-        // four bytes, four digits each: elements 240 + 4 n + j, sixteen consecutive outputs
-        uint2 e[4];
+#pragma unroll 1
+    for (int ti = 0; ti < kTq1TilesPerCta; ++ti) {
+        const int64_t b0 = first_block + ti * TILE_BLOCKS;
+        if (b0 + blk >= nblocks) break;
+        const uint8_t *b = tiles[ti] + blk * BYTES;
+        // the block's three outputs as 16-bit patterns
+        const float d = half_hw(lds_u16(b + 52));
+        const uint32_t lut_a = pack16<OutT>(d * -1.0f, d * 0.0f), lut_b = pack16<OutT>(d * 1.0f, d * 1.0f);
+        OutT *out = dst + (b0 + blk) * 256 + first;
+        const uint32_t w0 = lds_u32_a2(b + at);
+        if (tid >= 192) {
+            // four bytes, four digits each: elements 240 + 4 n + j, sixteen consecutive outputs
+            uint2 e[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) e[i] = table[(w0 >> (8 * i)) & 0xFFu];
-        uint32_t w[8];
+            for (int i = 0; i < 4; ++i) e[i] = table[(w0 >> (8 * i)) & 0xFFu];
+            uint32_t w[8];
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
-            const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
-            w[2 * n] = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
-            w[2 * n + 1] = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
+            for (int n = 0; n < 4; ++n) {
+                const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
+                w[2 * n] = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
+                w[2 * n + 1] = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
+            }
+            st_v8(out, w);
+            continue;
         }
-        st_v8(out, w);
-        return;
-    }
-    const uint32_t w1 = lds_u32_a2(b + at + 4);
-    uint2 e[8];
+        const uint32_t w1 = lds_u32_a2(b + at + 4);
+        uint2 e[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        e[i] = table[(w0 >> (8 * i)) & 0xFFu];
-        e[4 + i] = table[(w1 >> (8 * i)) & 0xFFu];
-    }
-#pragma unroll
-    for (int n = 0; n < 5; ++n) {
-        uint4 o;
-        if (n < 4) {
-            const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
-            o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
-            o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
-            o.z = __byte_perm(lut_a, lut_b, __byte_perm(e[4].x, e[5].x, pick));
-            o.w = __byte_perm(lut_a, lut_b, __byte_perm(e[6].x, e[7].x, pick));
-        } else {
-            o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].y, e[1].y, 0x40u));
-            o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].y, e[3].y, 0x40u));
-            o.z = __byte_perm(lut_a, lut_b, __byte_perm(e[4].y, e[5].y, 0x40u));
-            o.w = __byte_perm(lut_a, lut_b, __byte_perm(e[6].y, e[7].y, 0x40u));
+        for (int i = 0; i < 4; ++i) {
+            e[i] = table[(w0 >> (8 * i)) & 0xFFu];
+            e[4 + i] = table[(w1 >> (8 * i)) & 0xFFu];
         }
-        __stcs(reinterpret_cast<uint4 *>(out + n * stride), o);
+#pragma unroll
+        for (int n = 0; n < 5; ++n) {
+            uint4 o;
+            if (n < 4) {
+                const uint32_t pick = ((4u + n) << 4) | (uint32_t)n;
+                o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].x, e[1].x, pick));
+                o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].x, e[3].x, pick));
+                o.z = __byte_perm(lut_a, lut_b, __byte_perm(e[4].x, e[5].x, pick));
+                o.w = __byte_perm(lut_a, lut_b, __byte_perm(e[6].x, e[7].x, pick));
+            } else {
+                o.x = __byte_perm(lut_a, lut_b, __byte_perm(e[0].y, e[1].y, 0x40u));
+                o.y = __byte_perm(lut_a, lut_b, __byte_perm(e[2].y, e[3].y, 0x40u));
+                o.z = __byte_perm(lut_a, lut_b, __byte_perm(e[4].y, e[5].y, 0x40u));
+                o.w = __byte_perm(lut_a, lut_b, __byte_perm(e[6].y, e[7].y, 0x40u));
+            }
+            __stcs(reinterpret_cast<uint4 *>(out + n * stride), o);
+        }
     }
 }
 
@@ -1674,7 +1708,7 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
     const int aligned = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
     if constexpr (TYPE == GGML_TYPE_TQ1_0 && sizeof(OutT) == 2) {
         if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-            const cudaError_t launched = launch_overlapped(dequant_tq1_select_kernel<OutT>, (unsigned)grid, kTq1Threads, stream,
+            const cudaError_t launched = launch_overlapped(dequant_tq1_select_kernel<OutT>, (unsigned)((grid + kTq1TilesPerCta - 1) / kTq1TilesPerCta), kTq1Threads, stream,
                                                            static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks);
             count_launch();
             return launched != cudaSuccess ? launched : cudaGetLastError();
@@ -1682,7 +1716,8 @@ cudaError_t launch_typed(const void *src, void *dst, int64_t nelems, cudaStream_
     }
     if constexpr (Fast<TYPE>::kEnabled) {
         if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-            const cudaError_t launched = launch_overlapped(dequant_fast_kernel<TYPE, OutT>, (unsigned)grid, kThreads, stream,
+            constexpr int TILES = TilesPerCta<Fast<TYPE>>::value;
+            const cudaError_t launched = launch_overlapped(dequant_fast_kernel<TYPE, OutT>, (unsigned)((grid + TILES - 1) / TILES), kThreads, stream,
                                                            static_cast<const uint8_t *>(src), static_cast<OutT *>(dst), nblocks);
             count_launch();
             return launched != cudaSuccess ? launched : cudaGetLastError();
