@@ -555,6 +555,7 @@ struct CallElems<D, decltype((void)D::CALL)> { static constexpr int value = D::C
 template <>
 struct Fast<GGML_TYPE_Q8_0> {
     static constexpr bool kEnabled = true;
+    static constexpr int TILES = 1;
     static constexpr int ELEMS = 32, BYTES = 34, GROUP = 32;
     static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), 0.f); }
     static GGUF_D void run(const uint8_t *b, int e0, float2 c, float *v) {
@@ -596,6 +597,7 @@ struct Fast<GGML_TYPE_Q5_K> {
 template <>
 struct Fast<GGML_TYPE_Q6_K> {
     static constexpr bool kEnabled = true;
+    static constexpr int TILES = 1;
     static constexpr int ELEMS = 256, BYTES = 210, GROUP = 16;
     // group g covers elements 16g..16g+15: half n = g/8, quarter = (g/2)%4, is = g%2 -> scale 8n + is + 2*quarter
     static GGUF_D float2 prep(const uint8_t *b, int g) {
@@ -792,6 +794,7 @@ struct Fast<GGML_TYPE_Q5_0> {
 template <>
 struct Fast<GGML_TYPE_Q5_1> {
     static constexpr bool kEnabled = true;
+    static constexpr int TILES = 1;
     static constexpr int ELEMS = 32, BYTES = 24, GROUP = 32, CALL = 32;
     static GGUF_D float2 prep(const uint8_t *b, int) { return make_float2(half_hw(lds_u16(b)), -half_hw(lds_u16(b + 2))); }
     static GGUF_D void run(const uint8_t *b, int, float2 c, float *v) {
@@ -1466,12 +1469,16 @@ struct Call16Elems { static constexpr int value = CallElems<D>::value; };
 template <class D>
 struct Call16Elems<D, decltype((void)D::CALL16)> { static constexpr int value = D::CALL16; };
 
-// Tiles a CTA of the fast kernel decodes.  The decoders that copy a codebook table to shared memory (1-8 KB per CTA,
-// as much as half of the 16 KB a tile's 16-bit output has) take two, so that the table, the launch and the wait for
-// the previous kernel are paid once for 16384 elements; both tiles' loads are issued before the first is decoded.
-// For the other types one tile per CTA measured fastest.
+// Tiles a CTA of the fast kernel decodes: two (16384 elements), both tiles' loads issued before the first is decoded,
+// so that the launch of the CTA, the wait for the previous kernel and, for the codebook types, the copy of the table
+// to shared memory (1-8 KB, as much as half of the 16 KB of 16-bit output a tile has) are paid once for both.
+// Measured on 14336x4096 -> fp16 against one tile per CTA: the codebook types gain 3-14 points of the copy bandwidth
+// (IQ3_S 0.89 -> 0.95, IQ1_M 0.88 -> 0.93), IQ4_NL 0.87 -> 0.95, MXFP4 0.88 -> 0.95, Q3_K 0.90 -> 0.94, Q5_K 0.95 -> 0.97;
+// the three types with the most encoded bytes per element lose 1-2 points and keep one tile (they set TILES = 1).
+template <class D, class = void>
+struct TilesPerCta { static constexpr int value = 2; };
 template <class D>
-struct TilesPerCta { static constexpr int value = TableBytes<D>::value > 0 ? 2 : 1; };
+struct TilesPerCta<D, decltype((void)D::TILES)> { static constexpr int value = D::TILES; };
 
 template <int TYPE, class OutT>
 __global__ void __launch_bounds__(kThreads, 8) dequant_fast_kernel(const uint8_t *__restrict__ src, OutT *__restrict__ dst,
