@@ -1475,6 +1475,8 @@ struct Call16Elems<D, decltype((void)D::CALL16)> { static constexpr int value = 
 // Measured on 14336x4096 -> fp16 against one tile per CTA: the codebook types gain 3-14 points of the copy bandwidth
 // (IQ3_S 0.89 -> 0.95, IQ1_M 0.88 -> 0.93), IQ4_NL 0.87 -> 0.95, MXFP4 0.88 -> 0.95, Q3_K 0.90 -> 0.94, Q5_K 0.95 -> 0.97;
 // the three types with the most encoded bytes per element lose 1-2 points and keep one tile (they set TILES = 1).
+// Four tiles per CTA are slower again for nearly every type (0.80-0.92): the staged tiles and constants then take
+// enough shared memory to cost resident CTAs.
 template <class D, class = void>
 struct TilesPerCta { static constexpr int value = 2; };
 template <class D>
