@@ -62,8 +62,7 @@ template <class T>
 const T *upload(Slot &slot, const std::vector<T> &host) {
     void *p = nullptr;
     const size_t bytes = host.size() * sizeof(T);
-    // 64 zero bytes follow every table: the lattice quantizers read their neighbour lists in aligned 32-byte windows,
-    // and the window over the last entries of the last list reaches past the data
+    // 64 zero bytes follow every table (a look-ahead read just past the last entry stays inside the allocation)
     if (cudaMalloc(&p, bytes + 64) != cudaSuccess) { cudaGetLastError(); return nullptr; }
     if (cudaMemset(static_cast<char *>(p) + bytes, 0, 64) != cudaSuccess ||
         (bytes && cudaMemcpy(p, host.data(), bytes, cudaMemcpyHostToDevice) != cudaSuccess)) {
@@ -105,18 +104,24 @@ const DeviceState *device_state_for(int type, int dev) {
         t.grid = upload(slot, h.grid);
         t.map = upload(slot, h.map);
         t.neighbours = upload(slot, h.neighbours);
-        {   // one load then tells a scan where its list is and how long (offsets < 2^21, counts < 2^9 for every codebook)
+        if (id != IQT_1S) {   // one load then tells a scan where its list is and how many steps it has
             std::vector<int32_t> packed(h.map.size());
+            std::vector<uint16_t> steps;
             for (size_t i = 0; i < h.map.size(); ++i) {
                 const int32_t m = h.map[i];
                 if (m >= 0) { packed[i] = m; continue; }
                 const uint32_t off = (uint32_t)(-m - 1), n = h.neighbours[off];
-                if (off >= (1u << 21) || n >= (1u << 9)) return nullptr;
-                packed[i] = -(int32_t)(((off << 9) | n) + 1);
+                const uint32_t first_step = (uint32_t)(steps.size() / kIqStepEntries), nsteps = (n + kIqStepEntries - 1) / kIqStepEntries;
+                if (first_step >= (1u << 22) || nsteps >= (1u << 8) || (size_t)h.grid_size * h.dims * 2 > 65536) return nullptr;
+                for (uint32_t e = 0; e < nsteps * kIqStepEntries; ++e)
+                    steps.push_back((uint16_t)(h.neighbours[off + 1 + (e < n ? e : 0)] * h.dims * 2));
+                packed[i] = -(int32_t)(((first_step << 8) | nsteps) + 1);
             }
-            t.map_n = upload(slot, packed);
+            t.map_s = upload(slot, packed);
+            t.steps = reinterpret_cast<const uint2 *>(upload(slot, steps));
+            if (!t.map_s || !t.steps) return nullptr;
         }
-        if (!t.grid || !t.map || !t.neighbours || !t.map_n) return nullptr;
+        if (!t.grid || !t.map || !t.neighbours) return nullptr;
         t.grid_size = h.grid_size;
         t.dims = h.dims;
         t.map_size = (int)h.map.size();

@@ -10,13 +10,20 @@
 namespace gguf {
 
 constexpr int kMaxDevices = 64;
+constexpr int kIqStepEntries = 4;
 
 // One IQ codebook prepared for searching (device pointers).
 struct IqSearchTable {
     const uint8_t *grid = nullptr;         // grid_size x dims bytes, coordinate value 2*code+1
     const int32_t *map = nullptr;          // lattice index -> grid index (>= 0) or -(offset+1) into neighbours
     const uint16_t *neighbours = nullptr;  // [count, idx0, idx1, ...] runs
-    const int32_t *map_n = nullptr;        // as map, the list's count folded in: -(((offset << 9) | count) + 1)
+    // The neighbour lists again, laid out for the IQ2 / IQ3 scans: every list padded to whole steps of kIqStepEntries
+    // entries with copies of its first entry (a copy's distance equals the first entry's, so it is never a strict
+    // improvement), steps 8-byte aligned, an entry stored as the byte offset of its codebook row in the kernel's
+    // staged codebook (grid index x dims x 2).  map_s is map with a list's first step and step count folded in:
+    // -(((first_step << 8) | steps) + 1).  Both absent for the IQ1 codebook.
+    const uint2 *steps = nullptr;
+    const int32_t *map_s = nullptr;
     int grid_size = 0;
     int dims = 0;
     int map_size = 0;

@@ -33,27 +33,27 @@ constexpr unsigned kFull = 0xffffffffu;
 
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
-    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4, PER = 4;
+    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = true;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_XS> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5, PER = 6;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_S> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5, PER = 4;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_XXS> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6, PER = 6;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6;
     static constexpr bool PARITY = true, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_S> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6, PER = 6;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 0.f;  // upstream tests `!max`
 };
@@ -149,18 +149,19 @@ GGUF_D float qp_quants_reg(int nmax, const float (&x)[N], int (&L)[N], const flo
     return suml2 > 0.0f ? sumlx / suml2 : 0.0f;
 }
 
-// Codebook entry g of the staged codebook: coordinates are small odd integers, kept as bfloat16 pairs (exact), so an
-// entry is one 16-byte (8 coordinates) or 8-byte (4 coordinates) read and a shift or mask per coordinate.  As floats
-// an entry of eight took two 16-byte reads that used half of the banks, and the gathers of 32 lanes at 32 random
-// entries kept the shared-memory pipe busier than the arithmetic.
+// Codebook row at byte offset `at` of the staged codebook: coordinates are small odd integers, kept as bfloat16 pairs
+// (exact), so a row is one 16-byte (8 coordinates) or 8-byte (4 coordinates) read and a shift or mask per coordinate.
+// As floats a row of eight took two 16-byte reads that used half of the banks, and the gathers of 32 lanes at 32
+// random rows kept the shared-memory pipe busier than the arithmetic.
 template <int GD>
-GGUF_D void grid_entry(const uint32_t *gridh, int g, float (&q)[GD]) {
+GGUF_D void grid_row(const uint32_t *gridh, uint32_t at, float (&q)[GD]) {
     uint32_t w[GD / 2];
+    const char *row = reinterpret_cast<const char *>(gridh) + at;
     if constexpr (GD == 8) {
-        const uint4 t = *reinterpret_cast<const uint4 *>(gridh + g * 4);
+        const uint4 t = *reinterpret_cast<const uint4 *>(row);
         w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
     } else {
-        const uint2 t = *reinterpret_cast<const uint2 *>(gridh + g * 2);
+        const uint2 t = *reinterpret_cast<const uint2 *>(row);
         w[0] = t.x; w[1] = t.y;
     }
 #pragma unroll
@@ -169,12 +170,14 @@ GGUF_D void grid_entry(const uint32_t *gridh, int g, float (&q)[GD]) {
         q[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
 }
-
-// Weighted squared distance of codebook entry g from the group, terms added in coordinate order.
 template <int GD>
-GGUF_D float neighbour_d2(const uint32_t *gridh, int g, float scale, const float (&xv)[GD], const float (&wv)[GD]) {
+GGUF_D void grid_entry(const uint32_t *gridh, int g, float (&q)[GD]) { grid_row<GD>(gridh, (uint32_t)g * (GD * 2), q); }
+
+// Weighted squared distance of the codebook row at byte offset `at` from the group, terms added in coordinate order.
+template <int GD>
+GGUF_D float neighbour_d2(const uint32_t *gridh, uint32_t at, float scale, const float (&xv)[GD], const float (&wv)[GD]) {
     float q[GD];
-    grid_entry<GD>(gridh, g, q);
+    grid_row<GD>(gridh, at, q);
     float d2 = 0;
 #pragma unroll
     for (int i = 0; i < GD; ++i) {
@@ -195,116 +198,83 @@ GGUF_D void load_staged(const float *p, float (&x)[N]) {  // shared memory, 16-b
 
 // One neighbour scan a warp has to run: which list, which group of which lane's block, at which scale.
 struct ScanTask {
-    uint32_t list;   // offset of the list's count in the neighbour array
-    uint32_t xoff;   // float offset of the group in the warp's staged magnitudes / weights
+    uint32_t base;    // the list's first step in the step array
+    uint32_t nsteps;  // its length in steps
     float scale;
-    uint32_t n;      // list length
+    uint32_t xoff;    // float offset of the group in the warp's staged magnitudes / weights
 };
 
 constexpr unsigned long long kNoWinner = ~0ull;
+constexpr int PER = kIqStepEntries;
 
-// The warp's pending scans, evaluated with the work spread evenly: the T lists are laid end to end
-// (E entries, `first[t]` = position of list t's first entry) and every lane takes a contiguous
-// stretch of E/32 entries, whatever lists it crosses.  A list's winner is the first strict minimum
-// in list order, i.e. the minimum of (distance bits, position) as one 64-bit key; a lane that saw
-// a whole list stores its key, lanes that share a list combine theirs with a shared-memory
-// atomic minimum.  Distances are sums of non-negative terms, so their bit patterns order like
-// the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
-template <int GD, int TMAX, int PER>
-GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
-                          const float *xs, const float *ws, const uint32_t *gridh, const uint16_t *__restrict__ lists,
-                          uint32_t grid_mask) {
-    constexpr int AHEAD = PER == 2 ? 4 : 3;  // list entries are fetched this many steps early, across list boundaries
-    const uint32_t share = (E + 31) >> 5;
-    uint32_t e = umin((uint32_t)lane * share, E);
-    const uint32_t end = umin(e + share, E);
-    if (e >= end) return;
+// The warp's pending scans, evaluated with the work spread evenly.  A list is a whole number of steps of PER
+// entries (its tail repeats its first entry, which can never be a strict improvement), so the T lists laid end to end
+// are S steps (`first[t]` = position of list t's first step) and every lane takes a contiguous stretch of S/32 steps,
+// whatever lists it crosses: every lane runs the same number of iterations, each one aligned 8-byte load and PER
+// independent ordered sums with no bookkeeping per entry.  A list's winner is the first strict minimum in list order,
+// i.e. the minimum of (distance bits, position) as one 64-bit key; a lane that saw a whole list stores its key, lanes
+// that share a list combine theirs with a shared-memory atomic minimum.  Distances are sums of non-negative terms,
+// so their bit patterns order like the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
+template <int GD, int TMAX>
+GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
+                          const float *xs, const float *ws, const uint32_t *gridh, const uint2 *__restrict__ steps) {
+    constexpr int AHEAD = 3;  // steps are fetched this many iterations early, across list boundaries
+    const uint32_t share = (S + 31) >> 5;
+    uint32_t s = umin((uint32_t)lane * share, S);
+    const uint32_t end = umin(s + share, S);
+    if (s >= end) return;
     int t = 0;
 #pragma unroll
     for (int step = TMAX / 2; step; step >>= 1) {
         const int c = t + step;
-        if (c < T && first[c] <= e) t = c;
+        if (c < T && first[c] <= s) t = c;
     }
     ScanTask tk = tasks[t];
     float xv[GD], wv[GD];
     load_staged<GD>(xs + tk.xoff, xv);
     load_staged<GD>(ws + tk.xoff, wv);
-    uint32_t j = e - first[t];
+    uint32_t j = s - first[t];
     bool whole = j == 0;
     float best_d2 = FLT_MAX;
     uint32_t best_at = 0xFFFFFFFFu;
-    // Entries are taken PER at a time (PER independent ordered sums in flight); where a list or the lane's stretch
-    // ends inside a step the missing entries repeat the first one and are ignored.  The fetch cursor forms the same
-    // steps AHEAD of the evaluation cursor and hands them over packed two to a word.
+    // the fetch cursor runs AHEAD steps in front of the evaluation cursor
     int ft = t;
-    uint32_t fj = j, fn = tk.n, fe = e;
-    const uint16_t *fnb = lists + tk.list + 1;
-    constexpr int RW = PER / 2;  // words per step: two 12-bit entries each, the count in bits 24.. of the first
-    uint32_t ring[AHEAD][RW];
-    // A step's PER consecutive 16-bit entries start at any even address.  They are read as the aligned 32-byte window
-    // that holds them (two 16-byte loads; a load per entry, with 32 lanes on 32 different lines, made the list fetches the
-    // largest user of the L1 / shared-memory pipe), shifted into place by word selects and one funnel shift per word, and
-    // repacked two 12-bit entries to a word.  Entries past the end of the list or of the lane's stretch are whatever
-    // follows in memory (the tables are padded); they are masked to a valid codebook index where they are used and
-    // their distances are ignored.
-    auto fetch = [&](uint32_t (&rec)[RW]) {
-#pragma unroll
-        for (int q = 0; q < RW; ++q) rec[q] = 0;
-        if (fe < end) {
-            const uint32_t cnt = umin(umin(fn - fj, end - fe), (uint32_t)PER);
-            const uintptr_t at = reinterpret_cast<uintptr_t>(fnb + fj);
-            const uint4 *win = reinterpret_cast<const uint4 *>(at & ~(uintptr_t)15);
-            const uint4 a = __ldg(win), b = __ldg(win + 1);
-            const uint32_t o = (uint32_t)at & 15u;   // even
-            uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            uint32_t u[6], t4[RW + 1];
-#pragma unroll
-            for (int k = 0; k < 6; ++k) u[k] = (o & 4u) ? w[k + 1] : w[k];
-#pragma unroll
-            for (int k = 0; k <= RW; ++k) t4[k] = (o & 8u) ? u[k + 2] : u[k];
-#pragma unroll
-            for (int q = 0; q < RW; ++q) {
-                const uint32_t v = __funnelshift_r(t4[q], t4[q + 1], (o & 2u) * 8u);
-                rec[q] = (v & 0xFFFu) | ((v >> 4) & 0xFFF000u);
-            }
-            rec[0] |= cnt << 24;
-            fe += cnt;
-            fj += cnt;
-            if (fj == fn && fe < end) {
+    uint32_t fleft = tk.nsteps - j, fs = s;
+    const uint2 *fp = steps + tk.base + j;
+    uint2 ring[AHEAD];
+    auto fetch = [&](uint2 &rec) {
+        if (fs < end) {
+            rec = __ldg(fp);
+            ++fp;
+            ++fs;
+            if (--fleft == 0 && fs < end) {
                 ++ft;
-                fj = 0;
-                fn = tasks[ft].n;
-                fnb = lists + tasks[ft].list + 1;
+                const uint2 h = *reinterpret_cast<const uint2 *>(tasks + ft);
+                fp = steps + h.x;
+                fleft = h.y;
             }
         }
     };
 #pragma unroll
-    for (int d = 0; d < AHEAD; ++d) fetch(ring[d]);
-    while (e < end) {
-        uint32_t rec[RW];
+    for (int d = 0; d < AHEAD; ++d) { ring[d] = make_uint2(0u, 0u); fetch(ring[d]); }
+    while (s < end) {
+        const uint2 rec = ring[0];
 #pragma unroll
-        for (int q = 0; q < RW; ++q) rec[q] = ring[0][q];
-#pragma unroll
-        for (int d = 0; d + 1 < AHEAD; ++d) {
-#pragma unroll
-            for (int q = 0; q < RW; ++q) ring[d][q] = ring[d + 1][q];
-        }
+        for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
         fetch(ring[AHEAD - 1]);
-        const uint32_t cnt = rec[0] >> 24;
-        uint32_t g[PER];
+        static_assert(PER == 4, "a step is one 8-byte record of four 16-bit row offsets");
+        const uint32_t at[PER] = {rec.x & 0xFFFFu, rec.x >> 16, rec.y & 0xFFFFu, rec.y >> 16};
         float d2[PER];
 #pragma unroll
-        for (int q = 0; q < PER; ++q) g[q] = (rec[q / 2] >> (12 * (q & 1))) & grid_mask;
-#pragma unroll
-        for (int q = 0; q < PER; ++q) d2[q] = neighbour_d2<GD>(gridh, (int)g[q], tk.scale, xv, wv);
+        for (int q = 0; q < PER; ++q) d2[q] = neighbour_d2<GD>(gridh, at[q], tk.scale, xv, wv);
+        const uint32_t pos = j << 18;  // (PER * j) << 16
 #pragma unroll
         for (int q = 0; q < PER; ++q) {
-            if ((uint32_t)q < cnt && d2[q] < best_d2) { best_d2 = d2[q]; best_at = ((j + q) << 16) | g[q]; }
+            if (d2[q] < best_d2) { best_d2 = d2[q]; best_at = pos + ((uint32_t)q << 16) + at[q]; }
         }
-        const uint32_t adv = umax(cnt, 1u);  // cnt is never 0 while e < end (the cursors advance together); never spin on it
-        e += adv;
-        j += adv;
-        if (j == tk.n) {
+        ++s;
+        ++j;
+        if (j == tk.nsteps) {
             if (best_d2 < FLT_MAX) {
                 const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
                 if (whole) winner[t] = key;
@@ -315,7 +285,7 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t E, const ScanTask *tasks, co
             whole = true;
             best_d2 = FLT_MAX;
             best_at = 0xFFFFFFFFu;
-            if (e < end) {
+            if (s < end) {
                 tk = tasks[t];
                 load_staged<GD>(xs + tk.xoff, xv);
                 load_staged<GD>(ws + tk.xoff, wv);
@@ -444,7 +414,6 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
     {
         // Every lane rounds its groups for one candidate, the warp runs all the scans that came up with the
         // work spread evenly over the lanes, then every lane adds up its candidate and accepts or rejects it.
-        const uint16_t *lists = tab.neighbours;
         // the magnitudes are read back from the lane's staged row from here on, which frees their registers
         const float *const xrow = xs + lane * XP;
         // rounds the groups selected by `want` at inverse scale id and looks the lattice points up: a codebook entry
@@ -462,7 +431,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                         const int l = imax(0, imin(T::KMAXQ - 1, nearest_int(0.5f * (id * xk[i] - 1))));
                         u |= (uint32_t)l << (T::BITS * i);
                     }
-                    g[k] = __ldg(tab.map_n + u);
+                    g[k] = __ldg(tab.map_s + u);
                 }
             }
         };
@@ -476,17 +445,17 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 nk[k] = 0;
                 if (g[k] < 0) {
                     const uint32_t v = (uint32_t)(-g[k] - 1);
-                    if ((v & 511u) == 0) {
+                    if ((v & 255u) == 0) {
                         g[k] = 0;  // an empty list (no codebook has one) is not queued
                     } else {
                         off |= 1u << k;
-                        nk[k] = v & 511u;
-                        g[k] = (int)(v >> 9);  // the list's offset until the winner replaces it
+                        nk[k] = v & 255u;
+                        g[k] = (int)(v >> 8);  // the list's first step until the winner replaces it
                         total_n += nk[k];
                     }
                 }
             }
-            // slots and positions: one inclusive scan over (entries << 10 | scans)
+            // slots and positions: one inclusive scan over (steps << 10 | scans)
             const uint32_t mine = (total_n << 10) | (uint32_t)__popc(off);
             uint32_t incl = mine;
 #pragma unroll
@@ -502,10 +471,10 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
             for (int k = 0; k < NG; ++k) {
                 if ((off >> k) & 1) {
                     ScanTask tk;
-                    tk.list = (uint32_t)g[k];
-                    tk.xoff = (uint32_t)(lane * XP + GD * k);
+                    tk.base = (uint32_t)g[k];
+                    tk.nsteps = nk[k];
                     tk.scale = at_scale;
-                    tk.n = nk[k];
+                    tk.xoff = (uint32_t)(lane * XP + GD * k);
                     tasks[slot] = tk;
                     first[slot] = pos;
                     winner[slot] = kNoWinner;
@@ -514,14 +483,13 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 }
             }
             __syncwarp();
-            if (all >> 10) balanced_scan<GD, TMAX, T::PER>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, lists,
-                                                            (uint32_t)tab.grid_size - 1u);
+            if (all >> 10) balanced_scan<GD, TMAX>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, tab.steps);
             __syncwarp();
             slot = slot0;
 #pragma unroll
             for (int k = 0; k < NG; ++k) {
                 if ((off >> k) & 1) {
-                    const uint32_t w = (uint32_t)winner[slot++] & 0xFFFFu;
+                    const uint32_t w = ((uint32_t)winner[slot++] & 0xFFFFu) / (GD * 2);  // row offset -> codebook index
                     g[k] = w < (uint32_t)tab.grid_size ? (int)w : 0;
                 }
             }
@@ -707,7 +675,7 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
                    cudaStream_t stream) {
     using T = Traits<TYPE>;
     const IqSearchTable &tab = state->iq[T::TABLE];
-    if (!tab.grid) return cudaErrorInvalidValue;
+    if (!tab.grid || !tab.steps || !tab.map_s) return cudaErrorInvalidValue;
     const int64_t nblocks = nelems / T::BS;
     if (nblocks <= 0) return cudaSuccess;
     constexpr int kThreads = T::THREADS, NG = T::BS / T::GD, XP = T::BS + 4, TMAX = 32 * NG;
