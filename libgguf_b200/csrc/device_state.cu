@@ -104,22 +104,25 @@ const DeviceState *device_state_for(int type, int dev) {
         t.grid = upload(slot, h.grid);
         t.map = upload(slot, h.map);
         t.neighbours = upload(slot, h.neighbours);
-        if (id != IQT_1S) {   // one load then tells a scan where its list is and how many steps it has
+        if (id != IQT_1S) {   // one load then tells a scan where its list is and how many records it has
+            // the codebooks with long lists  (IQ2_XS, mean 58 entries) uses two-step records: half as many list loads
+            const uint32_t rec_steps = id == IQT_2XS ? 2 : 1, rec_entries = rec_steps * kIqStepEntries;
             std::vector<int32_t> packed(h.map.size());
-            std::vector<uint16_t> steps;
+            std::vector<uint16_t> entries;
             for (size_t i = 0; i < h.map.size(); ++i) {
                 const int32_t m = h.map[i];
                 if (m >= 0) { packed[i] = m; continue; }
                 const uint32_t off = (uint32_t)(-m - 1), n = h.neighbours[off];
-                const uint32_t first_step = (uint32_t)(steps.size() / kIqStepEntries), nsteps = (n + kIqStepEntries - 1) / kIqStepEntries;
-                if (first_step >= (1u << 22) || nsteps >= (1u << 8) || (size_t)h.grid_size * h.dims * 2 > 65536) return nullptr;
-                for (uint32_t e = 0; e < nsteps * kIqStepEntries; ++e)
-                    steps.push_back((uint16_t)(h.neighbours[off + 1 + (e < n ? e : 0)] * h.dims * 2));
-                packed[i] = -(int32_t)(((first_step << 8) | nsteps) + 1);
+                const uint32_t first_rec = (uint32_t)(entries.size() / rec_entries), nrec = (n + rec_entries - 1) / rec_entries;
+                if (first_rec >= (1u << 22) || nrec >= (1u << 8) || (size_t)h.grid_size * h.dims * 2 > 65536) return nullptr;
+                for (uint32_t e = 0; e < nrec * rec_entries; ++e)
+                    entries.push_back((uint16_t)(h.neighbours[off + 1 + (e < n ? e : 0)] * h.dims * 2));
+                packed[i] = -(int32_t)(((first_rec << 8) | nrec) + 1);
             }
             t.map_s = upload(slot, packed);
-            t.steps = reinterpret_cast<const uint2 *>(upload(slot, steps));
-            if (!t.map_s || !t.steps) return nullptr;
+            t.records = upload(slot, entries);
+            t.record_steps = (int)rec_steps;
+            if (!t.map_s || !t.records) return nullptr;
         }
         if (!t.grid || !t.map || !t.neighbours) return nullptr;
         t.grid_size = h.grid_size;

@@ -17,13 +17,14 @@ struct IqSearchTable {
     const uint8_t *grid = nullptr;         // grid_size x dims bytes, coordinate value 2*code+1
     const int32_t *map = nullptr;          // lattice index -> grid index (>= 0) or -(offset+1) into neighbours
     const uint16_t *neighbours = nullptr;  // [count, idx0, idx1, ...] runs
-    // The neighbour lists again, laid out for the IQ2 / IQ3 scans: every list padded to whole steps of kIqStepEntries
-    // entries with copies of its first entry (a copy's distance equals the first entry's, so it is never a strict
-    // improvement), steps 8-byte aligned, an entry stored as the byte offset of its codebook row in the kernel's
-    // staged codebook (grid index x dims x 2).  map_s is map with a list's first step and step count folded in:
-    // -(((first_step << 8) | steps) + 1).  Both absent for the IQ1 codebook.
-    const uint2 *steps = nullptr;
+    // The neighbour lists again, laid out for the IQ2 / IQ3 scans: every list padded to whole records of record_steps
+    // steps of kIqStepEntries entries with copies of its first entry (a copy's distance equals the first entry's, so
+    // it is never a strict improvement), records aligned to their size (8 or 16 bytes), an entry stored as the byte
+    // offset of its codebook row in the kernel's staged codebook (grid index x dims x 2).  map_s is map with a list's
+    // first record and record count folded in: -(((first_record << 8) | records) + 1).  Absent for the IQ1 codebook.
+    const void *records = nullptr;
     const int32_t *map_s = nullptr;
+    int record_steps = 0;
     int grid_size = 0;
     int dims = 0;
     int map_size = 0;

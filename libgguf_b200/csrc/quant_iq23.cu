@@ -33,27 +33,27 @@ constexpr unsigned kFull = 0xffffffffu;
 
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
-    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4;
+    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4, REC = 1;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = true;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_XS> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5, REC = 2;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_S> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5, REC = 1;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_XXS> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6, REC = 1;
     static constexpr bool PARITY = true, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_S> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6, REC = 1;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 0.f;  // upstream tests `!max`
 };
@@ -174,17 +174,33 @@ template <int GD>
 GGUF_D void grid_entry(const uint32_t *gridh, int g, float (&q)[GD]) { grid_row<GD>(gridh, (uint32_t)g * (GD * 2), q); }
 
 // Weighted squared distance of the codebook row at byte offset `at` from the group, terms added in coordinate order.
+// nx holds the negated magnitudes (a - b is a + (-b) exactly).  Coordinates 2i and 2i+1 share two-wide instructions
+// for the difference and its two multiplications; the products scale * q stay scalar multiplies (a packed multiply
+// feeding a packed add would be contracted into a fused multiply-add) and the sum stays a chain of scalar adds.
 template <int GD>
-GGUF_D float neighbour_d2(const uint32_t *gridh, uint32_t at, float scale, const float (&xv)[GD], const float (&wv)[GD]) {
+GGUF_D float neighbour_d2(const uint32_t *gridh, uint32_t at, float scale, const float2 (&nx)[GD / 2], const float2 (&wv)[GD / 2]) {
     float q[GD];
     grid_row<GD>(gridh, at, q);
     float d2 = 0;
 #pragma unroll
-    for (int i = 0; i < GD; ++i) {
-        const float diff = scale * q[i] - xv[i];
-        d2 += wv[i] * diff * diff;
+    for (int i = 0; i < GD / 2; ++i) {
+        const float2 diff = __fadd2_rn(make_float2(__fmul_rn(scale, q[2 * i]), __fmul_rn(scale, q[2 * i + 1])), nx[i]);
+        const float2 term = __fmul2_rn(__fmul2_rn(wv[i], diff), diff);
+        d2 = __fadd_rn(d2, term.x);
+        d2 = __fadd_rn(d2, term.y);
     }
     return d2;
+}
+
+// a group's negated magnitudes / its root weights from the staged rows, as pairs
+template <int GD>
+GGUF_D void load_pairs(const float *p, float2 (&v)[GD / 2], bool negate) {
+#pragma unroll
+    for (int k = 0; k < GD / 4; ++k) {
+        const float4 t = reinterpret_cast<const float4 *>(p)[k];
+        v[2 * k] = negate ? make_float2(-t.x, -t.y) : make_float2(t.x, t.y);
+        v[2 * k + 1] = negate ? make_float2(-t.z, -t.w) : make_float2(t.z, t.w);
+    }
 }
 
 template <int N>
@@ -198,27 +214,34 @@ GGUF_D void load_staged(const float *p, float (&x)[N]) {  // shared memory, 16-b
 
 // One neighbour scan a warp has to run: which list, which group of which lane's block, at which scale.
 struct ScanTask {
-    uint32_t base;    // the list's first step in the step array
-    uint32_t nsteps;  // its length in steps
+    uint32_t base;   // the list's first record in the record array
+    uint32_t nrec;   // its length in records
     float scale;
-    uint32_t xoff;    // float offset of the group in the warp's staged magnitudes / weights
+    uint32_t xoff;   // float offset of the group in the warp's staged magnitudes / weights
 };
 
 constexpr unsigned long long kNoWinner = ~0ull;
 constexpr int PER = kIqStepEntries;
+template <int REC> struct RecordOf;
+template <> struct RecordOf<1> { using type = uint2; };
+template <> struct RecordOf<2> { using type = uint4; };
 
-// The warp's pending scans, evaluated with the work spread evenly.  A list is a whole number of steps of PER
-// entries (its tail repeats its first entry, which can never be a strict improvement), so the T lists laid end to end
-// are S steps (`first[t]` = position of list t's first step) and every lane takes a contiguous stretch of S/32 steps,
-// whatever lists it crosses: every lane runs the same number of iterations, each one aligned 8-byte load and PER
-// independent ordered sums with no bookkeeping per entry.  A list's winner is the first strict minimum in list order,
-// i.e. the minimum of (distance bits, position) as one 64-bit key; a lane that saw a whole list stores its key, lanes
-// that share a list combine theirs with a shared-memory atomic minimum.  Distances are sums of non-negative terms,
-// so their bit patterns order like the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
-template <int GD, int TMAX>
+// The warp's pending scans, evaluated with the work spread evenly.  A list is a whole number of records of REC steps
+// of PER entries (its tail repeats its first entry, which can never be a strict improvement), so the T lists laid end
+// to end are S records (`first[t]` = position of list t's first record) and every lane takes a contiguous stretch
+// of S/32 records, whatever lists it crosses: every lane runs the same number of iterations, each one aligned 8- or
+// 16-byte load and, per step, PER independent ordered sums with no bookkeeping per entry.  (32 lanes loading from 32
+// different lines cost the L1 / shared-memory pipe as much as the steps' codebook gathers, which is why the long lists
+// use two-step records.)  A list's winner is the first strict minimum in list order, i.e. the minimum of (distance
+// bits, position) as one 64-bit key; a lane that saw a whole list stores its key, lanes that share a list combine
+// theirs with a shared-memory atomic minimum.  Distances are sums of non-negative terms, so their bit patterns order
+// like the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
+template <int GD, int TMAX, int REC>
 GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
-                          const float *xs, const float *ws, const uint32_t *gridh, const uint2 *__restrict__ steps) {
-    constexpr int AHEAD = 3;  // steps are fetched this many iterations early, across list boundaries
+                          const float *xs, const float *ws, const uint32_t *gridh, const void *__restrict__ records) {
+    using Record = typename RecordOf<REC>::type;
+    constexpr int AHEAD = REC == 1 ? 3 : 2;  // records are fetched this many iterations early, across list boundaries
+    const Record *const recs = static_cast<const Record *>(records);
     const uint32_t share = (S + 31) >> 5;
     uint32_t s = umin((uint32_t)lane * share, S);
     const uint32_t end = umin(s + share, S);
@@ -230,19 +253,19 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
         if (c < T && first[c] <= s) t = c;
     }
     ScanTask tk = tasks[t];
-    float xv[GD], wv[GD];
-    load_staged<GD>(xs + tk.xoff, xv);
-    load_staged<GD>(ws + tk.xoff, wv);
+    float2 xv[GD / 2], wv[GD / 2];
+    load_pairs<GD>(xs + tk.xoff, xv, true);
+    load_pairs<GD>(ws + tk.xoff, wv, false);
     uint32_t j = s - first[t];
     bool whole = j == 0;
     float best_d2 = FLT_MAX;
     uint32_t best_at = 0xFFFFFFFFu;
-    // the fetch cursor runs AHEAD steps in front of the evaluation cursor
+    // the fetch cursor runs AHEAD records in front of the evaluation cursor
     int ft = t;
-    uint32_t fleft = tk.nsteps - j, fs = s;
-    const uint2 *fp = steps + tk.base + j;
-    uint2 ring[AHEAD];
-    auto fetch = [&](uint2 &rec) {
+    uint32_t fleft = tk.nrec - j, fs = s;
+    const Record *fp = recs + tk.base + j;
+    Record ring[AHEAD];
+    auto fetch = [&](Record &rec) {
         if (fs < end) {
             rec = __ldg(fp);
             ++fp;
@@ -250,31 +273,37 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
             if (--fleft == 0 && fs < end) {
                 ++ft;
                 const uint2 h = *reinterpret_cast<const uint2 *>(tasks + ft);
-                fp = steps + h.x;
+                fp = recs + h.x;
                 fleft = h.y;
             }
         }
     };
 #pragma unroll
-    for (int d = 0; d < AHEAD; ++d) { ring[d] = make_uint2(0u, 0u); fetch(ring[d]); }
+    for (int d = 0; d < AHEAD; ++d) { ring[d] = Record(); fetch(ring[d]); }
     while (s < end) {
-        const uint2 rec = ring[0];
+        const Record rec = ring[0];
 #pragma unroll
         for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
         fetch(ring[AHEAD - 1]);
-        static_assert(PER == 4, "a step is one 8-byte record of four 16-bit row offsets");
-        const uint32_t at[PER] = {rec.x & 0xFFFFu, rec.x >> 16, rec.y & 0xFFFFu, rec.y >> 16};
-        float d2[PER];
+        static_assert(PER == 4, "a step is two words of two 16-bit row offsets");
+        uint32_t words[2 * REC];
+        if constexpr (REC == 1) { words[0] = rec.x; words[1] = rec.y; }
+        else { words[0] = rec.x; words[1] = rec.y; words[2] = rec.z; words[3] = rec.w; }
 #pragma unroll
-        for (int q = 0; q < PER; ++q) d2[q] = neighbour_d2<GD>(gridh, at[q], tk.scale, xv, wv);
-        const uint32_t pos = j << 18;  // (PER * j) << 16
+        for (int h = 0; h < REC; ++h) {
+            const uint32_t at[PER] = {words[2 * h] & 0xFFFFu, words[2 * h] >> 16, words[2 * h + 1] & 0xFFFFu, words[2 * h + 1] >> 16};
+            float d2[PER];
 #pragma unroll
-        for (int q = 0; q < PER; ++q) {
-            if (d2[q] < best_d2) { best_d2 = d2[q]; best_at = pos + ((uint32_t)q << 16) + at[q]; }
+            for (int q = 0; q < PER; ++q) d2[q] = neighbour_d2<GD>(gridh, at[q], tk.scale, xv, wv);
+            const uint32_t pos = (j * REC + h) << 18;  // (entry position of the step) << 16
+#pragma unroll
+            for (int q = 0; q < PER; ++q) {
+                if (d2[q] < best_d2) { best_d2 = d2[q]; best_at = pos + ((uint32_t)q << 16) + at[q]; }
+            }
         }
         ++s;
         ++j;
-        if (j == tk.nsteps) {
+        if (j == tk.nrec) {
             if (best_d2 < FLT_MAX) {
                 const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
                 if (whole) winner[t] = key;
@@ -287,8 +316,8 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
             best_at = 0xFFFFFFFFu;
             if (s < end) {
                 tk = tasks[t];
-                load_staged<GD>(xs + tk.xoff, xv);
-                load_staged<GD>(ws + tk.xoff, wv);
+                load_pairs<GD>(xs + tk.xoff, xv, true);
+                load_pairs<GD>(ws + tk.xoff, wv, false);
             }
         }
     }
@@ -450,12 +479,12 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                     } else {
                         off |= 1u << k;
                         nk[k] = v & 255u;
-                        g[k] = (int)(v >> 8);  // the list's first step until the winner replaces it
+                        g[k] = (int)(v >> 8);  // the list's first record until the winner replaces it
                         total_n += nk[k];
                     }
                 }
             }
-            // slots and positions: one inclusive scan over (steps << 10 | scans)
+            // slots and positions: one inclusive scan over (records << 10 | scans)
             const uint32_t mine = (total_n << 10) | (uint32_t)__popc(off);
             uint32_t incl = mine;
 #pragma unroll
@@ -472,7 +501,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 if ((off >> k) & 1) {
                     ScanTask tk;
                     tk.base = (uint32_t)g[k];
-                    tk.nsteps = nk[k];
+                    tk.nrec = nk[k];
                     tk.scale = at_scale;
                     tk.xoff = (uint32_t)(lane * XP + GD * k);
                     tasks[slot] = tk;
@@ -483,7 +512,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 }
             }
             __syncwarp();
-            if (all >> 10) balanced_scan<GD, TMAX>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, tab.steps);
+            if (all >> 10) balanced_scan<GD, TMAX, T::REC>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, tab.records);
             __syncwarp();
             slot = slot0;
 #pragma unroll
@@ -675,7 +704,7 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
                    cudaStream_t stream) {
     using T = Traits<TYPE>;
     const IqSearchTable &tab = state->iq[T::TABLE];
-    if (!tab.grid || !tab.steps || !tab.map_s) return cudaErrorInvalidValue;
+    if (!tab.grid || !tab.records || !tab.map_s || tab.record_steps != T::REC) return cudaErrorInvalidValue;
     const int64_t nblocks = nelems / T::BS;
     if (nblocks <= 0) return cudaSuccess;
     constexpr int kThreads = T::THREADS, NG = T::BS / T::GD, XP = T::BS + 4, TMAX = 32 * NG;
