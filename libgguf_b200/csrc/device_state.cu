@@ -122,6 +122,7 @@ const DeviceState *device_state_for(int type, int dev) {
             t.map_s = upload(slot, packed);
             t.records = upload(slot, entries);
             t.record_steps = (int)rec_steps;
+            t.records_bytes = (int)(entries.size() * sizeof(uint16_t));
             if (!t.map_s || !t.records) return nullptr;
         }
         if (!t.grid || !t.map || !t.neighbours) return nullptr;

@@ -25,6 +25,7 @@ struct IqSearchTable {
     const void *records = nullptr;
     const int32_t *map_s = nullptr;
     int record_steps = 0;
+    int records_bytes = 0;
     int grid_size = 0;
     int dims = 0;
     int map_size = 0;

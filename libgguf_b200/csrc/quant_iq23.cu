@@ -1,22 +1,23 @@
 // Lattice quantizers IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S.
 //
-// One lane owns one block of 32 (16 for IQ2_XS / IQ2_S) elements; the 8 or 16 lanes of a
-// super-block sit next to each other in a warp.  Per block the upstream algorithm is run
-// literally: sign extraction (with the even-parity fix where the format stores 7 sign bits), a
-// loop over candidate scales in which every group of 8 (or 4) magnitudes is rounded to the lattice
-// and, when the rounded point is not a codebook entry, replaced by the best of its precomputed
-// neighbours, the accept/reject chain on (sumqx, sumq2), the final re-projection, and the 4-bit
-// block scale against the super-block maximum.
+// One lane owns 32 (IQ2_XXS) or 16 elements: a whole block, or for the IQ3 types half of a 32-element block (the
+// two lanes of a block sit next to each other and hand the ordered sums from one to the other, which keeps the
+// kernel at 96 registers and 19-20 warps per SM); the lanes of a super-block sit next to each other in a warp.
+// Per block the upstream algorithm is run literally: sign extraction (with the even-parity fix where the format
+// stores 7 sign bits), a loop over candidate scales in which every group of 8 (or 4) magnitudes is rounded to the
+// lattice and, when the rounded point is not a codebook entry, replaced by the best of its precomputed neighbours,
+// the accept/reject chain on (sumqx, sumq2), the final re-projection (run as one more pass of the same loop), and
+// the 4-bit block scale against the super-block maximum.
 //
-// The neighbour scans are nine tenths of the arithmetic and their lengths differ from group to
-// group (1 to about 300 entries), so a lane that scanned its own lists left two thirds of the
-// warp idle.  Here the warp works in rounds: every lane rounds its groups for one candidate and
-// queues the scans that came up, the warp lays the queued lists end to end and every lane
-// evaluates an equal stretch of that sequence (whatever lists it crosses), and the owners read the
-// winners back and run the accept/reject chain.  The codebook is staged in shared memory as
-// bfloat16 pairs (exact for its small odd integers), every lane's magnitudes and root weights in
-// padded rows; the lattice map and the neighbour lists stay in global memory (L1/L2 resident) and
-// are fetched a few steps ahead of their use.
+// The neighbour scans are most of the arithmetic and their lengths differ from group to group (1 to about 300
+// entries), so a lane that scanned its own lists left two thirds of the warp idle.  Here the warp works in rounds:
+// every lane rounds its groups for one candidate and queues the scans that came up, the warp lays the queued lists
+// end to end and every lane evaluates an equal stretch of that sequence (whatever lists it crosses), and the owners
+// read the winners back and run the accept/reject chain.  The lists are kept in a layout of their own (whole,
+// aligned records of four or eight entries, an entry being the offset of its codebook row), the codebook is staged
+// in shared memory as bfloat16 pairs (exact for its small odd integers), every lane's magnitudes and root weights
+// in padded rows.  The IQ3 codebooks' records (47 and 58 KB) are staged in shared memory too, under one CTA per SM
+// that stays for the whole launch; the IQ2 records (0.5-1.3 MB) and the lattice map stay in global memory (L2).
 // upstream: csrc/quant/iq2_xxs.cpp:4-224, iq2_xs.cpp:4-230, iq2_s.cpp:4-218, iq3_xxs.cpp:4-273,
 // iq3_s.cpp:5-233, csrc/common/libgguf_iq_tables.cpp:434-462 and :683-711.
 #include <float.h>
@@ -33,27 +34,32 @@ constexpr unsigned kFull = 0xffffffffu;
 
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
-    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4, REC = 1;
+    static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4, REC = 1, LPB = 1;
+    static constexpr bool LISTS_SHARED = false, MERGED = true;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = true;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_XS> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5, REC = 2;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5, REC = 2, LPB = 1;
+    static constexpr bool LISTS_SHARED = false, MERGED = false;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_S> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5, REC = 1;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5, REC = 1, LPB = 1;
+    static constexpr bool LISTS_SHARED = false, MERGED = false;
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_XXS> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 64, CTAS = 6, REC = 1;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 640, CTAS = 1, REC = 1, LPB = 2;
+    static constexpr bool MERGED = true, LISTS_SHARED = true;  // 47 KB of records + 2 KB codebook + 20 warps x 8.5 KB
     static constexpr bool PARITY = true, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_S> {
-    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 64, CTAS = 6, REC = 1;
+    static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 608, CTAS = 1, REC = 1, LPB = 2;
+    static constexpr bool MERGED = true, LISTS_SHARED = true;  // 58 KB of records + 4 KB codebook + 19 warps x 8.5 KB
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 0.f;  // upstream tests `!max`
 };
@@ -236,11 +242,12 @@ template <> struct RecordOf<2> { using type = uint4; };
 // bits, position) as one 64-bit key; a lane that saw a whole list stores its key, lanes that share a list combine
 // theirs with a shared-memory atomic minimum.  Distances are sums of non-negative terms, so their bit patterns order
 // like the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
-template <int GD, int TMAX, int REC>
+template <int GD, int TMAX, int REC, bool SHARED>
 GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
                           const float *xs, const float *ws, const uint32_t *gridh, const void *__restrict__ records) {
     using Record = typename RecordOf<REC>::type;
-    constexpr int AHEAD = REC == 1 ? 3 : 2;  // records are fetched this many iterations early, across list boundaries
+    // records are fetched this many iterations early, across list boundaries (from shared memory: one)
+    constexpr int AHEAD = SHARED ? 1 : (REC == 1 ? 3 : 2);
     const Record *const recs = static_cast<const Record *>(records);
     const uint32_t share = (S + 31) >> 5;
     uint32_t s = umin((uint32_t)lane * share, S);
@@ -267,7 +274,7 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
     Record ring[AHEAD];
     auto fetch = [&](Record &rec) {
         if (fs < end) {
-            rec = __ldg(fp);
+            rec = SHARED ? *fp : __ldg(fp);
             ++fp;
             ++fs;
             if (--fleft == 0 && fs < end) {
@@ -327,34 +334,53 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
 
 template <int TYPE>
 __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) quant_iq23_kernel(const float *__restrict__ src, const float *__restrict__ qw,
-                                                             uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
+                                                             uint8_t *__restrict__ dst, int64_t nlanes, int64_t n_per_row,
                                                              IqSearchTable tab) {
     using T = Traits<TYPE>;
-    constexpr int BS = T::BS, GD = T::GD, NG = BS / GD, NS = BS / 8, W = 256 / BS;  // W lanes per super-block
-    // the codebook's coordinates as floats: no conversion in the neighbour scans, one or two 16-byte reads per entry
+    // A block of BS elements belongs to LPB neighbouring lanes, EL elements (NG groups) each; W lanes per super-block.
+    constexpr int BS = T::BS, LPB = T::LPB, EL = BS / LPB, GD = T::GD, NG = EL / GD, NS = EL / 8, W = 256 / EL;
+    static_assert(LPB == 1 || LPB == 2, "one or two lanes per block");
+    static_assert(!(T::QP_INIT && LPB != 1), "the initial scale search runs over a whole block in one lane");
     constexpr int kThreads = T::THREADS;
     extern __shared__ __align__(16) uint32_t gridh[];
     for (int i = threadIdx.x; i < tab.grid_size * GD / 2; i += kThreads) {
         const uint32_t lo = __float_as_uint((float)__ldg(tab.grid + 2 * i)), hi = __float_as_uint((float)__ldg(tab.grid + 2 * i + 1));
         gridh[i] = (lo >> 16) | (hi & 0xFFFF0000u);
     }
+    // The codebooks whose neighbour records fit (IQ3: 47 and 58 KB) keep them in shared memory next to the codebook,
+    // one copy per SM under a CTA that stays for the whole launch: a step's record is then a shared-memory read of
+    // a few wavefronts instead of a global load that touches 32 lines.
+    const void *records = tab.records;
+    int state_words = tab.grid_size * (GD / 2);
+    if constexpr (T::LISTS_SHARED) {
+        uint2 *const staged = reinterpret_cast<uint2 *>(gridh + state_words);
+        const uint2 *const from = static_cast<const uint2 *>(tab.records);
+        for (int i = threadIdx.x; i < tab.records_bytes / 8; i += kThreads) staged[i] = __ldg(from + i);
+        records = staged;
+        state_words += (tab.records_bytes / 4 + 3) & ~3;
+    }
     __syncthreads();
     // per warp: every lane's magnitudes and root weights in rows padded by four floats, the pending
     // scans of one candidate, where each list starts in the concatenation, and each scan's winner
-    constexpr int XP = BS + 4, TMAX = 32 * NG;
+    constexpr int XP = EL + 4, TMAX = 32 * NG;
     constexpr int kWarpFloats = 2 * 32 * XP + TMAX * 4 + TMAX + TMAX * 2;
-    float *const wbase = reinterpret_cast<float *>(gridh) + tab.grid_size * (GD / 2) + (threadIdx.x >> 5) * kWarpFloats;
+    float *const wbase = reinterpret_cast<float *>(gridh) + state_words + (threadIdx.x >> 5) * kWarpFloats;
     float *const xs = wbase, *const ws = wbase + 32 * XP;
     ScanTask *const tasks = reinterpret_cast<ScanTask *>(wbase + 2 * 32 * XP);
     unsigned long long *const winner = reinterpret_cast<unsigned long long *>(wbase + 2 * 32 * XP + TMAX * 4);
     uint32_t *const first = reinterpret_cast<uint32_t *>(wbase + 2 * 32 * XP + TMAX * 4 + TMAX * 2);
 
     const int lane = threadIdx.x & 31, j = lane & (W - 1), gbase = lane & ~(W - 1);
-    int64_t blk = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    const bool active = blk < nblocks;
-    if (!active) blk = nblocks - 1;
-    float xb[BS];
-    load_group<BS>(src + blk * BS, xb);
+    const int half = lane & (LPB - 1), pbase = lane & ~(LPB - 1), jb = j / LPB;  // lane within its block, block within its super-block
+    // a warp takes 32 lanes' worth of elements at a time; the launch gives every warp one such chunk, or, under the
+    // CTAs that stay, as many as it takes
+    const int64_t nchunks = (nlanes + 31) >> 5;
+    for (int64_t chunk = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); chunk < nchunks; chunk += (int64_t)gridDim.x * (kThreads / 32)) {
+    int64_t ln = chunk * 32 + lane;
+    const bool active = ln < nlanes;
+    if (!active) ln = nlanes - W + j;  // lanes past the end redo the last super-block (whole super-blocks per row) and write nothing
+    float xb[EL];
+    load_group<EL>(src + ln * EL, xb);
 
     // sum of squares over the super-block, in element order (lane to lane)
     float sumx2 = 0.f;
@@ -362,23 +388,23 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
     for (int s = 0; s < W; ++s) {
         if (j == s) {
 #pragma unroll
-            for (int i = 0; i < BS; ++i) sumx2 += xb[i] * xb[i];
+            for (int i = 0; i < EL; ++i) sumx2 += xb[i] * xb[i];
         }
         sumx2 = __shfl_sync(kFull, sumx2, gbase + s);
     }
     const float sigma2 = T::SIGMA_X2 ? 2 * sumx2 / QK_K : sumx2 / QK_K;
 
-    float weight[BS], waux[BS], xval[BS];
+    float weight[EL], waux[EL], xval[EL];
     if (qw) {
-        const float *qwp = qw + (blk * BS) % n_per_row;
+        const float *qwp = qw + (ln * EL) % n_per_row;
 #pragma unroll
-        for (int i = 0; i < BS; ++i) weight[i] = __ldg(qwp + i) * sqrtf(sigma2 + xb[i] * xb[i]);
+        for (int i = 0; i < EL; ++i) weight[i] = __ldg(qwp + i) * sqrtf(sigma2 + xb[i] * xb[i]);
     } else {
 #pragma unroll
-        for (int i = 0; i < BS; ++i) weight[i] = TYPE == GGML_TYPE_IQ2_S ? 0.25f * sigma2 + xb[i] * xb[i] : xb[i] * xb[i];
+        for (int i = 0; i < EL; ++i) weight[i] = TYPE == GGML_TYPE_IQ2_S ? 0.25f * sigma2 + xb[i] * xb[i] : xb[i] * xb[i];
     }
 #pragma unroll
-    for (int i = 0; i < BS; ++i) waux[i] = sqrtf(weight[i]);
+    for (int i = 0; i < EL; ++i) waux[i] = sqrtf(weight[i]);
 
     uint32_t signs[NS];
 #pragma unroll
@@ -406,34 +432,44 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
         }
         signs[k] = s;
     }
-    float max = xval[0];
+    // the block's maximum, folded in element order (the first lane of a block starts the fold, the next continues it)
+    float max = 0.f;
 #pragma unroll
-    for (int i = 1; i < BS; ++i) max = max > xval[i] ? max : xval[i];
+    for (int h = 0; h < LPB; ++h) {
+        if (half == h) {
+            if (h == 0) max = xval[0];
+#pragma unroll
+            for (int i = (h == 0 ? 1 : 0); i < EL; ++i) max = max > xval[i] ? max : xval[i];
+        }
+        if (LPB > 1) max = __shfl_sync(kFull, max, pbase + h);
+    }
     {
 #pragma unroll
-        for (int v = 0; v < BS / 4; ++v) {
-            *reinterpret_cast<float4 *>(xs + (threadIdx.x & 31) * XP + 4 * v) = make_float4(xval[4 * v], xval[4 * v + 1], xval[4 * v + 2], xval[4 * v + 3]);
-            *reinterpret_cast<float4 *>(ws + (threadIdx.x & 31) * XP + 4 * v) = make_float4(waux[4 * v], waux[4 * v + 1], waux[4 * v + 2], waux[4 * v + 3]);
+        for (int v = 0; v < EL / 4; ++v) {
+            *reinterpret_cast<float4 *>(xs + lane * XP + 4 * v) = make_float4(xval[4 * v], xval[4 * v + 1], xval[4 * v + 2], xval[4 * v + 3]);
+            *reinterpret_cast<float4 *>(ws + lane * XP + 4 * v) = make_float4(waux[4 * v], waux[4 * v + 1], waux[4 * v + 2], waux[4 * v + 3]);
         }
         __syncwarp();
     }
 
-    uint32_t L[BS / 4];
+    uint32_t L[EL / 4];
 #pragma unroll
-    for (int i = 0; i < BS / 4; ++i) L[i] = 0;
+    for (int i = 0; i < EL / 4; ++i) L[i] = 0;
     float scale = 0.f;
     bool skipped = T::EPS > 0.f ? (max < T::EPS) : !(max != 0.f);
     float eff_max = max;
-    if (!skipped && T::QP_INIT) {
-        int Linit[BS];
-        scale = qp_quants_reg<BS>(T::KMAXQ + 1, xval, Linit, weight);
-        eff_max = scale * T::KMAXQ;
-        if (eff_max <= 0) {
-            skipped = true;
-            scale = 0.f;
-        } else {
+    if constexpr (T::QP_INIT) {
+        if (!skipped) {
+            int Linit[EL];
+            scale = qp_quants_reg<EL>(T::KMAXQ + 1, xval, Linit, weight);
+            eff_max = scale * T::KMAXQ;
+            if (eff_max <= 0) {
+                skipped = true;
+                scale = 0.f;
+            } else {
 #pragma unroll
-            for (int i = 0; i < BS; ++i) lset(L, i, Linit[i]);
+                for (int i = 0; i < EL; ++i) lset(L, i, Linit[i]);
+            }
         }
     }
     int gidx[NG];
@@ -442,7 +478,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
 
     {
         // Every lane rounds its groups for one candidate, the warp runs all the scans that came up with the
-        // work spread evenly over the lanes, then every lane adds up its candidate and accepts or rejects it.
+        // work spread evenly over the lanes, then every block adds up its candidate and accepts or rejects it.
         // the magnitudes are read back from the lane's staged row from here on, which frees their registers
         const float *const xrow = xs + lane * XP;
         // rounds the groups selected by `want` at inverse scale id and looks the lattice points up: a codebook entry
@@ -512,7 +548,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 }
             }
             __syncwarp();
-            if (all >> 10) balanced_scan<GD, TMAX, T::REC>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, tab.records);
+            if (all >> 10) balanced_scan<GD, TMAX, T::REC, T::LISTS_SHARED>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, records);
             __syncwarp();
             slot = slot0;
 #pragma unroll
@@ -525,63 +561,26 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
             return off;
         };
         constexpr uint32_t kAllGroups = NG == 32 ? 0xFFFFFFFFu : ((1u << NG) - 1);
+        constexpr int NC = 2 * T::IS_MAX + 1;  // candidate scales; one more pass re-projects at the accepted scale
+        auto inverse_scale = [&](int is) { return ((float)(2 * T::KMAXQ - 1) + (float)is * T::STEP) / eff_max; };
         float best = 0;
         if (!T::QP_INIT && !skipped) scale = max / (2 * T::KMAXQ - 1);
         uint32_t on_grid = TYPE == GGML_TYPE_IQ3_S ? 0u : 0xFFFFFFFFu;
+        bool reproject = false;
+        uint32_t want = 0;
         // the look-ups of candidate is + 1 are issued before the scans of candidate is run
         int g_ahead[NG];
-        lookup(skipped ? 0u : kAllGroups, ((float)(2 * T::KMAXQ - 1) + (float)(-T::IS_MAX) * T::STEP) / eff_max, g_ahead);
-        for (int is = -T::IS_MAX; is <= T::IS_MAX; ++is) {
-            const float id = ((float)(2 * T::KMAXQ - 1) + (float)is * T::STEP) / eff_max;
-            const float this_scale = 1 / id;
+        lookup(skipped ? 0u : kAllGroups, inverse_scale(-T::IS_MAX), g_ahead);
+        // pass NC is the re-projection at the accepted scale: all groups (IQ2_XXS, IQ3_S) or those the accepted
+        // candidate scanned
+        auto one_pass = [&](const int it, const bool last) {
+            const float this_scale = last ? scale : 1 / inverse_scale(it - T::IS_MAX);
             int g[NG];
 #pragma unroll
             for (int k = 0; k < NG; ++k) g[k] = g_ahead[k];
-            if (is < T::IS_MAX) lookup(skipped ? 0u : kAllGroups, ((float)(2 * T::KMAXQ - 1) + (float)(is + 1) * T::STEP) / eff_max, g_ahead);
+            if (it + 1 < NC) lookup(skipped ? 0u : kAllGroups, inverse_scale(it + 1 - T::IS_MAX), g_ahead);
             const uint32_t off = project(this_scale, g);
-            if (!skipped) {
-                float sumqx = 0, sumq2 = 0;
-#pragma unroll
-                for (int k = 0; k < NG; ++k) {
-                    float q[GD], xk[GD];
-                    grid_entry<GD>(gridh, g[k], q);
-                    load_staged<GD>(xrow + GD * k, xk);
-#pragma unroll
-                    for (int i = 0; i < GD; ++i) {
-                        const float w = weight[GD * k + i];
-                        sumqx += w * xk[i] * q[i];
-                        sumq2 += w * q[i] * q[i];
-                    }
-                }
-                if (sumq2 > 0 && sumqx * sumqx > best * sumq2) {
-                    scale = sumqx / sumq2;
-                    best = scale * sumqx;
-#pragma unroll
-                    for (int k = 0; k < NG; ++k) {
-                        float q[GD];
-                        grid_entry<GD>(gridh, g[k], q);
-#pragma unroll
-                        for (int v = 0; v < GD / 4; ++v)
-                            L[(GD * k) / 4 + v] = (uint32_t)(((int)q[4 * v] - 1) >> 1) | ((uint32_t)(((int)q[4 * v + 1] - 1) >> 1) << 8) |
-                                                  ((uint32_t)(((int)q[4 * v + 2] - 1) >> 1) << 16) | ((uint32_t)(((int)q[4 * v + 3] - 1) >> 1) << 24);
-                    }
-                    on_grid = ~off;
-                }
-            }
-        }
-        // re-projection at the accepted scale: all groups (IQ2_XXS, IQ3_S) or those the accepted candidate scanned
-        bool reproject = false;
-        if (!skipped) {
-            if (TYPE == GGML_TYPE_IQ2_XXS) reproject = scale > 0;
-            else reproject = (on_grid & kAllGroups) != kAllGroups && scale > 0;
-        }
-        {
-            constexpr bool all_groups = TYPE == GGML_TYPE_IQ2_XXS || TYPE == GGML_TYPE_IQ3_S;
-            const uint32_t want = reproject ? (all_groups ? kAllGroups : (~on_grid & kAllGroups)) : 0u;
-            int g[NG];
-            lookup(want, reproject ? 1 / scale : 0.f, g);
-            project(scale, g);
-            if (reproject) {
+            if (last && reproject) {
 #pragma unroll
                 for (int k = 0; k < NG; ++k) {
                     if ((want >> k) & 1) {
@@ -591,16 +590,75 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                         for (int i = 0; i < GD; ++i) lset(L, GD * k + i, ((int)q[i] - 1) >> 1);
                     }
                 }
-                float sumqx = 0, sumq2 = 0;
-#pragma unroll
-                for (int i = 0; i < BS; ++i) {
-                    const float w = weight[i];
-                    const float q = (float)(2 * lget(L, i) + 1);
-                    sumqx += w * xrow[i] * q;
-                    sumq2 += w * q * q;
-                }
-                if (sumq2 > 0) scale = sumqx / sumq2;
             }
+            // The block's two sums in element order.  The products do not depend on the sums, so every lane forms
+            // its own first; with two lanes per block the first lane then adds its terms, hands the sums on, and the
+            // second continues (the shuffles are executed by every lane).
+            float tx[EL], t2[EL];
+            float sumqx = 0, sumq2 = 0;
+#pragma unroll
+            for (int k = 0; k < NG; ++k) {
+                float q[GD], xk[GD];
+                if (last) {
+#pragma unroll
+                    for (int i = 0; i < GD; ++i) q[i] = (float)(2 * lget(L, GD * k + i) + 1);
+                } else {
+                    grid_entry<GD>(gridh, g[k], q);
+                }
+                load_staged<GD>(xrow + GD * k, xk);
+#pragma unroll
+                for (int i = 0; i < GD; ++i) {
+                    const float w = weight[GD * k + i];
+                    tx[GD * k + i] = w * xk[i] * q[i];
+                    t2[GD * k + i] = w * q[i] * q[i];
+                    if (LPB == 1) { sumqx += tx[GD * k + i]; sumq2 += t2[GD * k + i]; }
+                }
+            }
+            if (LPB > 1) {
+#pragma unroll
+                for (int h = 0; h < LPB; ++h) {
+                    if (half == h) {
+#pragma unroll
+                        for (int i = 0; i < EL; ++i) { sumqx += tx[i]; sumq2 += t2[i]; }
+                    }
+                    sumqx = __shfl_sync(kFull, sumqx, pbase + h);
+                    sumq2 = __shfl_sync(kFull, sumq2, pbase + h);
+                }
+            }
+            if (last) {
+                if (reproject && sumq2 > 0) scale = sumqx / sumq2;
+                return;
+            }
+            if (!skipped && sumq2 > 0 && sumqx * sumqx > best * sumq2) {
+                scale = sumqx / sumq2;
+                best = scale * sumqx;
+#pragma unroll
+                for (int k = 0; k < NG; ++k) {
+                    float q[GD];
+                    grid_entry<GD>(gridh, g[k], q);
+#pragma unroll
+                    for (int v = 0; v < GD / 4; ++v)
+                        L[(GD * k) / 4 + v] = (uint32_t)(((int)q[4 * v] - 1) >> 1) | ((uint32_t)(((int)q[4 * v + 1] - 1) >> 1) << 8) |
+                                              ((uint32_t)(((int)q[4 * v + 2] - 1) >> 1) << 16) | ((uint32_t)(((int)q[4 * v + 3] - 1) >> 1) << 24);
+                }
+                on_grid = ~off;
+            }
+            if (it == NC - 1) {
+                bool any_off = !skipped && (on_grid & kAllGroups) != kAllGroups;
+                if (LPB > 1) any_off = ((__ballot_sync(kFull, any_off) >> pbase) & ((1u << LPB) - 1)) != 0;  // either lane of the block
+                if (!skipped) reproject = TYPE == GGML_TYPE_IQ2_XXS ? scale > 0 : (any_off && scale > 0);
+                constexpr bool all_groups = TYPE == GGML_TYPE_IQ2_XXS || TYPE == GGML_TYPE_IQ3_S;
+                want = reproject ? (all_groups ? kAllGroups : (~on_grid & kAllGroups)) : 0u;
+                lookup(want, reproject ? 1 / scale : 0.f, g_ahead);
+            }
+        };
+        if constexpr (T::MERGED) {  // the re-projection runs through the candidates' copy of the scan code
+#pragma unroll 1
+            for (int it = 0; it <= NC; ++it) one_pass(it, it == NC);
+        } else {                    // it gets a copy of its own
+#pragma unroll 1
+            for (int it = 0; it < NC; ++it) one_pass(it, false);
+            one_pass(NC, true);
         }
         if (!skipped) {
             if (scale < 0) {
@@ -631,20 +689,26 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
     const float idd = 1 / d;
     int lsc = 0;
     if (!empty) lsc = imax(0, imin(15, nearest_int(0.5f * (idd * (skipped ? 0.f : scale) - 1))));
-    const int lsc_next = __shfl_down_sync(kFull, lsc, 1);
+    const int lsc_next = __shfl_down_sync(kFull, lsc, LPB);  // the next block's
     // position of this block's payload for the format whose writer does not advance over skipped blocks
     const unsigned group_mask = (W == 32) ? kFull : (((1u << W) - 1) << gbase);
-    const unsigned live = __ballot_sync(kFull, !skipped) & group_mask;
+    const unsigned live = __ballot_sync(kFull, !skipped && half == 0) & group_mask;  // one bit per block
     const int nlive = __popc(live);
-    const int rank_live = __popc(live & ((1u << lane) - 1));
-    const int rank_dead = (lane - gbase) - rank_live;
-    // IQ2_S: two bits per group of eight go to qh[ib/2]; gather the neighbour lane's bits
+    const int rank_live = __popc(live & ((1u << pbase) - 1));
+    const int rank_dead = jb - rank_live;
+    // bits a block's first lane needs from its second (IQ3: index and sign bits of the block's upper half), or
+    // IQ2_S: two bits per group of eight go to qh[ib/2], gathered from the neighbour lane
     uint32_t hi_bits = 0;
     if (TYPE == GGML_TYPE_IQ2_S) hi_bits = (uint32_t)(gidx[0] >> 8) | ((uint32_t)(gidx[NG > 1 ? 1 : 0] >> 8) << 2);
+    if (TYPE == GGML_TYPE_IQ3_XXS) hi_bits = signs[0] | (signs[NS > 1 ? 1 : 0] << 7);
+    if (TYPE == GGML_TYPE_IQ3_S) {
+#pragma unroll
+        for (int k = 0; k < NG; ++k) hi_bits |= (uint32_t)(gidx[k] >> 8) << k;
+    }
     const uint32_t hi_next = __shfl_down_sync(kFull, hi_bits, 1);
-    if (!active) return;
+    if (!active) continue;
 
-    uint8_t *out = dst + (blk / W) * T::BYTES;
+    uint8_t *out = dst + (ln / W) * T::BYTES;
     const bool clear_all = empty && (TYPE == GGML_TYPE_IQ2_XXS || TYPE == GGML_TYPE_IQ2_XS || TYPE == GGML_TYPE_IQ3_XXS);
     if (j == 0) {
         float dd = d;
@@ -678,25 +742,26 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
             out[74 + (j >> 1)] = empty ? 0 : (uint8_t)(lsc | (lsc_next << 4));
         }
     } else if constexpr (TYPE == GGML_TYPE_IQ3_XXS) {
-        uint32_t sas = 0;
+        static_assert(TYPE != GGML_TYPE_IQ3_XXS || (LPB == 2 && NG == 4 && NS == 2), "two lanes of four groups per block");
 #pragma unroll
-        for (int k = 0; k < 8; ++k) out[2 + 8 * j + k] = (skipped || clear_all) ? 0 : (uint8_t)gidx[k];
-        if (!skipped && !clear_all) sas = signs[0] | (signs[1] << 7) | (signs[2] << 14) | (signs[3] << 21);
-        if (!clear_all) sas |= (uint32_t)lsc << 28;
-        st32(out + 2 + 64 + 4 * j, sas);
-    } else {  // IQ3_S: payload slots are consumed only by blocks that were not skipped
-        const int pos = skipped ? nlive + rank_dead : rank_live;
-        uint32_t qh = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            out[2 + 8 * pos + k] = skipped ? 0 : (uint8_t)gidx[k];
-            qh |= (uint32_t)(gidx[k] >> 8) << k;
+        for (int k = 0; k < NG; ++k) out[2 + 8 * jb + NG * half + k] = (skipped || clear_all) ? 0 : (uint8_t)gidx[k];
+        if (half == 0) {
+            uint32_t sas = 0;
+            if (!skipped && !clear_all) sas = hi_bits | (hi_next << 14);
+            if (!clear_all) sas |= (uint32_t)lsc << 28;
+            st32(out + 2 + 64 + 4 * jb, sas);
         }
-        out[66 + j] = skipped ? 0 : (uint8_t)qh;
+    } else {  // IQ3_S: payload slots are consumed only by blocks that were not skipped
+        static_assert(TYPE != GGML_TYPE_IQ3_S || (LPB == 2 && NG == 4 && NS == 2), "two lanes of four groups per block");
+        const int pos = skipped ? nlive + rank_dead : rank_live;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) out[74 + 4 * pos + k] = skipped ? 0 : (uint8_t)signs[k];
-        if ((j & 1) == 0) out[106 + (j >> 1)] = empty ? 0 : (uint8_t)(lsc | (lsc_next << 4));
+        for (int k = 0; k < NG; ++k) out[2 + 8 * pos + NG * half + k] = skipped ? 0 : (uint8_t)gidx[k];
+        if (half == 0) out[66 + jb] = skipped ? 0 : (uint8_t)(hi_bits | (hi_next << NG));
+#pragma unroll
+        for (int k = 0; k < NS; ++k) out[74 + 4 * pos + NS * half + k] = skipped ? 0 : (uint8_t)signs[k];
+        if (half == 0 && (jb & 1) == 0) out[106 + (jb >> 1)] = empty ? 0 : (uint8_t)(lsc | (lsc_next << 4));
     }
+    }  // chunks
 }
 
 template <int TYPE>
@@ -704,18 +769,29 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
                    cudaStream_t stream) {
     using T = Traits<TYPE>;
     const IqSearchTable &tab = state->iq[T::TABLE];
-    if (!tab.grid || !tab.records || !tab.map_s || tab.record_steps != T::REC) return cudaErrorInvalidValue;
-    const int64_t nblocks = nelems / T::BS;
-    if (nblocks <= 0) return cudaSuccess;
-    constexpr int kThreads = T::THREADS, NG = T::BS / T::GD, XP = T::BS + 4, TMAX = 32 * NG;
-    const int64_t grid = (nblocks + kThreads - 1) / kThreads;
+    if (!tab.grid || !tab.records || !tab.map_s || tab.record_steps != T::REC || (tab.records_bytes & 7)) return cudaErrorInvalidValue;
+    constexpr int EL = T::BS / T::LPB;  // elements per lane
+    const int64_t nlanes = nelems / EL;
+    if (nlanes <= 0) return cudaSuccess;
+    constexpr int kThreads = T::THREADS, NG = EL / T::GD, XP = EL + 4, TMAX = 32 * NG;
+    int64_t grid = (nlanes + kThreads - 1) / kThreads;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
-    const size_t smem = ((size_t)tab.grid_size * T::GD / 2 + (kThreads / 32) * (2 * 32 * XP + TMAX * 7)) * sizeof(float);
+    size_t smem = ((size_t)tab.grid_size * T::GD / 2 + (kThreads / 32) * (2 * 32 * XP + TMAX * 7)) * sizeof(float);
+    if (T::LISTS_SHARED) {  // one CTA per SM for the whole launch
+        static const int sms = [] {
+            int dev = 0, n = 148;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+            return n > 0 ? n : 1;
+        }();
+        if (grid > sms) grid = sms;
+        smem += ((size_t)tab.records_bytes + 15) & ~(size_t)15;
+    }
     // a per-device setting: made on every launch (microseconds against a kernel of milliseconds) so that every GPU
     // of a process that drives several has it
     const cudaError_t attr = cudaFuncSetAttribute(quant_iq23_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (attr != cudaSuccess) return attr;
-    quant_iq23_kernel<TYPE><<<(unsigned)grid, kThreads, smem, stream>>>(src, qw, static_cast<uint8_t *>(dst), nblocks, n_per_row, tab);
+    quant_iq23_kernel<TYPE><<<(unsigned)grid, kThreads, smem, stream>>>(src, qw, static_cast<uint8_t *>(dst), nlanes, n_per_row, tab);
     count_launch();
     return cudaGetLastError();
 }
