@@ -634,7 +634,7 @@ def convert(options: Options) -> dict:
     clock = time.perf_counter
     began = clock()
     # wall-clock seconds of the calling thread per stage; the reads and the host<->device copies overlap the encode
-    spent = {"metadata": 0.0, "read": 0.0, "cuda_quant": 0.0, "write": 0.0}
+    spent = {"metadata": 0.0, "setup": 0.0, "read": 0.0, "cuda_quant": 0.0, "write": 0.0, "close": 0.0}
     dst, _, _, kv, plans, result = plan_file(options)
     infos = [TensorInfo(p.key, tuple(p.write_shape), int(Q[p.qtype]), p.nbytes) for p in plans]
     head = header_bytes(kv, infos)
@@ -665,9 +665,29 @@ def convert(options: Options) -> dict:
         at += pad_to(p.nbytes)
     file_size = at
 
+    # The output is written through a shared mapping: writer threads copy finished pieces to their place, so the
+    # pages of a new file are allocated by all of them at once (write() calls on one file take turns on its lock:
+    # 1.8 GB to a RAM-backed file system took 0.36 s with eight threads calling pwrite).  A file system that is too
+    # full is an OSError before anything is written (free space is checked first) or from the reservation that runs
+    # beside the first batches (posix_fallocate on a thread of its own); waiting for the reservation before the first
+    # copy cost 0.1 s, since it touches every page once by itself.
+    out_map = None
+    reserved = None
+
+    def reserve():
+        import errno
+        try:
+            os.posix_fallocate(out_fd, 0, file_size)
+        except OSError as e:
+            if e.errno not in (errno.EOPNOTSUPP, errno.EINVAL, errno.ENOSYS):
+                raise
+
     def write_at(view, file_offset: int):
-        done, total = 0, len(view)
         buffer = memoryview(view).cast("B")
+        if out_map is not None:
+            out_map[file_offset:file_offset + len(buffer)] = np.frombuffer(buffer, np.uint8)
+            return
+        done, total = 0, len(buffer)
         while done < total:
             done += os.pwrite(out_fd, buffer[done:total], file_offset + done)
 
@@ -706,6 +726,17 @@ def convert(options: Options) -> dict:
     split_weights: dict[str, np.ndarray] = {}
     finished = False
     try:
+        out_fd = os.open(dst, os.O_RDWR | os.O_CREAT | os.O_TRUNC, 0o644)
+        room = os.fstatvfs(out_fd)
+        if room.f_bavail * room.f_frsize < file_size:
+            import errno
+            raise OSError(errno.ENOSPC, f"{dst}: {file_size} bytes needed, {room.f_bavail * room.f_frsize} free")
+        os.ftruncate(out_fd, file_size)       # the padding between tensors is the zeros of the extended file
+        reserved = writers.submit(reserve)
+        try:
+            out_map = np.memmap(dst, dtype=np.uint8, mode="r+", shape=(file_size,))
+        except (OSError, ValueError):
+            out_map = None                    # a file system without shared mappings: positioned writes
         pieces = list(_pieces(plans, cap))
         # A type that needs importance weights derives them from the WHOLE tensor (upstream compute_auto_imatrix,
         # csrc/_libgguf_module.cpp:1210-1242).  A tensor that goes through in one piece gets them inside the pipeline;
@@ -720,12 +751,11 @@ def convert(options: Options) -> dict:
                 split_weights[p.key] = whole_tensor_imatrix(whole)
         batches = list(_batches(pieces, cap))
         arenas = _arenas(lib, devices[0], cap + 4096, 2)
-        out_fd = os.open(dst, os.O_WRONLY | os.O_CREAT | os.O_TRUNC, 0o644)
-        os.ftruncate(out_fd, file_size)       # the padding between tensors is the zeros of the extended file
-        write_at(head, 0)
+        head_written = writers.submit(write_at, head, 0)   # behind the reservation, like every other write
         writes = [[], []]                      # write futures of the batch that last used each arena pair
         with ConversionPipeline(devices, slots=3, chunk_bytes=chunk) as pipe:
             staged = stage(batches[0], arenas[0]) if batches else None
+            spent["setup"] = clock() - began - spent["metadata"]   # devices, arenas, pipeline, output file
             for i, batch in enumerate(batches):
                 entries, outputs, futures = staged
                 t0 = clock()
@@ -758,11 +788,16 @@ def convert(options: Options) -> dict:
             for pending in writes:
                 for f in pending:
                     f.result()
+            head_written.result()
+            reserved.result()
             spent["write"] += clock() - t4
+            t5 = clock()
+        spent["close"] = clock() - t5   # the pipeline's streams and buffers
         finished = True
     finally:
         readers.shutdown(wait=True)
         writers.shutdown(wait=True)
+        out_map = None   # unmaps; the dirty pages belong to the file
         os.close(fd)
         if out_fd >= 0:
             os.close(out_fd)
