@@ -375,7 +375,8 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
     // a warp takes 32 lanes' worth of elements at a time; the launch gives every warp one such chunk, or, under the
     // CTAs that stay, as many as it takes
     const int64_t nchunks = (nlanes + 31) >> 5;
-    for (int64_t chunk = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); chunk < nchunks; chunk += (int64_t)gridDim.x * (kThreads / 32)) {
+    for (int64_t chunk = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); chunk < nchunks;
+         chunk = T::LISTS_SHARED ? chunk + (int64_t)gridDim.x * (kThreads / 32) : nchunks) {
     int64_t ln = chunk * 32 + lane;
     const bool active = ln < nlanes;
     if (!active) ln = nlanes - W + j;  // lanes past the end redo the last super-block (whole super-blocks per row) and write nothing
