@@ -158,6 +158,14 @@ LIBGGUF_CUDA_API int libgguf_cuda_iq_search_table(int64_t qtype, int32_t *grid_s
                                                   const int32_t **map, int64_t *map_size, const uint16_t **neighbours,
                                                   int64_t *neighbours_len);
 
+/* Inspection, no upstream counterpart: the same neighbour lists in the layout the IQ2 / IQ3 quantizers scan.  Every list
+ * is a whole number of records of `record_entries` 16-bit entries (4 or 8), its tail filled with copies of its first
+ * entry; an entry is grid index * dims * 2 (the byte offset of the codebook row as the kernel stages it).  map_s is
+ * `map` with a list's first record and record count folded in: -(((first_record << 8) | records) + 1).
+ * UNSUPPORTED_TYPE for the IQ1 types, which scan the lists as upstream stores them.  Needs no device. */
+LIBGGUF_CUDA_API int libgguf_cuda_iq_scan_records(int64_t qtype, int32_t *record_entries, const uint16_t **entries,
+                                                  int64_t *entries_len, const int32_t **map_s, int64_t *map_size);
+
 /* Self-test, no upstream counterpart: the MXFP4 / NVFP4 quantizers pick each element's level by threshold
  * comparisons instead of upstream's 16-way scan (libgguf_common.h:321-335).  This runs both on every one of the
  * 2^32 float bit patterns at block scale `scale` on the current device (about a second) and stores how many

@@ -79,6 +79,8 @@ NATIVE_ABI = {
     "libgguf_cuda_quantize_weighted_rows_static_max_rows": (c_int64, []),
     "libgguf_cuda_iq_search_table": (c_int, [c_int64, POINTER(c_int32), POINTER(c_int32), POINTER(c_void_p), POINTER(c_void_p),
                                      POINTER(c_int64), POINTER(c_void_p), POINTER(c_int64)]),
+    "libgguf_cuda_iq_scan_records": (c_int, [c_int64, POINTER(c_int32), POINTER(c_void_p), POINTER(c_int64), POINTER(c_void_p),
+                                     POINTER(c_int64)]),
     "libgguf_cuda_selftest_fp4": (c_int, [c_float, POINTER(c_uint64)]),
     "libgguf_cuda_selftest_fp4_mode": (c_int, [c_float, c_int, POINTER(c_uint64), POINTER(c_uint64)]),
     "libgguf_cuda_pipeline_create": (c_int, [POINTER(c_int), c_int, c_int, c_size_t, POINTER(c_void_p)]),

@@ -86,6 +86,40 @@ int table_for_type(int type) {
     }
 }
 
+// The IQ2 / IQ3 neighbour lists in the layout the scans read (see IqSearchTable), built on the host once per process.
+struct IqScanRecords {
+    bool valid = false;
+    int record_steps = 0;            // steps of kIqStepEntries entries per record
+    std::vector<uint16_t> entries;   // records back to back
+    std::vector<int32_t> map_s;
+};
+
+const IqScanRecords &iq_scan_records(int id) {
+    static IqScanRecords built[IQT_COUNT];
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    IqScanRecords &r = built[id];
+    if (r.record_steps) return r;
+    const IqHostTable &h = iq_host_table(id);
+    // the codebook with the longest lists (IQ2_XS, mean 58 entries) uses two-step records: half as many list loads
+    const uint32_t rec_steps = id == IQT_2XS ? 2 : 1, rec_entries = rec_steps * kIqStepEntries;
+    r.record_steps = (int)rec_steps;
+    r.map_s.resize(h.map.size());
+    bool ok = (size_t)h.grid_size * h.dims * 2 <= 65536;
+    for (size_t i = 0; ok && i < h.map.size(); ++i) {
+        const int32_t m = h.map[i];
+        if (m >= 0) { r.map_s[i] = m; continue; }
+        const uint32_t off = (uint32_t)(-m - 1), n = h.neighbours[off];
+        const uint32_t first_rec = (uint32_t)(r.entries.size() / rec_entries), nrec = (n + rec_entries - 1) / rec_entries;
+        if (first_rec >= (1u << 22) || nrec >= (1u << 8)) { ok = false; break; }
+        for (uint32_t e = 0; e < nrec * rec_entries; ++e)
+            r.entries.push_back((uint16_t)(h.neighbours[off + 1 + (e < n ? e : 0)] * h.dims * 2));
+        r.map_s[i] = -(int32_t)(((first_rec << 8) | nrec) + 1);
+    }
+    r.valid = ok;
+    return r;
+}
+
 }  // namespace
 
 const DeviceState *device_state_for(int type, int dev) {
@@ -105,24 +139,12 @@ const DeviceState *device_state_for(int type, int dev) {
         t.map = upload(slot, h.map);
         t.neighbours = upload(slot, h.neighbours);
         if (id != IQT_1S) {   // one load then tells a scan where its list is and how many records it has
-            // the codebooks with long lists  (IQ2_XS, mean 58 entries) uses two-step records: half as many list loads
-            const uint32_t rec_steps = id == IQT_2XS ? 2 : 1, rec_entries = rec_steps * kIqStepEntries;
-            std::vector<int32_t> packed(h.map.size());
-            std::vector<uint16_t> entries;
-            for (size_t i = 0; i < h.map.size(); ++i) {
-                const int32_t m = h.map[i];
-                if (m >= 0) { packed[i] = m; continue; }
-                const uint32_t off = (uint32_t)(-m - 1), n = h.neighbours[off];
-                const uint32_t first_rec = (uint32_t)(entries.size() / rec_entries), nrec = (n + rec_entries - 1) / rec_entries;
-                if (first_rec >= (1u << 22) || nrec >= (1u << 8) || (size_t)h.grid_size * h.dims * 2 > 65536) return nullptr;
-                for (uint32_t e = 0; e < nrec * rec_entries; ++e)
-                    entries.push_back((uint16_t)(h.neighbours[off + 1 + (e < n ? e : 0)] * h.dims * 2));
-                packed[i] = -(int32_t)(((first_rec << 8) | nrec) + 1);
-            }
-            t.map_s = upload(slot, packed);
-            t.records = upload(slot, entries);
-            t.record_steps = (int)rec_steps;
-            t.records_bytes = (int)(entries.size() * sizeof(uint16_t));
+            const IqScanRecords &r = iq_scan_records(id);
+            if (!r.valid) return nullptr;
+            t.map_s = upload(slot, r.map_s);
+            t.records = upload(slot, r.entries);
+            t.record_steps = r.record_steps;
+            t.records_bytes = (int)(r.entries.size() * sizeof(uint16_t));
             if (!t.map_s || !t.records) return nullptr;
         }
         if (!t.grid || !t.map || !t.neighbours) return nullptr;
@@ -165,5 +187,20 @@ extern "C" int libgguf_cuda_iq_search_table(int64_t qtype, int32_t *grid_size, i
     if (map_size) *map_size = (int64_t)t.map.size();
     if (neighbours) *neighbours = t.neighbours.data();
     if (neighbours_len) *neighbours_len = (int64_t)t.neighbours.size();
+    return LIBGGUF_CUDA_STATUS_SUCCESS;
+}
+
+// Host view of the scan layout of one IQ2 / IQ3 quantizer's neighbour lists (no device involved).
+extern "C" int libgguf_cuda_iq_scan_records(int64_t qtype, int32_t *record_entries, const uint16_t **entries, int64_t *entries_len,
+                                            const int32_t **map_s, int64_t *map_size) {
+    const int id = gguf::table_for_type((int)qtype);
+    if (id < 0 || id == gguf::IQT_1S) return LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE;
+    const gguf::IqScanRecords &r = gguf::iq_scan_records(id);
+    if (!r.valid) return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;  // a codebook outside the layout's field widths
+    if (record_entries) *record_entries = r.record_steps * gguf::kIqStepEntries;
+    if (entries) *entries = r.entries.data();
+    if (entries_len) *entries_len = (int64_t)r.entries.size();
+    if (map_s) *map_s = r.map_s.data();
+    if (map_size) *map_size = (int64_t)r.map_s.size();
     return LIBGGUF_CUDA_STATUS_SUCCESS;
 }

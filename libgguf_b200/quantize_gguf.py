@@ -728,7 +728,7 @@ def convert(options: Options) -> dict:
     try:
         out_fd = os.open(dst, os.O_RDWR | os.O_CREAT | os.O_TRUNC, 0o644)
         room = os.fstatvfs(out_fd)
-        if room.f_bavail * room.f_frsize < file_size:
+        if room.f_blocks > 0 and room.f_bavail * room.f_frsize < file_size:   # (a file system that reports no sizes is not judged)
             import errno
             raise OSError(errno.ENOSPC, f"{dst}: {file_size} bytes needed, {room.f_bavail * room.f_frsize} free")
         os.ftruncate(out_fd, file_size)       # the padding between tensors is the zeros of the extended file

@@ -193,3 +193,29 @@ def test_a_row_wider_than_the_batch_still_converts_and_failures_leave_no_file(gg
     finally:
         conv.ConversionPipeline = original
     assert not Path(broken).exists()
+
+
+def test_a_full_file_system_is_an_error_before_anything_is_written(tmp_path, monkeypatch):
+    """The output is filled through a shared mapping, where running out of blocks would be a fault inside a copy; the
+    converter therefore checks the free space first and reports ENOSPC as an OSError, leaving no file."""
+    import errno
+    import os
+    from libgguf_b200 import quantize_gguf as qg
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal((64, 1024)) * 0.05).astype(np.float32)
+    src = str(tmp_path / "m.safetensors")
+    cm.write_safetensors(src, [("model.layers.0.self_attn.q_proj.weight", "F32", w), ("model.norm.weight", "F32", w[0, :256])])
+    dst = str(tmp_path / "full.gguf")
+    real = os.fstatvfs
+
+    class NoRoom:
+        def __init__(self, st):
+            self.f_blocks, self.f_frsize, self.f_bavail = st.f_blocks, st.f_frsize, 0
+
+    monkeypatch.setattr(os, "fstatvfs", lambda fd: NoRoom(real(fd)))
+    with pytest.raises(OSError) as caught:
+        qg.convert(qg.parse_args(["--src", src, "--dst", dst, "--qtype", "Q8_0", "--gpus", "1"]))
+    assert caught.value.errno == errno.ENOSPC
+    assert not Path(dst).exists()
+    monkeypatch.undo()
+    assert qg.main(["--src", src, "--dst", dst, "--qtype", "Q8_0", "--gpus", "1"]) == 0 and Path(dst).stat().st_size > w.size

@@ -67,6 +67,46 @@ def test_search_tables_equal_upstreams(ref, name):
     assert (nb[offs] > 0).all()
 
 
+@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S"])
+def test_scan_records_hold_upstreams_lists(name):
+    """The layout the IQ2 / IQ3 kernels scan is derived from the lists above: same entries in the same order, a tail of
+    copies of the first entry up to a whole record, records back to back, map_s pointing at them."""
+    from libgguf_b200._native import lib
+    qtype, _, _, _, grid_size, dims, map_size = CASES[name]
+    _, mp, nb = _ours(qtype)
+    per, n_entries, n_map = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64()
+    ent, ms = ctypes.c_void_p(), ctypes.c_void_p()
+    assert lib.libgguf_cuda_iq_scan_records(qtype, ctypes.byref(per), ctypes.byref(ent), ctypes.byref(n_entries), ctypes.byref(ms),
+                                            ctypes.byref(n_map)) == 0
+    per = per.value
+    assert per == (8 if name == "IQ2_XS" else 4) and n_map.value == map_size and n_entries.value % per == 0
+    entries = np.ctypeslib.as_array(ctypes.cast(ent.value, ctypes.POINTER(ctypes.c_uint16)), (n_entries.value,))
+    map_s = np.ctypeslib.as_array(ctypes.cast(ms.value, ctypes.POINTER(ctypes.c_int32)), (map_size,))
+    on_grid = mp >= 0
+    np.testing.assert_array_equal(map_s[on_grid], mp[on_grid])
+    assert (map_s[~on_grid] < 0).all()
+    packed = (-map_s[~on_grid].astype(np.int64) - 1)
+    first, count = packed >> 8, packed & 255
+    offs = -mp[~on_grid].astype(np.int64) - 1
+    n = nb[offs].astype(np.int64)
+    np.testing.assert_array_equal(count, (n + per - 1) // per)
+    # records back to back in map order, nothing between them
+    np.testing.assert_array_equal(first, np.concatenate(([0], np.cumsum(count)[:-1])))
+    assert int(first[-1] + count[-1]) * per == n_entries.value
+    assert int(entries.max()) == (grid_size - 1) * dims * 2 or int(entries.max()) < grid_size * dims * 2
+    for i in np.random.default_rng(0).choice(len(offs), 400, replace=False).tolist() + [0, len(offs) - 1, int(np.argmax(n))]:
+        want = nb[offs[i] + 1:offs[i] + 1 + n[i]].astype(np.int64) * dims * 2
+        got = entries[first[i] * per:(first[i] + count[i]) * per].astype(np.int64)
+        np.testing.assert_array_equal(got[:n[i]], want)
+        assert (got[n[i]:] == want[0]).all()
+
+
+def test_scan_records_reject_other_types():
+    from libgguf_b200._native import lib
+    assert lib.libgguf_cuda_iq_scan_records(19, None, None, None, None, None) == 2   # IQ1_S scans upstream's lists
+    assert lib.libgguf_cuda_iq_scan_records(12, None, None, None, None, None) == 2
+
+
 def test_search_table_rejects_other_types():
     from libgguf_b200._native import lib
     assert lib.libgguf_cuda_iq_search_table(12, None, None, None, None, None, None, None) == 2
