@@ -204,7 +204,8 @@ def test_a_full_file_system_is_an_error_before_anything_is_written(tmp_path, mon
     rng = np.random.default_rng(5)
     w = (rng.standard_normal((64, 1024)) * 0.05).astype(np.float32)
     src = str(tmp_path / "m.safetensors")
-    cm.write_safetensors(src, [("model.layers.0.self_attn.q_proj.weight", "F32", w), ("model.norm.weight", "F32", w[0, :256])])
+    cm.write_safetensors(src, [("model.layers.0.self_attn.q_proj.weight", "F32", w), ("model.layers.0.mlp.down_proj.weight", "F32", w),
+                               ("model.norm.weight", "F32", w[0, :256])])
     dst = str(tmp_path / "full.gguf")
     real = os.fstatvfs
 
