@@ -96,7 +96,7 @@ def test_importance_weighted_rows_match_checker(gguf, checker, name):
     np.testing.assert_array_equal(gguf.quantize_rows(x, qtype, im), checker.quantize_rows(x, qtype, im))
 
 
-@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_S", "IQ3_XXS", "IQ1_S"])
+@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"])
 def test_lattice_workload_slice_at_full_width(gguf, checker, name):
     """The lattice-quantizer benchmark workload at its own width: a 256-row slice of the 4096 x 11008 Student-t matrix with the
     chi-square importance weights, plus rows whose blocks are partly zero (lanes that queue no scans next to lanes
