@@ -246,8 +246,9 @@ template <int GD, int TMAX, int REC, bool SHARED>
 GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
                           const float *xs, const float *ws, const uint32_t *gridh, const void *__restrict__ records) {
     using Record = typename RecordOf<REC>::type;
-    // records are fetched this many iterations early, across list boundaries (from shared memory: one)
-    constexpr int AHEAD = SHARED ? 1 : (REC == 1 ? 3 : 2);
+    // records in global memory are fetched this many iterations early, across list boundaries; records in shared
+    // memory are read where they are used (no second cursor to keep)
+    constexpr int AHEAD = REC == 1 ? 3 : 2;
     const Record *const recs = static_cast<const Record *>(records);
     const uint32_t share = (S + 31) >> 5;
     uint32_t s = umin((uint32_t)lane * share, S);
@@ -273,8 +274,8 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
     const Record *fp = recs + tk.base + j;
     Record ring[AHEAD];
     auto fetch = [&](Record &rec) {
-        if (fs < end) {
-            rec = SHARED ? *fp : __ldg(fp);
+        if (!SHARED && fs < end) {
+            rec = __ldg(fp);
             ++fp;
             ++fs;
             if (--fleft == 0 && fs < end) {
@@ -288,10 +289,15 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
 #pragma unroll
     for (int d = 0; d < AHEAD; ++d) { ring[d] = Record(); fetch(ring[d]); }
     while (s < end) {
-        const Record rec = ring[0];
+        Record rec;
+        if constexpr (SHARED) {
+            rec = recs[tk.base + j];
+        } else {
+            rec = ring[0];
 #pragma unroll
-        for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
-        fetch(ring[AHEAD - 1]);
+            for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
+            fetch(ring[AHEAD - 1]);
+        }
         static_assert(PER == 4, "a step is two words of two 16-bit row offsets");
         uint32_t words[2 * REC];
         if constexpr (REC == 1) { words[0] = rec.x; words[1] = rec.y; }
