@@ -90,6 +90,7 @@ int table_for_type(int type) {
 struct IqScanRecords {
     bool valid = false;
     int record_steps = 0;            // steps of kIqStepEntries entries per record
+    int hot_bytes = 0;               // whole lists at the front of `entries` that fit kIqHotBudget
     std::vector<uint16_t> entries;   // records back to back
     std::vector<int32_t> map_s;
 };
@@ -106,16 +107,41 @@ const IqScanRecords &iq_scan_records(int id) {
     r.record_steps = (int)rec_steps;
     r.map_s.resize(h.map.size());
     bool ok = (size_t)h.grid_size * h.dims * 2 <= 65536;
-    for (size_t i = 0; ok && i < h.map.size(); ++i) {
-        const int32_t m = h.map[i];
-        if (m >= 0) { r.map_s[i] = m; continue; }
-        const uint32_t off = (uint32_t)(-m - 1), n = h.neighbours[off];
+    // lattice points off the codebook, most common first: by the sum of their levels, then by index
+    const int bits = h.dims == 8 ? 2 : 3;
+    std::vector<uint32_t> order;
+    for (size_t i = 0; i < h.map.size(); ++i) {
+        if (h.map[i] >= 0) r.map_s[i] = h.map[i];
+        else order.push_back((uint32_t)i);
+    }
+    auto level_sum = [&](uint32_t u) {
+        int sum = 0;
+        for (int c = 0; c < h.dims; ++c) {
+            const int level = (int)((u >> (bits * c)) & ((1u << bits) - 1));
+            sum += (bits == 2 && level == 3) ? 1000 : level;  // a 2-bit field of 3 is no level: the quantizers never look such a point up
+        }
+        return sum;
+    };
+    if (kIqHotBudget[id] < (1 << 20))   // (a codebook whose records all fit keeps them in index order)
+        std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return level_sum(a) < level_sum(b); });
+    bool hot_open = true;
+    for (size_t k = 0; ok && k < order.size(); ++k) {
+        const uint32_t i = order[k];
+        const uint32_t off = (uint32_t)(-h.map[i] - 1), n = h.neighbours[off];
         const uint32_t first_rec = (uint32_t)(r.entries.size() / rec_entries), nrec = (n + rec_entries - 1) / rec_entries;
         if (first_rec >= (1u << 22) || nrec >= (1u << 8)) { ok = false; break; }
         for (uint32_t e = 0; e < nrec * rec_entries; ++e)
             r.entries.push_back((uint16_t)(h.neighbours[off + 1 + (e < n ? e : 0)] * h.dims * 2));
         r.map_s[i] = -(int32_t)(((first_rec << 8) | nrec) + 1);
+        const size_t bytes = r.entries.size() * sizeof(uint16_t);
+        if (hot_open && bytes <= (size_t)kIqHotBudget[id]) {
+            if (bytes % 16 == 0) r.hot_bytes = (int)bytes;   // the prefix is copied in 16-byte pieces
+        } else {
+            hot_open = false;
+        }
     }
+    while (r.entries.size() % 8) r.entries.push_back(0);     // a whole number of 16-byte pieces
+    if (r.entries.size() * sizeof(uint16_t) <= (size_t)kIqHotBudget[id]) r.hot_bytes = (int)(r.entries.size() * sizeof(uint16_t));
     r.valid = ok;
     return r;
 }
@@ -145,6 +171,7 @@ const DeviceState *device_state_for(int type, int dev) {
             t.records = upload(slot, r.entries);
             t.record_steps = r.record_steps;
             t.records_bytes = (int)(r.entries.size() * sizeof(uint16_t));
+            t.hot_bytes = r.hot_bytes;
             if (!t.map_s || !t.records) return nullptr;
         }
         if (!t.grid || !t.map || !t.neighbours) return nullptr;

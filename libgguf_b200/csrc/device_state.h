@@ -11,6 +11,11 @@ namespace gguf {
 
 constexpr int kMaxDevices = 64;
 constexpr int kIqStepEntries = 4;
+enum IqTableId { IQT_2XXS = 0, IQT_2XS, IQT_1S, IQT_2S, IQT_3XXS, IQT_3S, IQT_COUNT };
+// shared memory a kernel has for neighbour records beside its codebook and per-warp state (quant_iq23.cu), bytes:
+// IQ2_XXS stages none (its 128 registers and 12.5 KB per warp leave 23 KB, and fewer warps cost more than that buys),
+// IQ2_XS 84 KB (about 80 % of the reads on Student-t data, 70 % on normal data), IQ2_S 76 KB (97 % / 95 %), IQ3 everything
+constexpr int kIqHotBudget[IQT_COUNT] = {0, 86016, 0, 77824, 1 << 20, 1 << 20};
 
 // One IQ codebook prepared for searching (device pointers).
 struct IqSearchTable {
@@ -22,6 +27,10 @@ struct IqSearchTable {
     // it is never a strict improvement), records aligned to their size (8 or 16 bytes), an entry stored as the byte
     // offset of its codebook row in the kernel's staged codebook (grid index x dims x 2).  map_s is map with a list's
     // first record and record count folded in: -(((first_record << 8) | records) + 1).  Absent for the IQ1 codebook.
+    // Where a kernel can keep only part of the array in shared memory (IQ2) the lists are ordered by how often their
+    // lattice point comes up (sum of its levels, ascending: blocks scaled to their maximum are mostly small levels), so
+    // a prefix holds most of the scans' reads: hot_bytes = the whole lists at the front that fit kIqHotBudget (0: none
+    // staged; records_bytes: all of it, the IQ3 codebooks).
     const void *records = nullptr;
     const int32_t *map_s = nullptr;
     int record_steps = 0;
@@ -30,9 +39,8 @@ struct IqSearchTable {
     int dims = 0;
     int map_size = 0;
     int neighbours_len = 0;
+    int hot_bytes = 0;
 };
-
-enum IqTableId { IQT_2XXS = 0, IQT_2XS, IQT_1S, IQT_2S, IQT_3XXS, IQT_3S, IQT_COUNT };
 
 struct DeviceState {
     int device = -1;

@@ -17,7 +17,9 @@
 // aligned records of four or eight entries, an entry being the offset of its codebook row), the codebook is staged
 // in shared memory as bfloat16 pairs (exact for its small odd integers), every lane's magnitudes and root weights
 // in padded rows.  The IQ3 codebooks' records (47 and 58 KB) are staged in shared memory too, under one CTA per SM
-// that stays for the whole launch; the IQ2 records (0.5-1.3 MB) and the lattice map stay in global memory (L2).
+// that stays for the whole launch; of the IQ2_XS and IQ2_S records (1.1 and 0.5 MB) the front of the array, which
+// holds the most common lattice points' lists, is staged the same way (84 and 76 KB) and the rest read from global
+// memory; the IQ2_XXS records and every lattice map stay in global memory (L2).
 // upstream: csrc/quant/iq2_xxs.cpp:4-224, iq2_xs.cpp:4-230, iq2_s.cpp:4-218, iq3_xxs.cpp:4-273,
 // iq3_s.cpp:5-233, csrc/common/libgguf_iq_tables.cpp:434-462 and :683-711.
 #include <float.h>
@@ -35,31 +37,31 @@ constexpr unsigned kFull = 0xffffffffu;
 template <int TYPE> struct Traits;
 template <> struct Traits<GGML_TYPE_IQ2_XXS> {
     static constexpr int BS = 32, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 6, BYTES = 66, TABLE = IQT_2XXS, THREADS = 128, CTAS = 4, REC = 1, LPB = 1;
-    static constexpr bool LISTS_SHARED = false, MERGED = true;
+    static constexpr bool LISTS_SHARED = false, LISTS_HOT = false, MERGED = true;
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = true;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_XS> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 128, CTAS = 5, REC = 2, LPB = 1;
-    static constexpr bool LISTS_SHARED = false, MERGED = false;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 74, TABLE = IQT_2XS, THREADS = 640, CTAS = 1, REC = 2, LPB = 1;
+    static constexpr bool LISTS_SHARED = false, LISTS_HOT = true, MERGED = false;  // 8 KB codebook + 20 warps x 6.75 KB + 84 KB of records
     static constexpr bool PARITY = true, SIGMA_X2 = false, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-15f;
 };
 template <> struct Traits<GGML_TYPE_IQ2_S> {
-    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 128, CTAS = 5, REC = 1, LPB = 1;
-    static constexpr bool LISTS_SHARED = false, MERGED = false;
+    static constexpr int BS = 16, GD = 8, BITS = 2, KMAXQ = 3, IS_MAX = 9, BYTES = 82, TABLE = IQT_2S, THREADS = 640, CTAS = 1, REC = 1, LPB = 1;
+    static constexpr bool LISTS_SHARED = false, LISTS_HOT = true, MERGED = false;  // 16 KB codebook + 20 warps x 6.75 KB + 76 KB of records
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.1f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_XXS> {
     static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 15, BYTES = 98, TABLE = IQT_3XXS, THREADS = 640, CTAS = 1, REC = 1, LPB = 2;
-    static constexpr bool MERGED = true, LISTS_SHARED = true;  // 47 KB of records + 2 KB codebook + 20 warps x 8.5 KB
+    static constexpr bool MERGED = true, LISTS_SHARED = true, LISTS_HOT = false;  // 47 KB of records + 2 KB codebook + 20 warps x 8.5 KB
     static constexpr bool PARITY = true, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 1e-8f;
 };
 template <> struct Traits<GGML_TYPE_IQ3_S> {
     static constexpr int BS = 32, GD = 4, BITS = 3, KMAXQ = 8, IS_MAX = 9, BYTES = 110, TABLE = IQT_3S, THREADS = 608, CTAS = 1, REC = 1, LPB = 2;
-    static constexpr bool MERGED = true, LISTS_SHARED = true;  // 58 KB of records + 4 KB codebook + 19 warps x 8.5 KB
+    static constexpr bool MERGED = true, LISTS_SHARED = true, LISTS_HOT = false;  // 58 KB of records + 4 KB codebook + 19 warps x 8.5 KB
     static constexpr bool PARITY = false, SIGMA_X2 = true, QP_INIT = false;
     static constexpr float STEP = 0.2f, EPS = 0.f;  // upstream tests `!max`
 };
@@ -219,7 +221,7 @@ GGUF_D void load_staged(const float *p, float (&x)[N]) {  // shared memory, 16-b
 }
 
 // One neighbour scan a warp has to run: which list, which group of which lane's block, at which scale.
-struct ScanTask {
+struct alignas(16) ScanTask {
     uint32_t base;   // the list's first record in the record array
     uint32_t nrec;   // its length in records
     float scale;
@@ -242,9 +244,10 @@ template <> struct RecordOf<2> { using type = uint4; };
 // bits, position) as one 64-bit key; a lane that saw a whole list stores its key, lanes that share a list combine
 // theirs with a shared-memory atomic minimum.  Distances are sums of non-negative terms, so their bit patterns order
 // like the floats; a NaN or FLT_MAX never wins, as upstream's `<` against FLT_MAX.
-template <int GD, int TMAX, int REC, bool SHARED>
+template <int GD, int TMAX, int REC, bool SHARED, bool HOT>
 GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
-                          const float *xs, const float *ws, const uint32_t *gridh, const void *__restrict__ records) {
+                          const float *xs, const float *ws, const uint32_t *gridh, const void *__restrict__ records, uint32_t nhot = 0,
+                          const void *__restrict__ cold_records = nullptr) {
     using Record = typename RecordOf<REC>::type;
     // records in global memory are fetched this many iterations early, across list boundaries; records in shared
     // memory are read where they are used (no second cursor to keep)
@@ -274,7 +277,7 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
     const Record *fp = recs + tk.base + j;
     Record ring[AHEAD];
     auto fetch = [&](Record &rec) {
-        if (!SHARED && fs < end) {
+        if (!SHARED && !HOT && fs < end) {
             rec = __ldg(fp);
             ++fp;
             ++fs;
@@ -292,6 +295,11 @@ GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, co
         Record rec;
         if constexpr (SHARED) {
             rec = recs[tk.base + j];
+        } else if constexpr (HOT) {
+            // the front of the record array (the most common lattice points' lists) is in shared memory, the rest in global
+            const uint32_t at_record = tk.base + j;
+            if (at_record < nhot) rec = recs[at_record];
+            else rec = __ldg(static_cast<const Record *>(cold_records) + at_record);
         } else {
             rec = ring[0];
 #pragma unroll
@@ -358,12 +366,15 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
     // a few wavefronts instead of a global load that touches 32 lines.
     const void *records = tab.records;
     int state_words = tab.grid_size * (GD / 2);
-    if constexpr (T::LISTS_SHARED) {
+    if constexpr (T::LISTS_SHARED || T::LISTS_HOT) {
         uint2 *const staged = reinterpret_cast<uint2 *>(gridh + state_words);
         const uint2 *const from = static_cast<const uint2 *>(tab.records);
-        for (int i = threadIdx.x; i < tab.records_bytes / 8; i += kThreads) staged[i] = __ldg(from + i);
+        const int staged_bytes = T::LISTS_SHARED ? tab.records_bytes : tab.hot_bytes;   // a multiple of 16
+        for (int i = threadIdx.x; i < staged_bytes / 8; i += kThreads) staged[i] = __ldg(from + i);
         records = staged;
-        state_words += (tab.records_bytes / 4 + 3) & ~3;
+        // (rounded although it is whole already: the expression tells the compiler the alignment of what follows, and the
+        // IQ3 kernels are 4 % slower without it)
+        state_words += (staged_bytes / 4 + 3) & ~3;
     }
     __syncthreads();
     // per warp: every lane's magnitudes and root weights in rows padded by four floats, the pending
@@ -382,7 +393,7 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
     // CTAs that stay, as many as it takes
     const int64_t nchunks = (nlanes + 31) >> 5;
     for (int64_t chunk = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); chunk < nchunks;
-         chunk = T::LISTS_SHARED ? chunk + (int64_t)gridDim.x * (kThreads / 32) : nchunks) {
+         chunk = (T::LISTS_SHARED || T::LISTS_HOT) ? chunk + (int64_t)gridDim.x * (kThreads / 32) : nchunks) {
     int64_t ln = chunk * 32 + lane;
     const bool active = ln < nlanes;
     if (!active) ln = nlanes - W + j;  // lanes past the end redo the last super-block (whole super-blocks per row) and write nothing
@@ -555,7 +566,8 @@ __global__ void __launch_bounds__(Traits<TYPE>::THREADS, Traits<TYPE>::CTAS) qua
                 }
             }
             __syncwarp();
-            if (all >> 10) balanced_scan<GD, TMAX, T::REC, T::LISTS_SHARED>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, records);
+            if (all >> 10) balanced_scan<GD, TMAX, T::REC, T::LISTS_SHARED, T::LISTS_HOT>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, gridh, records,
+                                                                                     T::LISTS_HOT ? (uint32_t)tab.hot_bytes / (8 * T::REC) : 0u, T::LISTS_HOT ? tab.records : nullptr);
             __syncwarp();
             slot = slot0;
 #pragma unroll
@@ -776,7 +788,9 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
                    cudaStream_t stream) {
     using T = Traits<TYPE>;
     const IqSearchTable &tab = state->iq[T::TABLE];
-    if (!tab.grid || !tab.records || !tab.map_s || tab.record_steps != T::REC || (tab.records_bytes & 7)) return cudaErrorInvalidValue;
+    if (!tab.grid || !tab.records || !tab.map_s || tab.record_steps != T::REC || (tab.hot_bytes & 15) ||
+        (T::LISTS_SHARED && tab.hot_bytes != tab.records_bytes))
+        return cudaErrorInvalidValue;
     constexpr int EL = T::BS / T::LPB;  // elements per lane
     const int64_t nlanes = nelems / EL;
     if (nlanes <= 0) return cudaSuccess;
@@ -784,7 +798,7 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
     int64_t grid = (nlanes + kThreads - 1) / kThreads;
     if (grid > 0x7fffffffLL) return cudaErrorInvalidValue;
     size_t smem = ((size_t)tab.grid_size * T::GD / 2 + (kThreads / 32) * (2 * 32 * XP + TMAX * 7)) * sizeof(float);
-    if (T::LISTS_SHARED) {  // one CTA per SM for the whole launch
+    if (T::LISTS_SHARED || T::LISTS_HOT) {  // one CTA per SM for the whole launch
         static const int sms = [] {
             int dev = 0, n = 148;
             cudaGetDevice(&dev);
@@ -792,7 +806,7 @@ cudaError_t launch(const float *src, const float *qw, void *dst, int64_t nelems,
             return n > 0 ? n : 1;
         }();
         if (grid > sms) grid = sms;
-        smem += ((size_t)tab.records_bytes + 15) & ~(size_t)15;
+        smem += (size_t)tab.hot_bytes;
     }
     // a per-device setting: made on every launch (microseconds against a kernel of milliseconds) so that every GPU
     // of a process that drives several has it

@@ -90,9 +90,20 @@ def test_scan_records_hold_upstreams_lists(name):
     offs = -mp[~on_grid].astype(np.int64) - 1
     n = nb[offs].astype(np.int64)
     np.testing.assert_array_equal(count, (n + per - 1) // per)
-    # records back to back in map order, nothing between them
-    np.testing.assert_array_equal(first, np.concatenate(([0], np.cumsum(count)[:-1])))
-    assert int(first[-1] + count[-1]) * per == n_entries.value
+    # every list has a range of its own and together they tile the array (up to a tail that rounds it to 16 bytes).
+    # IQ2 (a kernel keeps only the front of the array in shared memory): most common lattice point first, by the sum of
+    # the point's levels (a 2-bit field of 3 is no level), then by index.  IQ3 (all of it fits): by index.
+    by_start = np.argsort(first)
+    np.testing.assert_array_equal(first[by_start], np.concatenate(([0], np.cumsum(count[by_start])[:-1])))
+    used = int((first[by_start[-1]] + count[by_start[-1]]) * per)
+    assert used <= n_entries.value < used + 8 and n_entries.value % 8 == 0
+    points = np.flatnonzero(~on_grid)
+    bits = 2 if dims == 8 else 3
+    fields = (points[:, None] >> (bits * np.arange(dims))) & ((1 << bits) - 1)
+    key = np.where((bits == 2) & (fields == 3), 1000, fields).sum(1) if dims == 8 else np.zeros(len(points), np.int64)
+    assert (np.diff(key[by_start]) >= 0).all()
+    same = np.diff(key[by_start]) == 0
+    assert (np.diff(points[by_start])[same] > 0).all()
     assert int(entries.max()) == (grid_size - 1) * dims * 2 or int(entries.max()) < grid_size * dims * 2
     for i in np.random.default_rng(0).choice(len(offs), 400, replace=False).tolist() + [0, len(offs) - 1, int(np.argmax(n))]:
         want = nb[offs[i] + 1:offs[i] + 1 + n[i]].astype(np.int64) * dims * 2
