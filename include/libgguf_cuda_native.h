@@ -162,7 +162,7 @@ LIBGGUF_CUDA_API int libgguf_cuda_iq_search_table(int64_t qtype, int32_t *grid_s
  * is a whole number of records of `record_entries` 16-bit entries (4 or 8), its tail filled with copies of its first
  * entry; an entry is grid index * dims * 2 (the byte offset of the codebook row as the kernel stages it).  map_s is
  * `map` with a list's first record and record count folded in: -(((first_record << 8) | records) + 1).
- * UNSUPPORTED_TYPE for the IQ1 types, which scan the lists as upstream stores them.  Needs no device. */
+ * (IQ1: 16 x the grid index.)  Needs no device. */
 LIBGGUF_CUDA_API int libgguf_cuda_iq_scan_records(int64_t qtype, int32_t *record_entries, const uint16_t **entries,
                                                   int64_t *entries_len, const int32_t **map_s, int64_t *map_size);
 

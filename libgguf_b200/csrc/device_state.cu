@@ -164,7 +164,7 @@ const DeviceState *device_state_for(int type, int dev) {
         t.grid = upload(slot, h.grid);
         t.map = upload(slot, h.map);
         t.neighbours = upload(slot, h.neighbours);
-        if (id != IQT_1S) {   // one load then tells a scan where its list is and how many records it has
+        {   // one load then tells a scan where its list is and how many records it has
             const IqScanRecords &r = iq_scan_records(id);
             if (!r.valid) return nullptr;
             t.map_s = upload(slot, r.map_s);
@@ -221,7 +221,7 @@ extern "C" int libgguf_cuda_iq_search_table(int64_t qtype, int32_t *grid_size, i
 extern "C" int libgguf_cuda_iq_scan_records(int64_t qtype, int32_t *record_entries, const uint16_t **entries, int64_t *entries_len,
                                             const int32_t **map_s, int64_t *map_size) {
     const int id = gguf::table_for_type((int)qtype);
-    if (id < 0 || id == gguf::IQT_1S) return LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE;
+    if (id < 0) return LIBGGUF_CUDA_STATUS_UNSUPPORTED_TYPE;
     const gguf::IqScanRecords &r = gguf::iq_scan_records(id);
     if (!r.valid) return LIBGGUF_CUDA_STATUS_INVALID_ARGUMENT;  // a codebook outside the layout's field widths
     if (record_entries) *record_entries = r.record_steps * gguf::kIqStepEntries;

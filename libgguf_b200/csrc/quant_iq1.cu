@@ -33,36 +33,129 @@ GGUF_D void load_group(const float *p, float (&x)[N]) {
     }
 }
 
-// upstream libgguf_iq_tables.cpp:714-781 (the reachable part: a non-empty neighbour list), run by the whole warp for
-// the group of one of its lanes: lane i evaluates entries i, i + 32, ... of the list; the winner is the first strict
-// minimum in list order, i.e. the smallest (distance, position), found with two warp-wide integer minima (distances
-// are sums of non-negative terms, so their bit patterns order like the values; FLT_MAX and NaN never win, as
-// upstream's `<` against FLT_MAX).  All lanes pass the same list, scale and values.  Left to the owning lane alone the
-// four scans of a block (1 to 205 entries each) ran with a third of the warp busy.
-GGUF_D int best_neighbour_ternary(const uint16_t *__restrict__ nb, const uint8_t *__restrict__ grid, const float (&xv)[8],
-                                  const float (&wv)[8], float scale, const float (&xg)[3], int lane) {
-    const int n = __ldg(nb);
-    float best_score = FLT_MAX;
-    uint32_t best_j = 0xFFFFFFFFu;
-    int best = 0;
-    for (int j = lane; j < n; j += 32) {
-        const int g = __ldg(nb + 1 + j);
-        const uint2 pgw = __ldg(reinterpret_cast<const uint2 *>(grid) + g);
-        float d2 = 0;
+// The neighbour scans (upstream libgguf_iq_tables.cpp:714-781, the reachable part: a non-empty list) of a warp's 32
+// blocks, run the way the IQ2 / IQ3 kernels run theirs: every lane stages its block's values and weights in a padded
+// shared-memory row and queues a task per group that is off the codebook; the lists (kept as aligned records of four
+// entries whose tails repeat their first entry, an entry being 16 x its codebook index) are laid end to end and every
+// lane evaluates an equal stretch of records, whatever lists it crosses.  A list's winner is the first strict minimum
+// in list order = the minimum of (distance bits, position) as one 64-bit key (distances are sums of non-negative
+// terms, so their bit patterns order like the values; FLT_MAX and NaN never win, as upstream's `<` against FLT_MAX);
+// a lane that saw a whole list stores its key, lanes that share one combine theirs with a shared-memory atomic
+// minimum.  With one list at a time and all 32 lanes on it (16 shuffles to hand the group over, lists of 1 to 205
+// entries, two warp-wide minima per list) the scans were a fifth of the instructions and half of the time.
+struct alignas(16) ScanTask {
+    uint32_t base;   // the list's first record in the record array
+    uint32_t nrec;   // its length in records
+    float scale;
+    uint32_t xoff;   // float offset of the group in the warp's staged rows; bit 31: the +1/8 levels (else -1/8)
+};
+constexpr unsigned long long kNoWinner = ~0ull;
+
+GGUF_D uint32_t umin_(uint32_t a, uint32_t b) { return a < b ? a : b; }
+
+template <int TMAX>
+GGUF_D void balanced_scan(int lane, int T, uint32_t S, const ScanTask *tasks, const uint32_t *first, unsigned long long *winner,
+                          const float *xs, const float *ws, const uint8_t *__restrict__ grid, const uint2 *__restrict__ recs) {
+    constexpr int AHEAD = 3;  // records are fetched this many iterations early, across list boundaries
+    const uint32_t share = (S + 31) >> 5;
+    uint32_t s = umin_((uint32_t)lane * share, S);
+    const uint32_t end = umin_(s + share, S);
+    if (s >= end) return;
+    int t = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int c = (((i < 4 ? pgw.x : pgw.y) >> (8 * (i & 3))) & 0xFF) >> 1;  // (pg-1)/2 for pg in {1,3,5}
-            const float q = c == 0 ? xg[0] : c == 1 ? xg[1] : xg[2];
-            const float diff = scale * q - xv[i];
-            d2 += wv[i] * diff * diff;
-        }
-        if (d2 < best_score) { best_score = d2; best_j = (uint32_t)j; best = g; }
+    for (int step = TMAX / 2; step; step >>= 1) {
+        const int c = t + step;
+        if (c < T && first[c] <= s) t = c;
     }
-    const uint32_t bits = best_j == 0xFFFFFFFFu ? 0xFFFFFFFFu : __float_as_uint(best_score);
-    const uint32_t low = __reduce_min_sync(kFull, bits);
-    const uint32_t first = __reduce_min_sync(kFull, bits == low ? best_j : 0xFFFFFFFFu);
-    if (first == 0xFFFFFFFFu) return 0;  // nothing comparable (upstream would index with -1)
-    return __shfl_sync(kFull, best, (int)(first & 31u));
+    ScanTask tk;
+    float2 nx[4], wv[4];
+    float sq0, sq1, sq2;   // scale times the three level values
+    auto take = [&](int which) {
+        tk = tasks[which];
+        const float *xr = xs + (tk.xoff & 0x7FFFFFFFu), *wr = ws + (tk.xoff & 0x7FFFFFFFu);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float4 a = reinterpret_cast<const float4 *>(xr)[k], b = reinterpret_cast<const float4 *>(wr)[k];
+            nx[2 * k] = make_float2(-a.x, -a.y); nx[2 * k + 1] = make_float2(-a.z, -a.w);
+            wv[2 * k] = make_float2(b.x, b.y); wv[2 * k + 1] = make_float2(b.z, b.w);
+        }
+        const float shift = (tk.xoff >> 31) ? 0.125f : -0.125f;
+        sq0 = tk.scale * (-1.f + shift);
+        sq1 = tk.scale * shift;
+        sq2 = tk.scale * (1.f + shift);
+    };
+    take(t);
+    uint32_t j = s - first[t];
+    bool whole = j == 0;
+    float best_d2 = FLT_MAX;
+    uint32_t best_at = 0xFFFFFFFFu;
+    int ft = t;
+    uint32_t fleft = tk.nrec - j, fs = s;
+    const uint2 *fp = recs + tk.base + j;
+    uint2 ring[AHEAD];
+    auto fetch = [&](uint2 &rec) {
+        if (fs < end) {
+            rec = __ldg(fp);
+            ++fp;
+            ++fs;
+            if (--fleft == 0 && fs < end) {
+                ++ft;
+                const uint2 h = *reinterpret_cast<const uint2 *>(tasks + ft);
+                fp = recs + h.x;
+                fleft = h.y;
+            }
+        }
+    };
+#pragma unroll
+    for (int d = 0; d < AHEAD; ++d) { ring[d] = make_uint2(0u, 0u); fetch(ring[d]); }
+    while (s < end) {
+        const uint2 rec = ring[0];
+#pragma unroll
+        for (int d = 0; d + 1 < AHEAD; ++d) ring[d] = ring[d + 1];
+        fetch(ring[AHEAD - 1]);
+        const uint32_t at[4] = {rec.x & 0xFFFFu, rec.x >> 16, rec.y & 0xFFFFu, rec.y >> 16};
+        float d2[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            // the codebook row: eight bytes 1, 3 or 5 = level 0, 1 or 2 (bit 2 set: level 2, bit 1 set: level 1)
+            const uint2 row = __ldg(reinterpret_cast<const uint2 *>(grid + (at[q] >> 1)));
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t w = i < 2 ? row.x : row.y;
+                const uint32_t b0 = w >> (16 * (i & 1)), b1 = w >> (16 * (i & 1) + 8);
+                const float qa = (b0 & 4u) ? sq2 : ((b0 & 2u) ? sq1 : sq0);
+                const float qb = (b1 & 4u) ? sq2 : ((b1 & 2u) ? sq1 : sq0);
+                const float2 diff = __fadd2_rn(make_float2(qa, qb), nx[i]);
+                const float2 term = __fmul2_rn(__fmul2_rn(wv[i], diff), diff);
+                acc = __fadd_rn(acc, term.x);
+                acc = __fadd_rn(acc, term.y);
+            }
+            d2[q] = acc;
+        }
+        const uint32_t pos = j << 18;  // (entry position of the step) << 16
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (d2[q] < best_d2) { best_d2 = d2[q]; best_at = pos + ((uint32_t)q << 16) + at[q]; }
+        }
+        ++s;
+        ++j;
+        if (j == tk.nrec) {
+            if (best_d2 < FLT_MAX) {
+                const unsigned long long key = ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at;
+                if (whole) winner[t] = key;
+                else atomicMin(winner + t, key);
+            }
+            ++t;
+            j = 0;
+            whole = true;
+            best_d2 = FLT_MAX;
+            best_at = 0xFFFFFFFFu;
+            if (s < end) take(t);
+        }
+    }
+    if (j != 0 && best_d2 < FLT_MAX)
+        atomicMin(winner + t, ((unsigned long long)__float_as_uint(best_d2) << 32) | best_at);
 }
 
 GGUF_D float level_value(const uint8_t *__restrict__ grid, int index, int i, const float (&xg)[3]) {
@@ -102,7 +195,7 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
                                                             uint8_t *__restrict__ dst, int64_t nblocks, int64_t n_per_row,
                                                             IqSearchTable tab) {
     constexpr int BS = IS_M ? 16 : 32, NG = BS / 8, W = 256 / BS, BYTES = IS_M ? 56 : 50;
-    __shared__ Scratch<BS> s;
+    __shared__ __align__(16) Scratch<BS> s;
     const int t = threadIdx.x;
     const int lane = t & 31, j = lane & (W - 1), gbase = lane & ~(W - 1);
     int64_t blk = (int64_t)blockIdx.x * kThreads + t;
@@ -256,35 +349,85 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
                 uint32_t u = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) u |= (uint32_t)L[8 * k + i] << (2 * i);
-                index[k] = __ldg(tab.map + u);  // negative: off the codebook, scanned below by the whole warp
+                index[k] = __ldg(tab.map_s + u);  // negative: off the codebook; where its list is and how long
             }
             shift = best_k;
         }
     }
-    // the scans: one list at a time, all 32 lanes on it
+    // the scans, spread over the warp (balanced_scan above).  The search's scratch arrays are done with: each warp
+    // takes half of their memory for its rows, its task queue, the lists' positions and the winners.
+    __syncthreads();
+    constexpr int XP = BS + 4, TMAX = 32 * NG;
+    static_assert(sizeof(Scratch<BS>) / 2 >= (2 * 32 * XP + TMAX * 7) * sizeof(float) && (sizeof(Scratch<BS>) / 2) % 16 == 0, "scratch reuse");
+    float *const wbase = reinterpret_cast<float *>(reinterpret_cast<char *>(&s) + (t >> 5) * (sizeof(Scratch<BS>) / 2));
+    float *const xs = wbase, *const ws = wbase + 32 * XP;
+    ScanTask *const tasks = reinterpret_cast<ScanTask *>(wbase + 2 * 32 * XP);
+    unsigned long long *const winner = reinterpret_cast<unsigned long long *>(wbase + 2 * 32 * XP + TMAX * 4);
+    uint32_t *const first = reinterpret_cast<uint32_t *>(wbase + 2 * 32 * XP + TMAX * 6);
+#pragma unroll
+    for (int v = 0; v < BS / 4; ++v) {
+        *reinterpret_cast<float4 *>(xs + lane * XP + 4 * v) = make_float4(xb[4 * v], xb[4 * v + 1], xb[4 * v + 2], xb[4 * v + 3]);
+        *reinterpret_cast<float4 *>(ws + lane * XP + 4 * v) = make_float4(weight[4 * v], weight[4 * v + 1], weight[4 * v + 2], weight[4 * v + 3]);
+    }
     bool all_on_grid = true;
+    {
+        uint32_t queued = 0, total_n = 0;
+        uint32_t nk[NG];
 #pragma unroll
-    for (int k = 0; k < NG; ++k) {
-        const bool mine = !skipped && index[k] < 0;
-        const bool plus = IS_M ? (k == 0 ? shift < 2 : (shift % 2 == 0)) : shift == 1;
-        unsigned pending = __ballot_sync(kFull, mine);
-        while (pending) {
-            const int owner = __ffs(pending) - 1;
-            pending &= pending - 1;
-            const int list = __shfl_sync(kFull, -index[k] - 1, owner);
-            const float sc = __shfl_sync(kFull, scale, owner);
-            const bool pl = __shfl_sync(kFull, (int)plus, owner) != 0;
-            const float xx[3] = {pl ? x_p[0] : x_m[0], pl ? x_p[1] : x_m[1], pl ? x_p[2] : x_m[2]};
-            float xv[8], wv[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                xv[i] = __shfl_sync(kFull, xb[8 * k + i], owner);
-                wv[i] = __shfl_sync(kFull, weight[8 * k + i], owner);
+        for (int k = 0; k < NG; ++k) {
+            nk[k] = 0;
+            if (!skipped && index[k] < 0) {
+                const uint32_t v = (uint32_t)(-index[k] - 1);
+                all_on_grid = false;
+                if ((v & 255u) == 0) {
+                    index[k] = 0;  // an empty list (the codebook has none) is not queued
+                } else {
+                    queued |= 1u << k;
+                    nk[k] = v & 255u;
+                    index[k] = (int)(v >> 8);  // the list's first record until the winner replaces it
+                    total_n += nk[k];
+                }
             }
-            const int g = best_neighbour_ternary(tab.neighbours + list, tab.grid, xv, wv, sc, xx, lane);
-            if (lane == owner) index[k] = g;
         }
-        if (mine) all_on_grid = false;
+        // slots and positions: one inclusive scan over (records << 10 | scans)
+        const uint32_t mine = (total_n << 10) | (uint32_t)__popc(queued);
+        uint32_t incl = mine;
+#pragma unroll
+        for (int dlt = 1; dlt < 32; dlt <<= 1) {
+            const uint32_t o = __shfl_up_sync(kFull, incl, dlt);
+            if (lane >= dlt) incl += o;
+        }
+        const uint32_t all = __shfl_sync(kFull, incl, 31);
+        uint32_t slot = (incl - mine) & 1023u, pos = (incl - mine) >> 10;
+        const uint32_t slot0 = slot;
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            if ((queued >> k) & 1) {
+                const bool plus = IS_M ? (k == 0 ? shift < 2 : (shift % 2 == 0)) : shift == 1;
+                ScanTask tk;
+                tk.base = (uint32_t)index[k];
+                tk.nrec = nk[k];
+                tk.scale = scale;
+                tk.xoff = (uint32_t)(lane * XP + 8 * k) | (plus ? 0x80000000u : 0u);
+                tasks[slot] = tk;
+                first[slot] = pos;
+                winner[slot] = kNoWinner;
+                ++slot;
+                pos += nk[k];
+            }
+        }
+        __syncwarp();
+        if (all >> 10)
+            balanced_scan<TMAX>(lane, (int)(all & 1023u), all >> 10, tasks, first, winner, xs, ws, tab.grid, static_cast<const uint2 *>(tab.records));
+        __syncwarp();
+        slot = slot0;
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+            if ((queued >> k) & 1) {
+                const uint32_t w = ((uint32_t)winner[slot++] & 0xFFFFu) >> 4;  // 16 x index -> index
+                index[k] = w < (uint32_t)tab.grid_size ? (int)w : 0;           // nothing comparable: upstream would index with -1
+            }
+        }
     }
     if (!skipped && !all_on_grid) {
         float sumqx = 0, sumq2 = 0;
@@ -374,7 +517,7 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
 cudaError_t launch_quantize_iq1(int type, const float *src, const float *qw, void *dst, int64_t nelems, int64_t n_per_row,
                                 const DeviceState *state, cudaStream_t stream) {
     const IqSearchTable &tab = state->iq[IQT_1S];
-    if (!tab.grid) return cudaErrorInvalidValue;
+    if (!tab.grid || !tab.records || !tab.map_s || tab.record_steps != 1) return cudaErrorInvalidValue;
     const bool is_m = type == GGML_TYPE_IQ1_M;
     const int64_t nblocks = nelems / (is_m ? 16 : 32);
     if (nblocks <= 0) return cudaSuccess;

@@ -67,7 +67,7 @@ def test_search_tables_equal_upstreams(ref, name):
     assert (nb[offs] > 0).all()
 
 
-@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S"])
+@pytest.mark.parametrize("name", ["IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"])
 def test_scan_records_hold_upstreams_lists(name):
     """The layout the IQ2 / IQ3 kernels scan is derived from the lists above: same entries in the same order, a tail of
     copies of the first entry up to a whole record, records back to back, map_s pointing at them."""
@@ -114,8 +114,8 @@ def test_scan_records_hold_upstreams_lists(name):
 
 def test_scan_records_reject_other_types():
     from libgguf_b200._native import lib
-    assert lib.libgguf_cuda_iq_scan_records(19, None, None, None, None, None) == 2   # IQ1_S scans upstream's lists
     assert lib.libgguf_cuda_iq_scan_records(12, None, None, None, None, None) == 2
+    assert lib.libgguf_cuda_iq_scan_records(20, None, None, None, None, None) == 2   # IQ4_NL has no lattice search
 
 
 def test_search_table_rejects_other_types():
