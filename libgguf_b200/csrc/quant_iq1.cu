@@ -165,10 +165,10 @@ GGUF_D float level_value(const uint8_t *__restrict__ grid, int index, int i, con
 
 template <int BS>
 struct Scratch {
-    float ws[BS][kThreads];       // weights, by element; once they are no longer needed, the level of each element
+    float ws[BS][kThreads];       // weights, by element
     float pa[BS + 1][kThreads];   // sort keys (the values), then prefix sums of w*x (IQ1_S)
     float pb[BS + 1][kThreads];   // prefix sums of w (IQ1_S)
-    uint8_t order[BS][kThreads];  // element index at each sorted position
+    uint8_t order[BS][kThreads];  // element index at each sorted position; after the search, the level of each element
 };
 
 // Stable ascending insertion sort of the keys in s.pa[0..BS) with their element indices
@@ -358,14 +358,23 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
             }
             if (besti1 < 0 || besti2 < 0 || best_k < 0) skipped = true;
         }
+        // The block's values and weights are not kept in registers across the search (the search needs them for itself):
+        // the values are read again from the source row, the weights from their scratch rows.
+        load_group<BS>(src + blk * BS, xb);
+#pragma unroll
+        for (int i = 0; i < BS; ++i) weight[i] = s.ws[i][t];
         if (skipped) {
             scale = 0.f;
         } else {
-            uint8_t (*level)[kThreads] = reinterpret_cast<uint8_t (*)[kThreads]>(&s.ws[0][0]);  // the weights are done with
-            for (int jj = 0; jj < BS; ++jj) level[s.order[jj][t]][t] = (uint8_t)(jj < besti1 ? 0 : (jj < besti2 ? 1 : 2));
+            // the level of every element: the sorted order is read out, then its column (this thread's own) takes the levels
+            uint8_t at_position[BS];
+#pragma unroll
+            for (int jj = 0; jj < BS; ++jj) at_position[jj] = s.order[jj][t];
+#pragma unroll
+            for (int jj = 0; jj < BS; ++jj) s.order[at_position[jj]][t] = (uint8_t)(jj < besti1 ? 0 : (jj < besti2 ? 1 : 2));
             int L[BS];
 #pragma unroll
-            for (int i = 0; i < BS; ++i) L[i] = level[i][t];
+            for (int i = 0; i < BS; ++i) L[i] = s.order[i][t];
             if (scale < 0) {
 #pragma unroll
                 for (int i = 0; i < BS; ++i) L[i] = 2 - L[i];
