@@ -1,13 +1,14 @@
 // Ternary lattice quantizers IQ1_S (32-element blocks) and IQ1_M (16-element blocks).
 //
-// One thread per block.  The upstream algorithm sorts the block's values, then searches all
-// split points (i1 <= i2) of the sorted order into the three levels {-1, 0, +1} (+- a fixed
-// shift), keeping the split with the best weighted projection score; the accept/reject chain is
-// order dependent through fp32 rounding, so it is replayed sequentially.  The winning level
-// pattern of each group of eight is then mapped to the 2048-entry codebook, through the
-// neighbour lists when it is not a codebook point.  Arrays that are indexed by data (the sorted
-// order, the prefix sums, the level scatter) live in shared memory, laid out [index][thread] so
-// that the uniform loops of a warp hit one row; everything indexed statically stays in registers.
+// One thread per block.  The upstream algorithm sorts the block's values (here: by counting ranks
+// in registers), then searches all split points (i1 <= i2) of the sorted order into the three
+// levels {-1, 0, +1} (+- a fixed shift), keeping the split with the best weighted projection score;
+// the accept/reject chain is order dependent through fp32 rounding, so it is replayed sequentially.
+// The winning level pattern of each group of eight is then mapped to the 2048-entry codebook,
+// through the neighbour lists when it is not a codebook point: those scans are pooled per warp and
+// spread evenly over its lanes.  Arrays that are indexed by data (the sorted order, the prefix sums,
+// the level scatter) live in shared memory, laid out [index][thread] so that the uniform loops of a
+// warp hit one row; everything indexed statically stays in registers; the scans reuse that memory.
 // upstream: csrc/quant/iq1_s.cpp:6-204, iq1_m.cpp:4-318, libgguf_iq_tables.cpp:714-789.
 #include <float.h>
 #include <math.h>
