@@ -359,11 +359,14 @@ __global__ void __launch_bounds__(kThreads, IS_M ? 8 : 7) quant_iq1_kernel(const
             }
             if (besti1 < 0 || besti2 < 0 || best_k < 0) skipped = true;
         }
-        // The block's values and weights are not kept in registers across the search (the search needs them for itself):
-        // the values are read again from the source row, the weights from their scratch rows.
-        load_group<BS>(src + blk * BS, xb);
+        // IQ1_M: the block's values and weights are not kept in registers across the search (the search needs them for
+        // itself): the values are read again from the source row, the weights from their scratch rows.  (IQ1_S, whose
+        // search works on prefix sums in shared memory, has the registers to keep them.)
+        if constexpr (IS_M) {
+            load_group<BS>(src + blk * BS, xb);
 #pragma unroll
-        for (int i = 0; i < BS; ++i) weight[i] = s.ws[i][t];
+            for (int i = 0; i < BS; ++i) weight[i] = s.ws[i][t];
+        }
         if (skipped) {
             scale = 0.f;
         } else {
